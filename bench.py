@@ -1,0 +1,318 @@
+"""MoE-layer throughput benchmark for the B200 MoE expert hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A step is one pass of the MoE layer (router top-K -> token grouping -> MXFP8
+activation quantisation -> grouped gate/up contraction + SwiGLU -> grouped down
+contraction + affinity -> combine) over one batch of seeded synthetic tokens.
+Rank 0 prints one JSON line.  ``value`` is tokens/s with inputs resident in HBM;
+``e2e`` is the same metric through the public API with host buffers (pinned
+host -> device copy of the tokens and device -> host copy of the result inside
+the timed region).  ``--impl reference`` times the reference's CPU algorithm
+(the oracle restatement) on this host's cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs that fit one GPU (configs[1] is the headline prefill case)
+WORKLOADS = {
+    "mixtral_prefill": dict(kind="prefill", T=4096, H=4096, I=14336, E=8, K=2, B=512, zipf=None),
+    "mixtral_decode": dict(kind="decode", T=64, H=4096, I=14336, E=8, K=2, B=128, zipf=None),
+    "finegrained_prefill": dict(kind="prefill", T=8192, H=7168, I=2048, E=256, K=8, B=128, zipf=1.2),
+    "ep_prefill": dict(kind="prefill", T=32768, H=4096, I=1536, E=128, K=8, B=256, zipf=None),
+    "tiny_prefill": dict(kind="prefill", T=256, H=512, I=1024, E=4, K=2, B=128, zipf=None),
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        busy = [s for s in sm if s > 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def algorithmic_work(cfg):
+    """Figures used for roofline.achieved: useful work only, no padding rows, no re-reads."""
+    T, H, I, E, K = cfg["T"], cfg["H"], cfg["I"], cfg["E"], cfg["K"]
+    return {
+        "gemm1_flops": 4.0 * T * K * H * I,
+        "gemm2_flops": 2.0 * T * K * H * I,
+        "layer_flops": 6.0 * T * K * H * I,
+        # decode: every expert's weights and scales once, tokens in and out, router weight
+        "decode_bytes": E * 3.0 * H * I * (1 + 1 / 32) + 2.0 * T * H * 2 + H * E * 2,
+        "gemm1_weight_bytes": E * 2.0 * H * I * (1 + 1 / 32),
+        "gemm2_weight_bytes": E * 1.0 * H * I * (1 + 1 / 32),
+    }
+
+
+def make_inputs(cfg, device, seed):
+    import torch
+    g = torch.Generator()
+    g.manual_seed(1234 + seed)
+    T, H, E = cfg["T"], cfg["H"], cfg["E"]
+    hidden = torch.randn((T, H), generator=g, dtype=torch.float32).to(torch.bfloat16)
+    router_w = (torch.randn((H, E), generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    bias = None
+    if cfg["zipf"] is not None:
+        rank = torch.randperm(E, generator=g).float() + 1.0
+        bias = (-cfg["zipf"] * torch.log(rank)).to(torch.bfloat16)
+    return hidden, router_w, bias
+
+
+# ------------------------------------------------------------------ CPU legs (oracle)
+def cpu_sample(cfg, steps, warmup, threads):
+    """Time the oracle restatement of the reference's per-block golden loop on a bounded sample.
+
+    Sample: ``n_rows`` token-expert rows of one expert at the workload's H and I
+    (one weight dequantisation + the block recipe), which is how the reference's
+    golden walks blocks.  tokens/s = rows / K / time.
+    """
+    import numpy as np
+    import torch
+
+    from oracle import moe, mx
+    torch.set_num_threads(threads)
+    H, I, K = cfg["H"], cfg["I"], cfg["K"]
+    n_rows = min(cfg["T"] * K // max(cfg["E"], 1), 512) if cfg["kind"] == "prefill" else max(cfg["T"] * K // cfg["E"], 1)
+    n_rows = max(n_rows, 1)
+    rng = np.random.default_rng(0)
+    c1 = rng.integers(0, 0x7E, size=(1, 2, I, H), dtype=np.uint8)
+    s1 = rng.integers(110, 120, size=(1, 2, I, H // 32), dtype=np.uint8)
+    c2 = rng.integers(0, 0x7E, size=(1, H, I), dtype=np.uint8)
+    s2 = rng.integers(110, 120, size=(1, H, I // 32), dtype=np.uint8)
+    x = torch.randn(n_rows, H).to(torch.bfloat16).float().numpy()
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        ew = moe.ExpertWeights(c1, s1, c2, s2, 0)
+        y = moe.expert_mlp_rows(x, ew)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+        del ew, y
+    t = sum(times) / len(times)
+    return dict(value=n_rows / K / t, seconds_per_step=t, rows=n_rows,
+                sample=f"{n_rows} token-expert rows through one expert (dequantise weights + quantise/gate-up/SwiGLU/"
+                       f"re-quantise/down) at H={H}, I={I}; tokens/s = rows/K/time")
+
+
+def run_reference(args, cfg, name):
+    threads = os.cpu_count() or 1
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    r = cpu_sample(cfg, steps, 1 if args.warmup > 0 else 0, threads)
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": r["value"], "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": 1 if args.warmup > 0 else 0,
+        "ms_per_step": r["seconds_per_step"] * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "mxfp8_e4m3", "data": "synthetic", "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}},
+        "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ GPU leg
+def run_ours(args, cfg, name):
+    import torch
+    import torch.distributed as dist
+
+    import nki_library_b200 as m
+    from nki_library_b200.layer import MoELayer, random_expert_weights
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    T, H, I, E, K, B = (cfg[k] for k in "THIEKB")
+
+    # Experts are independent given the routing, so N GPUs run as N replicas of the
+    # single-GPU layer on their own token batches (weak scaling, no data-path collective).
+    weights = random_expert_weights(E, H, I, dev, seed=7)
+    hidden_h, router_w, bias = make_inputs(cfg, dev, rank)
+    hidden_pin = hidden_h.pin_memory()
+    out_pin = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+    hidden_d = hidden_h.to(dev)
+    layer = MoELayer(router_w.to(dev), weights, K, B, T, None if bias is None else bias.to(dev))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        layer.forward(hidden_d)
+    barrier()
+    status = layer.device_status()
+    if any(status):
+        raise RuntimeError(f"device status after warm-up: {status}")
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.2)
+    # -------- resident-input leg (value) with per-kernel events
+    timers = {}
+    barrier()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for _ in range(args.steps):
+        layer.forward(hidden_d, timers)
+    t_end.record()
+    barrier()
+    ms_total = t_start.elapsed_time(t_end)
+    # -------- end-to-end leg: host buffers through the public layer call
+    barrier()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        hidden_d.copy_(hidden_pin, non_blocking=True)
+        out = layer.forward(hidden_d)
+        out_pin.copy_(out, non_blocking=True)
+    e_end.record()
+    barrier()
+    ms_e2e = e_start.elapsed_time(e_end)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if world > 1:
+        t = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = t.tolist()
+    status = layer.device_status()
+    if any(status):
+        raise RuntimeError(f"device status after timing: {status}")
+
+    if rank == 0:
+        work = algorithmic_work(cfg)
+        per_kernel = {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in timers.items()}
+        ms_step = ms_total / args.steps
+        if cfg["kind"] == "prefill":
+            dom = "gemm1_swiglu"
+            peak = 2.0 * peaks["bf16_tflops"]
+            achieved = work["gemm1_flops"] / (per_kernel[dom] * 1e-3) / 1e12
+            roofline = {"bound": "tensor", "kernel": "grouped_mxfp8_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
+                        "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                        "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s); "
+                                       "dense fp8/mxfp8 issues at twice the bf16 rate",
+                        "layer_tflops": work["layer_flops"] / (ms_step * 1e-3) / 1e12}
+        else:
+            dom = "gemm1_swiglu"
+            peak = peaks["hbm_gbs"]
+            achieved = work["gemm1_weight_bytes"] / (per_kernel[dom] * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "kernel": "grouped_mxfp8_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
+                        "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                        "peak_source": f"{peaks['source']} copy bandwidth",
+                        "layer_gbs": work["decode_bytes"] / (ms_step * 1e-3) / 1e9}
+        cpu = cpu_sample(cfg, 2, 1, os.cpu_count() or 1)
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": world * T / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8_e4m3",
+            "data": "synthetic",
+            "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}, "n_blocks": layer.N,
+                       "parallelism": f"replicas x{world}" if world > 1 else "single",
+                       "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)" % (weights.nbytes() / 1e9)},
+            "roofline": roofline,
+            "kernel_ms": per_kernel,
+            "cpu_baseline": {"value": cpu["value"], "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+                             "sample": cpu["sample"]},
+            "e2e": {"value": world * T / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2},
+            "gpu_launches": layer.kernels_per_forward * args.steps * 2,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mixtral_prefill", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, cfg, args.workload)
+    else:
+        run_ours(args, cfg, args.workload)
+
+
+if __name__ == "__main__":
+    main()

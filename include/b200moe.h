@@ -1,0 +1,190 @@
+/*
+ * b200moe.h -- C ABI of the B200 (sm_100a) MoE expert hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, never
+ * allocates or frees user-visible memory, never synchronises the stream, and
+ * returns 0 on success or a negative B200MOE_ERR_* code (details through
+ * b200moe_last_error()).  Scratch memory is supplied by the caller; its size
+ * comes from the matching *_workspace_bytes query.
+ *
+ * Each function names the reference interface it stands in for (paths are
+ * relative to the reference project root).  The Python package in
+ * nki_library_b200/ binds these with ctypes and re-exposes the reference's
+ * kernel signatures.
+ *
+ * Device data formats
+ *   "rows" fp8 operand ... uint8 e4m3fn codes [rows, K], K contiguous.
+ *   "scale atoms" ........ UE8M0 bytes, one per (row, 32 consecutive K), stored as
+ *                          512-byte atoms ordered [ceil(rows/128)][ceil(K/128)];
+ *                          byte of (r, c) in an atom at (r%32)*16 + (r/32)*4 + c.
+ *                          Size: b200moe_sf_bytes(rows, K).  Unused bytes must be 0.
+ *   gate/up device weight  [E, 2I, H]: rows interleaved per 32 intermediate
+ *                          columns (32 gate rows, then the matching 32 up rows).
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* b200moe_stream_t; /* cudaStream_t */
+
+enum {
+  B200MOE_OK = 0,
+  B200MOE_ERR_INVALID = -1,   /* argument validation failed */
+  B200MOE_ERR_CUDA = -2,      /* a CUDA runtime/driver call failed */
+  B200MOE_ERR_WORKSPACE = -3, /* workspace too small */
+  B200MOE_ERR_DEVICE = -4     /* kernel reported an error through its status word */
+};
+
+/* element types of loosely typed pointers */
+enum { B200MOE_F32 = 0, B200MOE_BF16 = 1, B200MOE_I32 = 2 };
+/* ActFnType (core/utils/common_types.py:32-36) */
+enum { B200MOE_ACT_SILU = 0, B200MOE_ACT_GELU = 1, B200MOE_ACT_GELU_TANH = 2, B200MOE_ACT_SWISH = 3 };
+/* RouterActFnType (core/utils/common_types.py:39-46) */
+enum { B200MOE_ROUTER_SIGMOID = 0, B200MOE_ROUTER_SOFTMAX = 1 };
+/* weight source layouts accepted by the prepare functions */
+enum { B200MOE_LAYOUT_ROWS = 0, B200MOE_LAYOUT_NKI_X4 = 1 };
+/* routing source accepted by b200moe_group_tokens */
+enum { B200MOE_ROUTING_INDEX = 0, B200MOE_ROUTING_MASK = 1 };
+
+/* Message describing the last failure on the calling thread ("" if none).
+ * Stands in for kernel_assert's exception text (core/utils/kernel_assert.py:15-16). */
+const char* b200moe_last_error(void);
+int b200moe_version(void);
+
+/* Bytes of a scale-atom buffer for a [rows, K] operand. */
+size_t b200moe_sf_bytes(int64_t rows, int64_t K);
+
+/* ---- router ------------------------------------------------------------------
+ * router_topk (core/router_topk/router_topk.py:55-75): logits = x @ w (+ bias) in
+ * fp32, top-k (ties -> lowest expert id), affinities by one of the three pipelines
+ * (router_topk.py:515-547).  x is bf16 [T,H] (x_is_TH=1) or [H,T]; w bf16 [H,E];
+ * w_bias bf16 [E] or NULL.  Outputs (each may be NULL to skip): router_logits
+ * [T,E], expert_index uint32 [T,k], expert_affinities [T,E] (dense, zeros outside
+ * the top-k when scattered).  E <= 512, k <= 8. */
+int b200moe_router_topk(const void* x, int x_is_TH, const void* w, const void* w_bias, int T, int H, int E, int k,
+                        int act_fn, int router_pre_norm, int norm_topk_prob, void* router_logits, int logits_dtype,
+                        uint32_t* expert_index, void* expert_affinities, int aff_dtype, b200moe_stream_t stream);
+
+/* ---- grouping ----------------------------------------------------------------
+ * find_nonzero_indices (core/subkernels/find_nonzero_indices.py:34-40): per column
+ * c of input [T, C_full] (f32 / bf16 / i32), ascending row ids of non-zeros padded
+ * with -1 to length T, and their count.  col_start_dev: device int32[1] or NULL. */
+size_t b200moe_find_nonzero_workspace_bytes(int T, int n_cols);
+int b200moe_find_nonzero_indices(const void* input, int in_dtype, int T, int C_full, const int32_t* col_start_dev,
+                                 int n_cols, int32_t* indices, int32_t* nonzero_counts, void* workspace,
+                                 size_t workspace_bytes, b200moe_stream_t stream);
+
+/* cumsum (core/cumsum/cumsum.py:29): inclusive, along the last axis, fp32 accumulate. */
+int b200moe_cumsum(const void* x, int dtype, int64_t rows, int64_t cols, void* out, b200moe_stream_t stream);
+
+/* indexed_flatten (core/subkernels/indexed_flatten.py:28-35): out[(row_offsets[s+e]+p)*f_len + j]
+ * = input[e, p*f_len + j]; the highest e wins where rows overlap; blocks outside
+ * the output are dropped; the rest is padding_val. */
+int b200moe_indexed_flatten(const int32_t* input, int E, int T, int f_len, int64_t output_len,
+                            const int32_t* row_offsets, int n_row_offsets, const int32_t* row_offsets_start_dev,
+                            int padding_val, int32_t* out, b200moe_stream_t stream);
+
+/* Fused grouping = find_nonzero_indices + cumsum + indexed_flatten plus the
+ * block_to_expert / conditions bookkeeping of the reference's block-assignment
+ * generator (test/integration/nkilib/core/moe/moe_cte/test_moe_cte_common.py:199-264).
+ * routing: uint32/int32 expert ids [T,K] (B200MOE_ROUTING_INDEX) or a [T,E] mask /
+ * masked affinities of routing_dtype (B200MOE_ROUTING_MASK, K ignored).
+ * Outputs: token_position_to_id [N*B] (pad -1 if skip_token else T), block_to_expert
+ * [N], conditions [N+2] (mx_conditions) or [N+1], counts [E], inverse_map [T,K]
+ * (position of each (t,k) pair; NULL to skip; index mode only), status[0] != 0 if N
+ * was too small for the routing. */
+size_t b200moe_group_tokens_workspace_bytes(int T, int E);
+int b200moe_group_tokens(const void* routing, int routing_mode, int routing_dtype, int T, int E, int K, int B, int N,
+                         int skip_token, int mx_conditions, int32_t* token_position_to_id, int32_t* block_to_expert,
+                         int32_t* conditions, int32_t* counts, int32_t* inverse_map, int32_t* status, void* workspace,
+                         size_t workspace_bytes, b200moe_stream_t stream);
+
+/* position table for the combine when only token_position_to_id is known (moe_cte's
+ * own argument list): pos_table[t*E + e] = position of token t in a block of expert e, else -1. */
+int b200moe_build_position_table(const int32_t* token_position_to_id, const int32_t* block_to_expert,
+                                 const int32_t* conditions, int n_blocks, int B, int T, int E, int32_t* pos_table,
+                                 b200moe_stream_t stream);
+
+/* ---- MXFP8 activation quantisation --------------------------------------------
+ * load_and_quantize_hidden_states (core/moe/moe_cte/moe_cte_mx_utils.py:456-945) with
+ * nisa.quantize_mx semantics as defined on CPU by quantize_to_mx
+ * (core/utils/mx_torch_common.py:157-221).  Row p of the output is
+ * hidden[token_position_to_id[p]] (zeros for pad ids; identity if the pointer is
+ * NULL), with the H axis taken in the reference's packed order
+ * k' = t*512 + p*4 + q <- h = q*(H/4) + t*128 + p when h_packed_order != 0.
+ * tile_flags (int32 [ceil(n_pos/128)], may be NULL) is set to 1 for every
+ * 128-position tile that holds at least one real token; the contractions skip
+ * the others. */
+int b200moe_gather_quantize_mxfp8(const void* hidden_bf16, int hidden_rows, int H, const int32_t* token_position_to_id,
+                                  int64_t n_pos, int h_packed_order, uint8_t* codes, uint8_t* sf_atoms,
+                                  int32_t* tile_flags, b200moe_stream_t stream);
+
+/* ---- weight preparation (once per model load) ----------------------------------
+ * Source B200MOE_LAYOUT_ROWS: codes [E,2,I,H] + scales [E,2,I,H/32] (gate_up) and
+ * codes [E,H,I] + scales [E,H,I/32] (down).
+ * Source B200MOE_LAYOUT_NKI_X4: the reference's storage
+ * gate_up [E,128,2,H/512,I] x4 + scale [E,16,2,H/512,I],
+ * down [E,p_I,ceil(I/512),H] x4 + scale [E,p_I/8,ceil(I/512),H]
+ * (core/moe/moe_cte/bwmm_shard_on_block_mx.py:70-230).
+ * Bias sources: gate_up [E,2,I] fp32 (ROWS) or [E,p_I,2,ceil(I/512),4] (NKI_X4), any of F32/BF16. */
+int b200moe_prepare_gate_up(const void* w, const uint8_t* scale, int layout, int E, int H, int I, uint8_t* w_dev,
+                            uint8_t* sf_dev, b200moe_stream_t stream);
+int b200moe_prepare_down(const void* w, const uint8_t* scale, int layout, int E, int H, int I, uint8_t* w_dev,
+                         uint8_t* sf_dev, b200moe_stream_t stream);
+int b200moe_prepare_gate_up_bias(const void* bias, int dtype, int layout, int E, int I, float* bias_dev,
+                                 b200moe_stream_t stream);
+
+/* ---- grouped expert contractions -----------------------------------------------
+ * Parameters common to both: block_to_expert [n_blocks]; conditions (NULL = all
+ * blocks run; otherwise a block runs iff conditions[b] != 0); tile_flags (NULL = all
+ * tiles run; see b200moe_gather_quantize_mxfp8); token_position_to_id [n_blocks*B] and
+ * hidden_rows (ids outside [0, hidden_rows) are pads, their rows are not written); status: device
+ * int32[1], set non-zero if a kernel-internal wait ran out; impl: 0 = tcgen05
+ * tensor-core kernel, 1 = plain CUDA-core validation kernel (slow, same results
+ * up to summation order).
+ *
+ * gemm1 = gate_up_projection_mx + clamp + act(gate)*up + quantize_mx of the result
+ * (core/mlp/mlp_tkg/gate_up_projection_mx_shard_H.py:48-225,
+ *  core/moe/moe_cte/bwmm_shard_on_block_mx.py:1159-1278,
+ *  core/mlp/mlp_tkg/down_projection_mx_shard_H.py:73-78).  Clamp limits are
+ * ignored when NaN.  Output: codes [n_blocks*B, I] + scale atoms. */
+int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_t* x_sf, const uint8_t* w1_dev,
+                                 const uint8_t* w1_sf, const float* bias_gu_dev, const int32_t* block_to_expert,
+                                 const int32_t* conditions, const int32_t* tile_flags,
+                                 int n_blocks, int B, int E, int H, int I, int act_fn, float gate_lo, float gate_hi,
+                                 float up_lo, float up_hi, uint8_t* m_codes, uint8_t* m_sf, int32_t* status, int impl,
+                                 b200moe_stream_t stream);
+
+/* gemm2 = down_projection_mx + bias + affinity scaling of each row
+ * (core/mlp/mlp_tkg/down_projection_mx_shard_H.py:212-387,
+ *  core/moe/moe_cte/bwmm_shard_on_block_mx.py:1297-1317).  affinities is the flat
+ * [(rows)*E] table addressed tok*E + e (core/moe/moe_cte/moe_cte_utils.py:544-636),
+ * or NULL for no scaling.  Output: bf16 y_pos [n_blocks*B, H] (pad rows untouched). */
+int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
+                                const uint8_t* w2_sf, const float* bias_d, const int32_t* block_to_expert,
+                                const int32_t* conditions, const int32_t* tile_flags,
+                                const int32_t* token_position_to_id, int hidden_rows,
+                                int n_blocks, int B, int E, int H, int I, const void* affinities, int aff_dtype,
+                                void* y_pos_bf16, int32_t* status, int impl, b200moe_stream_t stream);
+
+/* Weight rows per tile of the tensor-core kernel: 256 (default) or 128.  Tuning knob
+ * with no counterpart in the reference. */
+int b200moe_set_gemm_tile_n(int block_n);
+
+/* combine = the accumulate-and-scatter tail of the block loop
+ * (core/moe/moe_cte/bwmm_shard_on_block_mx.py:1303-1347): out[t,:] = sum over the
+ * valid entries p = table[t, j] (j ascending) of y_pos[p,:], fp32 accumulation,
+ * one bf16 rounding.  table is inverse_map [T,K] or a position table [T,E]. */
+int b200moe_combine(const void* y_pos_bf16, const int32_t* table, int T, int n_cand, int H, void* out_bf16,
+                    b200moe_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

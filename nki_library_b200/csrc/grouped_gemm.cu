@@ -1,0 +1,654 @@
+// Grouped MXFP8 expert contractions on the sm_100a tensor cores.
+//
+// One persistent, warp-specialised kernel template serves both projections:
+//   warp 0      TMA producer: per 128-byte K slab, a [128 x 128B] tile of the
+//               activation rows, a [BLOCK_N x 128B] tile of the expert's weight
+//               rows (both 128B-swizzled) and their UE8M0 scale atoms (bulk copies)
+//   warp 1      allocates TMEM and issues tcgen05.cp (scales -> TMEM) followed by
+//               four tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 each) per slab
+//   warps 2..5  epilogue: tcgen05.ld of the fp32 accumulator (one row per thread)
+//               EPI 0: + bias, clamp, act(gate) * up, bf16 rounding, MXFP8
+//                      re-quantisation (32 consecutive intermediates live in one
+//                      thread), codes + scale atoms out
+//               EPI 1: + bias, x routing affinity, bf16 rows out
+// Tiles are (128 positions) x (BLOCK_N weight rows); a tile's expert comes from
+// block_to_expert, padded / inactive tiles are skipped.  The tile order walks
+// 16 consecutive position tiles per weight tile so CTAs running side by side
+// share a weight tile in L2.  Every mbarrier wait is bounded: on expiry the
+// kernel records a code in `status`, stops issuing work and tears down.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 128;  // bytes (= e4m3 elements) per pipeline slab
+constexpr int kGroupM = 16;
+constexpr int kThreads = 192;
+constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+
+struct GemmParams {
+  const uint8_t* a_sf;
+  const uint8_t* b_sf;
+  int64_t b_sf_expert_stride;
+  int b_row_atoms;  // scale atoms along the weight-row axis per expert
+  const int32_t* block_to_expert;
+  const int32_t* conditions;
+  const int32_t* tile_flags;  // per 128-position tile: non-zero if it holds a real token (NULL = all)
+  const int32_t* tpi;
+  int hidden_rows, n_blocks, B, E;
+  int m_tiles_total, n_tiles, k_blocks;
+  int n_total;  // weight rows per expert
+  const float* bias;
+  int act;
+  float gate_lo, gate_hi, up_lo, up_hi;
+  uint8_t* m_codes;
+  uint8_t* m_sf;
+  int I;
+  const void* aff;
+  int aff_dtype;
+  __nv_bfloat16* y_pos;
+  int H_out;
+  int32_t* status;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false once the budget is spent or another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand tile, rows of 128 bytes, 128B swizzle: 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+  uint64_t d = static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;             // leading byte offset (unused for swizzled K-major)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;     // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;             // descriptor version (Blackwell)
+  d |= static_cast<uint64_t>(2) << 61;             // SWIZZLE_128B
+  return d;
+}
+// Scale atom: 32 rows of 16 bytes, no swizzle, 8-row groups 128 B apart.
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+  uint64_t d = static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+// kind::mxf8f6f4 block-scaled instruction descriptor: e4m3 x e4m3, UE8M0 scales, K-major A and B.
+__host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
+  return (0u << 7) | (0u << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (1u << 23) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, int& m_tile, int& n_tile, int& expert) {
+  const int per_group = kGroupM * p.n_tiles;
+  const int g = tile / per_group;
+  const int first_m = g * kGroupM;
+  const int gs = min(kGroupM, p.m_tiles_total - first_m);
+  const int within = tile - g * per_group;
+  m_tile = first_m + within % gs;
+  n_tile = within / gs;
+  const int block = m_tile / (p.B >> 7);
+  if (p.conditions != nullptr && p.conditions[block] == 0) return false;
+  if (p.tile_flags != nullptr && p.tile_flags[m_tile] == 0) return false;
+  expert = p.block_to_expert[block];
+  return expert >= 0 && expert < p.E;
+}
+
+template <int BLOCK_N, int STAGES>
+struct SmemLayout {
+  static constexpr int kA = kBlockM * kBlockK;
+  static constexpr int kB = BLOCK_N * kBlockK;
+  static constexpr int kSfa = 512;
+  static constexpr int kSfb = (BLOCK_N / 128) * 512;
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kOffA + STAGES * kA;
+  static constexpr int kOffSfa = kOffB + STAGES * kB;
+  static constexpr int kOffSfb = kOffSfa + STAGES * kSfa;
+  static constexpr int kOffBar = kOffSfb + STAGES * kSfb;
+  static constexpr int kBytes = kOffBar + 512 + 1024;  // barriers + alignment slack
+};
+
+template <int BLOCK_N, int STAGES, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const GemmParams p) {
+  using L = SmemLayout<BLOCK_N, STAGES>;
+  constexpr int kAcc = (BLOCK_N <= 128) ? 2 : 1;
+  constexpr int kSfCol = kAcc * BLOCK_N;  // TMEM columns: accumulators, then SFA (4), then SFB
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kIdesc = make_idesc(kBlockM, BLOCK_N);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tmem_full = bars + 2 * STAGES;
+  uint64_t* tmem_empty = bars + 2 * STAGES + kAcc;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * kAcc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles_total * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < kAcc; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int m_tile, n_tile, e;
+        if (!decode_tile(p, tile, m_tile, n_tile, e)) continue;
+        const uint8_t* sfa = p.a_sf + static_cast<int64_t>(m_tile) * p.k_blocks * 512;
+        const uint8_t* sfb = p.b_sf + static_cast<int64_t>(e) * p.b_sf_expert_stride;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+          uint32_t bytes = L::kA + L::kB + L::kSfa;
+          int n_sfb = 0;
+#pragma unroll
+          for (int j = 0; j < BLOCK_N / 128; ++j)
+            if (n_tile * (BLOCK_N / 128) + j < p.b_row_atoms) ++n_sfb;
+          bytes += n_sfb * 512;
+          mbar_expect_tx(&full[stage], bytes);
+          tma_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
+          tma_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK, n_tile * BLOCK_N, e, &full[stage]);
+          bulk_load(smem + L::kOffSfa + stage * L::kSfa, sfa + static_cast<int64_t>(kb) * 512, 512, &full[stage]);
+          for (int j = 0; j < n_sfb; ++j)
+            bulk_load(smem + L::kOffSfb + stage * L::kSfb + j * 512,
+                      sfb + (static_cast<int64_t>(n_tile * (BLOCK_N / 128) + j) * p.k_blocks + kb) * 512, 512,
+                      &full[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // let copies already in flight land before the CTA retires
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int m_tile, n_tile, e;
+        if (!decode_tile(p, tile, m_tile, n_tile, e)) continue;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        const uint32_t sfa_tmem = tmem_base + kSfCol;
+        const uint32_t sfb_tmem = tmem_base + kSfCol + 4;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
+          tc_fence_after();
+          tc_cp_sf(sfa_tmem, desc_sf(smem_u32(smem + L::kOffSfa + stage * L::kSfa)));
+#pragma unroll
+          for (int j = 0; j < BLOCK_N / 128; ++j)
+            tc_cp_sf(sfb_tmem + 4 * j, desc_sf(smem_u32(smem + L::kOffSfb + stage * L::kSfb + j * 512)));
+          const uint64_t a_desc = desc_sw128(smem_u32(smem + L::kOffA + stage * L::kA));
+          const uint64_t b_desc = desc_sw128(smem_u32(smem + L::kOffB + stage * L::kB));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t idesc = kIdesc | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
+            tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(&tmem_full[acc]);
+        if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      int m_tile, n_tile, e;
+      if (!decode_tile(p, tile, m_tile, n_tile, e)) continue;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, 4)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
+      const int64_t row = static_cast<int64_t>(m_tile) * kBlockM + row_in_tile;
+      if constexpr (EPI == 0) {
+        const int64_t k_atoms = (p.I + 127) >> 7;
+        const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.n_total : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 64; ++c) {
+          float g[32], u[32];
+          tc_ld32(taddr + c * 64, g);
+          tc_ld32(taddr + c * 64 + 32, u);
+          const int n0 = n_tile * BLOCK_N + c * 64;
+          const int i0 = n0 >> 1;
+          if (i0 >= p.I) continue;
+          uint32_t mx = 0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float gv = g[j], uv = u[j];
+            if (bias) { gv += bias[n0 + j]; uv += bias[n0 + 32 + j]; }
+            if (p.gate_lo == p.gate_lo) gv = fmaxf(gv, p.gate_lo);
+            if (p.gate_hi == p.gate_hi) gv = fminf(gv, p.gate_hi);
+            if (p.up_lo == p.up_lo) uv = fmaxf(uv, p.up_lo);
+            if (p.up_hi == p.up_hi) uv = fminf(uv, p.up_hi);
+            const float m = __bfloat162float(__float2bfloat16_rn(apply_act(gv, p.act) * uv));
+            g[j] = m;
+            mx = max(mx, __float_as_uint(m) & 0x7fffffffu);
+          }
+          float f1, f2;
+          mx_block_factors(mx, f1, f2);
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            w[j] = pack4_e4m3(g[4 * j] * f1 * f2, g[4 * j + 1] * f1 * f2, g[4 * j + 2] * f1 * f2, g[4 * j + 3] * f1 * f2);
+          uint4* dst = reinterpret_cast<uint4*>(p.m_codes + row * p.I + i0);
+          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          p.m_sf[sf_atom_offset(row, i0 >> 5, k_atoms)] = mx_block_scale_byte(mx);
+        }
+      } else {
+        const int tok = p.tpi ? p.tpi[row] : static_cast<int>(row);
+        const bool valid = tok >= 0 && tok < p.hidden_rows;
+        float aff = 1.0f;
+        if (valid && p.aff != nullptr) aff = load_as_float(p.aff, static_cast<int64_t>(tok) * p.E + e, p.aff_dtype);
+        const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.H_out : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          float v[32];
+          tc_ld32(taddr + c * 32, v);
+          const int col0 = n_tile * BLOCK_N + c * 32;
+          if (col0 >= p.H_out || !valid) continue;
+          uint32_t o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float a0 = v[2 * j], a1 = v[2 * j + 1];
+            if (bias) { a0 += bias[col0 + 2 * j]; a1 += bias[col0 + 2 * j + 1]; }
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(a0 * aff, a1 * aff);
+            o[j] = *reinterpret_cast<const uint32_t*>(&b2);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(p.y_pos + row * p.H_out + col0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ validation kernels (CUDA cores)
+__device__ __forceinline__ float e4m3_to_float(uint8_t c) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(c), __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+__device__ float mx_dot(const uint8_t* a, const uint8_t* a_sf, int64_t a_row, const uint8_t* b, const uint8_t* b_sf,
+                        int64_t b_row, int K) {
+  const int64_t k_atoms = (K + 127) >> 7;
+  float acc = 0.f;
+  for (int kb = 0; kb < K / 32; ++kb) {
+    float part = 0.f;
+    for (int j = 0; j < 32; ++j)
+      part += e4m3_to_float(a[a_row * K + kb * 32 + j]) * e4m3_to_float(b[b_row * K + kb * 32 + j]);
+    const int sa = a_sf[sf_atom_offset(a_row, kb, k_atoms)], sb = b_sf[sf_atom_offset(b_row, kb, k_atoms)];
+    acc += part * exp2f(static_cast<float>(sa - 127)) * exp2f(static_cast<float>(sb - 127));
+  }
+  return acc;
+}
+
+__global__ void simt_gemm1_kernel(const uint8_t* x, const uint8_t* w, GemmParams p, int K) {
+  // one thread per (position, 32-block of intermediates)
+  const int blocks_i = p.I / 32;
+  const int64_t total = static_cast<int64_t>(p.m_tiles_total) * 128 * blocks_i;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int ib = static_cast<int>(idx % blocks_i);
+    const int64_t row = idx / blocks_i;
+    const int m_tile = static_cast<int>(row >> 7);
+    const int block = m_tile / (p.B >> 7);
+    if (p.conditions && p.conditions[block] == 0) continue;
+    if (p.tile_flags && p.tile_flags[m_tile] == 0) continue;
+    const int e = p.block_to_expert[block];
+    if (e < 0 || e >= p.E) continue;
+    const uint8_t* we = w + static_cast<int64_t>(e) * p.n_total * K;
+    const uint8_t* wsf = p.b_sf + static_cast<int64_t>(e) * p.b_sf_expert_stride;
+    const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.n_total : nullptr;
+    float m[32];
+    uint32_t mx = 0;
+    for (int j = 0; j < 32; ++j) {
+      const int n_g = ib * 64 + j, n_u = n_g + 32;
+      float gv = mx_dot(x, p.a_sf, row, we, wsf, n_g, K);
+      float uv = mx_dot(x, p.a_sf, row, we, wsf, n_u, K);
+      if (bias) { gv += bias[n_g]; uv += bias[n_u]; }
+      if (p.gate_lo == p.gate_lo) gv = fmaxf(gv, p.gate_lo);
+      if (p.gate_hi == p.gate_hi) gv = fminf(gv, p.gate_hi);
+      if (p.up_lo == p.up_lo) uv = fmaxf(uv, p.up_lo);
+      if (p.up_hi == p.up_hi) uv = fminf(uv, p.up_hi);
+      m[j] = __bfloat162float(__float2bfloat16_rn(apply_act(gv, p.act) * uv));
+      mx = max(mx, __float_as_uint(m[j]) & 0x7fffffffu);
+    }
+    float f1, f2;
+    mx_block_factors(mx, f1, f2);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(p.m_codes + row * p.I + ib * 32);
+    for (int j = 0; j < 8; ++j)
+      dst[j] = pack4_e4m3(m[4 * j] * f1 * f2, m[4 * j + 1] * f1 * f2, m[4 * j + 2] * f1 * f2, m[4 * j + 3] * f1 * f2);
+    p.m_sf[sf_atom_offset(row, ib, (p.I + 127) >> 7)] = mx_block_scale_byte(mx);
+  }
+}
+
+__global__ void simt_gemm2_kernel(const uint8_t* m, const uint8_t* w, GemmParams p, int K) {
+  const int64_t total = static_cast<int64_t>(p.m_tiles_total) * 128 * p.H_out;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int h = static_cast<int>(idx % p.H_out);
+    const int64_t row = idx / p.H_out;
+    const int m_tile = static_cast<int>(row >> 7);
+    const int block = m_tile / (p.B >> 7);
+    if (p.conditions && p.conditions[block] == 0) continue;
+    if (p.tile_flags && p.tile_flags[m_tile] == 0) continue;
+    const int e = p.block_to_expert[block];
+    if (e < 0 || e >= p.E) continue;
+    const int tok = p.tpi ? p.tpi[row] : static_cast<int>(row);
+    if (tok < 0 || tok >= p.hidden_rows) continue;
+    float y = mx_dot(m, p.a_sf, row, w + static_cast<int64_t>(e) * p.n_total * K,
+                     p.b_sf + static_cast<int64_t>(e) * p.b_sf_expert_stride, h, K);
+    if (p.bias) y += p.bias[static_cast<int64_t>(e) * p.H_out + h];
+    if (p.aff) y *= load_as_float(p.aff, static_cast<int64_t>(tok) * p.E + e, p.aff_dtype);
+    p.y_pos[row * p.H_out + h] = __float2bfloat16_rn(y);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+int make_rows_map(CUtensorMap* map, const void* base, int64_t K, int64_t rows, int64_t batch, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  B200MOE_REQUIRE(enc != nullptr, B200MOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint32_t rank = batch > 0 ? 3 : 2;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch > 0 ? batch : 1)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(K) * static_cast<cuuint64_t>(rows)};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200MOE_REQUIRE(r == CUDA_SUCCESS, B200MOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+  return B200MOE_OK;
+}
+
+template <int BLOCK_N, int STAGES, int EPI>
+int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
+  using L = SmemLayout<BLOCK_N, STAGES>;
+  auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200MOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    attr_set = true;
+  }
+  const int total = p.m_tiles_total * p.n_tiles;
+  const int grid = total < sm_count() ? total : sm_count();
+  kern<<<grid, kThreads, L::kBytes, st>>>(ma, mb, p);
+  B200MOE_LAUNCH_OK("grouped_mxfp8_gemm_kernel");
+  return B200MOE_OK;
+}
+
+int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128 or 256)
+
+int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, int impl, cudaStream_t st) {
+  B200MOE_REQUIRE(p.B > 0 && p.B % 128 == 0, B200MOE_ERR_INVALID, "block size must be a multiple of 128, got %d", p.B);
+  B200MOE_REQUIRE(K % 32 == 0 && K >= 32, B200MOE_ERR_INVALID, "contraction length must be a multiple of 32, got %d", K);
+  B200MOE_REQUIRE(p.n_blocks > 0 && p.E > 0, B200MOE_ERR_INVALID, "need at least one block and one expert");
+  B200MOE_REQUIRE(p.status != nullptr, B200MOE_ERR_INVALID, "status pointer must not be null");
+  p.m_tiles_total = p.n_blocks * (p.B / 128);
+  p.k_blocks = (K + kBlockK - 1) / kBlockK;
+  p.b_row_atoms = (p.n_total + 127) / 128;
+  p.b_sf_expert_stride = static_cast<int64_t>(p.b_row_atoms) * p.k_blocks * 512;
+  B200MOE_CUDA_OK(cudaMemsetAsync(p.status, 0, 4, st));
+  if (impl == 1) {
+    const int64_t work = epi == 0 ? static_cast<int64_t>(p.m_tiles_total) * 128 * (p.I / 32)
+                                  : static_cast<int64_t>(p.m_tiles_total) * 128 * p.H_out;
+    const int grid = static_cast<int>(ceil_div64(work, 128) < 148 * 32 ? ceil_div64(work, 128) : 148 * 32);
+    if (epi == 0) simt_gemm1_kernel<<<grid, 128, 0, st>>>(a, b, p, K);
+    else simt_gemm2_kernel<<<grid, 128, 0, st>>>(a, b, p, K);
+    B200MOE_LAUNCH_OK("simt_gemm_kernel");
+    return B200MOE_OK;
+  }
+  B200MOE_REQUIRE(K % 16 == 0, B200MOE_ERR_INVALID, "TMA needs row pitches that are multiples of 16 bytes");
+  const int bn = g_block_n;
+  p.n_tiles = (p.n_total + bn - 1) / bn;
+  CUtensorMap ma, mb;
+  int rc = make_rows_map(&ma, a, K, static_cast<int64_t>(p.m_tiles_total) * 128, 0, kBlockM);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_rows_map(&mb, b, K, p.n_total, p.E, bn);
+  if (rc != B200MOE_OK) return rc;
+  if (bn == 256) return epi == 0 ? launch_tc<256, 4, 0>(ma, mb, p, st) : launch_tc<256, 4, 1>(ma, mb, p, st);
+  return epi == 0 ? launch_tc<128, 6, 0>(ma, mb, p, st) : launch_tc<128, 6, 1>(ma, mb, p, st);
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" int b200moe_set_gemm_tile_n(int block_n) {
+  B200MOE_REQUIRE(block_n == 128 || block_n == 256, B200MOE_ERR_INVALID, "tile width must be 128 or 256, got %d", block_n);
+  g_block_n = block_n;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_t* x_sf, const uint8_t* w1_dev,
+                                            const uint8_t* w1_sf, const float* bias_gu_dev,
+                                            const int32_t* block_to_expert, const int32_t* conditions,
+                                            const int32_t* tile_flags, int n_blocks, int B, int E, int H, int I,
+                                            int act_fn, float gate_lo, float gate_hi, float up_lo, float up_hi,
+                                            uint8_t* m_codes, uint8_t* m_sf, int32_t* status, int impl,
+                                            b200moe_stream_t stream) {
+  B200MOE_REQUIRE(x_codes && x_sf && w1_dev && w1_sf && block_to_expert && m_codes && m_sf, B200MOE_ERR_INVALID,
+                  "grouped_gemm1: null pointer argument");
+  B200MOE_REQUIRE(I % 32 == 0 && I > 0, B200MOE_ERR_INVALID, "grouped_gemm1: I must be a positive multiple of 32, got %d", I);
+  B200MOE_REQUIRE(act_fn >= 0 && act_fn <= 3, B200MOE_ERR_INVALID, "grouped_gemm1: unknown activation %d", act_fn);
+  GemmParams p{};
+  p.a_sf = x_sf;
+  p.b_sf = w1_sf;
+  p.block_to_expert = block_to_expert;
+  p.conditions = conditions;
+  p.tile_flags = tile_flags;
+  p.n_blocks = n_blocks;
+  p.B = B;
+  p.E = E;
+  p.n_total = 2 * I;
+  p.bias = bias_gu_dev;
+  p.act = act_fn;
+  p.gate_lo = gate_lo;
+  p.gate_hi = gate_hi;
+  p.up_lo = up_lo;
+  p.up_hi = up_hi;
+  p.m_codes = m_codes;
+  p.m_sf = m_sf;
+  p.I = I;
+  p.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (I % 128 != 0)  // partially filled scale atoms along I must read as zero
+    B200MOE_CUDA_OK(cudaMemsetAsync(m_sf, 0, b200moe_sf_bytes(static_cast<int64_t>(n_blocks) * B, I), st));
+  return run_gemm(0, x_codes, w1_dev, p, H, impl, st);
+}
+
+extern "C" int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
+                                           const uint8_t* w2_sf, const float* bias_d, const int32_t* block_to_expert,
+                                           const int32_t* conditions, const int32_t* tile_flags,
+                                           const int32_t* token_position_to_id, int hidden_rows, int n_blocks, int B,
+                                           int E, int H, int I, const void* affinities, int aff_dtype,
+                                           void* y_pos_bf16, int32_t* status, int impl, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(m_codes && m_sf && w2_dev && w2_sf && block_to_expert && y_pos_bf16, B200MOE_ERR_INVALID,
+                  "grouped_gemm2: null pointer argument");
+  B200MOE_REQUIRE(H % 32 == 0 && H > 0, B200MOE_ERR_INVALID, "grouped_gemm2: H must be a positive multiple of 32, got %d", H);
+  B200MOE_REQUIRE(aff_dtype == B200MOE_F32 || aff_dtype == B200MOE_BF16, B200MOE_ERR_INVALID,
+                  "grouped_gemm2: affinities must be fp32 or bf16");
+  GemmParams p{};
+  p.a_sf = m_sf;
+  p.b_sf = w2_sf;
+  p.block_to_expert = block_to_expert;
+  p.conditions = conditions;
+  p.tile_flags = tile_flags;
+  p.tpi = token_position_to_id;
+  p.hidden_rows = hidden_rows;
+  p.n_blocks = n_blocks;
+  p.B = B;
+  p.E = E;
+  p.n_total = H;
+  p.bias = bias_d;
+  p.aff = affinities;
+  p.aff_dtype = aff_dtype;
+  p.y_pos = static_cast<__nv_bfloat16*>(y_pos_bf16);
+  p.H_out = H;
+  p.I = I;
+  p.status = status;
+  return run_gemm(1, m_codes, w2_dev, p, I, impl, static_cast<cudaStream_t>(stream));
+}

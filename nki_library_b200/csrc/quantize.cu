@@ -1,0 +1,270 @@
+// MXFP8 activation quantisation fused with the token gather, and the one-time
+// relayout of expert weights into the tensor-core feed format.
+//
+// gather_quantize: one thread owns one 32-element block (64 bytes of bf16 in,
+// 32 code bytes + 1 scale byte out).  In packed-order mode the 32 elements of
+// block (t, g) are four 8-element runs at h = q*(H/4) + t*128 + 8g (q = 0..3),
+// interleaved as p*4 + q; otherwise they are 32 consecutive columns.
+#include "common.cuh"
+
+namespace b200moe {
+namespace {
+
+__device__ __forceinline__ void quantize_block32(const float (&v)[32], uint32_t (&codes)[8], uint8_t& scale) {
+  uint32_t mx = 0;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) mx = max(mx, __float_as_uint(v[i]) & 0x7fffffffu);
+  scale = mx_block_scale_byte(mx);
+  float f1, f2;
+  mx_block_factors(mx, f1, f2);
+#pragma unroll
+  for (int w = 0; w < 8; ++w)
+    codes[w] = pack4_e4m3(v[4 * w] * f1 * f2, v[4 * w + 1] * f1 * f2, v[4 * w + 2] * f1 * f2, v[4 * w + 3] * f1 * f2);
+}
+
+__device__ __forceinline__ void unpack8_bf16(const uint4& raw, float* out) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+__global__ void __launch_bounds__(256) gather_quantize_kernel(const __nv_bfloat16* __restrict__ hidden, int hidden_rows,
+                                                              int H, const int32_t* __restrict__ tpi, int64_t n_pos,
+                                                              int packed, uint8_t* __restrict__ codes,
+                                                              uint8_t* __restrict__ sf,
+                                                              int32_t* __restrict__ tile_flags) {
+  const int blocks_per_row = H >> 5;
+  const int64_t k_atoms = (H + 127) >> 7;
+  const int64_t total = n_pos * blocks_per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t p = i / blocks_per_row;
+    const int kb = static_cast<int>(i - p * blocks_per_row);
+    const int tok = tpi ? tpi[p] : static_cast<int>(p);
+    uint32_t c[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint8_t s = 0;
+    if (tok >= 0 && tok < hidden_rows) {
+      const __nv_bfloat16* row = hidden + static_cast<int64_t>(tok) * H;
+      float v[32];
+      if (!packed) {
+        const uint4* src = reinterpret_cast<const uint4*>(row + kb * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) unpack8_bf16(__ldg(src + j), v + 8 * j);
+      } else {
+        const int t = kb >> 4, g = kb & 15;
+        float tmp[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(row + q * (H >> 2) + t * 128 + g * 8)), tmp);
+#pragma unroll
+          for (int pp = 0; pp < 8; ++pp) v[pp * 4 + q] = tmp[pp];
+        }
+      }
+      quantize_block32(v, c, s);
+      if (tile_flags != nullptr && kb == 0) tile_flags[p >> 7] = 1;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(codes + p * H + kb * 32);
+    dst[0] = make_uint4(c[0], c[1], c[2], c[3]);
+    dst[1] = make_uint4(c[4], c[5], c[6], c[7]);
+    sf[sf_atom_offset(p, kb, k_atoms)] = s;
+  }
+}
+
+// ---- weight relayout ---------------------------------------------------------
+// Destination row of gate/up source row (s = 0 gate / 1 up, i): 32 gate rows then
+// the matching 32 up rows.
+__host__ __device__ inline int64_t gate_up_dev_row(int s, int i) { return (static_cast<int64_t>(i >> 5) << 6) + (s << 5) + (i & 31); }
+
+// Logical -> packed intermediate position maps of the reference storage
+// (tile of 512, or the whole axis when I < 512): packed j = tile*rows + p*4 + q
+// holds logical column tile*rows + q*(rows/4) + p.
+__device__ __forceinline__ int nki_logical_i(int j, int I) {
+  const int rows = I < 512 ? I : 512;
+  const int tile = j / rows, r = j - tile * rows;
+  return tile * rows + (r & 3) * (rows >> 2) + (r >> 2);
+}
+
+__global__ void prepare_gate_up_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ scale, int layout, int E,
+                                       int H, int I, uint8_t* __restrict__ w_dev, uint8_t* __restrict__ sf_dev) {
+  // one thread per (e, s, j, 32-block of H): copies 32 code bytes and 1 scale byte
+  const int kblocks = H >> 5;
+  const int64_t k_atoms = (H + 127) >> 7;
+  const int64_t sf_per_expert = ((2LL * I + 127) >> 7) * k_atoms * 512;
+  const int64_t total = static_cast<int64_t>(E) * 2 * I * kblocks;
+  const int nt = H >> 9;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int kb = static_cast<int>(idx % kblocks);
+    int64_t r = idx / kblocks;
+    const int j = static_cast<int>(r % I);
+    r /= I;
+    const int s = static_cast<int>(r & 1);
+    const int e = static_cast<int>(r >> 1);
+    uint32_t c[8];
+    uint8_t sc;
+    if (layout == B200MOE_LAYOUT_ROWS) {
+      const uint4* src = reinterpret_cast<const uint4*>(w + ((static_cast<int64_t>(e) * 2 + s) * I + j) * H + kb * 32);
+      const uint4 a = src[0], b = src[1];
+      c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+      sc = scale[((static_cast<int64_t>(e) * 2 + s) * I + j) * kblocks + kb];
+    } else {
+      // source word (e, p, s, t, i) holds q = 0..3; block kb = 16 t + g covers p in [8g, 8g+8)
+      const int i = nki_logical_i(j, I);
+      const int t = kb >> 4, g = kb & 15;
+      const uint32_t* w32 = reinterpret_cast<const uint32_t*>(w);
+#pragma unroll
+      for (int pp = 0; pp < 8; ++pp)
+        c[pp] = w32[(((static_cast<int64_t>(e) * 128 + (g * 8 + pp)) * 2 + s) * nt + t) * I + i];
+      sc = scale[(((static_cast<int64_t>(e) * 16 + g) * 2 + s) * nt + t) * I + i];
+    }
+    const int64_t row = gate_up_dev_row(s, j);
+    uint4* dst = reinterpret_cast<uint4*>(w_dev + (static_cast<int64_t>(e) * 2 * I + row) * H + kb * 32);
+    dst[0] = make_uint4(c[0], c[1], c[2], c[3]);
+    dst[1] = make_uint4(c[4], c[5], c[6], c[7]);
+    sf_dev[e * sf_per_expert + sf_atom_offset(row, kb, k_atoms)] = sc;
+  }
+}
+
+__global__ void prepare_down_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ scale, int layout, int E,
+                                    int H, int I, uint8_t* __restrict__ w_dev, uint8_t* __restrict__ sf_dev) {
+  // one thread per (e, h, 32-block of I)
+  const int kblocks = I >> 5;
+  const int64_t k_atoms = (I + 127) >> 7;
+  const int64_t sf_per_expert = ((static_cast<int64_t>(H) + 127) >> 7) * k_atoms * 512;
+  const int64_t total = static_cast<int64_t>(E) * H * kblocks;
+  const int pI = I > 512 ? 128 : I / 4;
+  const int n_tiles = I > 512 ? I / 512 : 1;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int kb = static_cast<int>(idx % kblocks);
+    int64_t r = idx / kblocks;
+    const int h = static_cast<int>(r % H);
+    const int e = static_cast<int>(r / H);
+    uint32_t c[8];
+    uint8_t sc;
+    if (layout == B200MOE_LAYOUT_ROWS) {
+      const uint4* src = reinterpret_cast<const uint4*>(w + (static_cast<int64_t>(e) * H + h) * I + kb * 32);
+      const uint4 a = src[0], b = src[1];
+      c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+      sc = scale[(static_cast<int64_t>(e) * H + h) * kblocks + kb];
+    } else {
+      // packed position j = tile*(pI*4) + p*4 + q; block kb covers p in [8g, 8g+8) of one tile
+      const int blocks_per_tile = pI >> 3;
+      const int tile = kb / blocks_per_tile, g = kb - tile * blocks_per_tile;
+      const uint32_t* w32 = reinterpret_cast<const uint32_t*>(w);
+#pragma unroll
+      for (int pp = 0; pp < 8; ++pp)
+        c[pp] = w32[((static_cast<int64_t>(e) * pI + (g * 8 + pp)) * n_tiles + tile) * H + h];
+      sc = scale[((static_cast<int64_t>(e) * (pI >> 3) + g) * n_tiles + tile) * H + h];
+    }
+    uint4* dst = reinterpret_cast<uint4*>(w_dev + (static_cast<int64_t>(e) * H + h) * I + kb * 32);
+    dst[0] = make_uint4(c[0], c[1], c[2], c[3]);
+    dst[1] = make_uint4(c[4], c[5], c[6], c[7]);
+    sf_dev[e * sf_per_expert + sf_atom_offset(h, kb, k_atoms)] = sc;
+  }
+}
+
+__global__ void prepare_bias_kernel(const void* bias, int dtype, int layout, int E, int I, float* out) {
+  const int64_t total = static_cast<int64_t>(E) * 2 * I;
+  const int pI = I > 512 ? 128 : I / 4;
+  const int n_tiles = I > 512 ? I / 512 : 1;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(idx % I);
+    const int s = static_cast<int>((idx / I) & 1);
+    const int e = static_cast<int>(idx / (2LL * I));
+    float v;
+    if (layout == B200MOE_LAYOUT_ROWS) {
+      v = load_as_float(bias, idx, dtype);
+    } else {
+      // [E, pI, 2, n_tiles, 4] is already in packed order: j = tile*(pI*4) + p*4 + q
+      const int tile = j / (pI * 4), r = j - tile * pI * 4;
+      v = load_as_float(bias, (((static_cast<int64_t>(e) * pI + (r >> 2)) * 2 + s) * n_tiles + tile) * 4 + (r & 3), dtype);
+    }
+    out[static_cast<int64_t>(e) * 2 * I + gate_up_dev_row(s, j)] = v;
+  }
+}
+
+inline int grid_for(int64_t n, int threads) {
+  const int64_t g = ceil_div64(n, threads);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  return static_cast<int>(g < cap ? (g > 0 ? g : 1) : cap);
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" size_t b200moe_sf_bytes(int64_t rows, int64_t K) {
+  return static_cast<size_t>(ceil_div64(rows, 128) * ceil_div64(K, 128) * 512);
+}
+
+extern "C" int b200moe_gather_quantize_mxfp8(const void* hidden_bf16, int hidden_rows, int H,
+                                             const int32_t* token_position_to_id, int64_t n_pos, int h_packed_order,
+                                             uint8_t* codes, uint8_t* sf_atoms, int32_t* tile_flags,
+                                             b200moe_stream_t stream) {
+  B200MOE_REQUIRE(hidden_bf16 && codes && sf_atoms, B200MOE_ERR_INVALID, "gather_quantize: null pointer argument");
+  B200MOE_REQUIRE(H > 0 && H % 32 == 0, B200MOE_ERR_INVALID, "gather_quantize: H must be a multiple of 32, got %d", H);
+  B200MOE_REQUIRE(!h_packed_order || H % 512 == 0, B200MOE_ERR_INVALID,
+                  "gather_quantize: packed hidden order needs H %% 512 == 0, got %d", H);
+  B200MOE_REQUIRE(n_pos > 0 && hidden_rows > 0, B200MOE_ERR_INVALID, "gather_quantize: empty input");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((n_pos % 128) != 0 || (H % 128) != 0)  // partially filled atoms must read as zero
+    B200MOE_CUDA_OK(cudaMemsetAsync(sf_atoms, 0, b200moe_sf_bytes(n_pos, H), st));
+  if (tile_flags != nullptr)
+    B200MOE_CUDA_OK(cudaMemsetAsync(tile_flags, 0, static_cast<size_t>(ceil_div64(n_pos, 128)) * 4, st));
+  gather_quantize_kernel<<<grid_for(n_pos * (H / 32), 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(hidden_bf16), hidden_rows, H, token_position_to_id, n_pos, h_packed_order,
+      codes, sf_atoms, tile_flags);
+  B200MOE_LAUNCH_OK("gather_quantize_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_prepare_gate_up(const void* w, const uint8_t* scale, int layout, int E, int H, int I,
+                                       uint8_t* w_dev, uint8_t* sf_dev, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(w && scale && w_dev && sf_dev, B200MOE_ERR_INVALID, "prepare_gate_up: null pointer argument");
+  B200MOE_REQUIRE(layout == B200MOE_LAYOUT_ROWS || layout == B200MOE_LAYOUT_NKI_X4, B200MOE_ERR_INVALID,
+                  "prepare_gate_up: unknown layout %d", layout);
+  B200MOE_REQUIRE(H % 32 == 0 && I % 32 == 0, B200MOE_ERR_INVALID, "prepare_gate_up: H and I must be multiples of 32");
+  if (layout == B200MOE_LAYOUT_NKI_X4)
+    B200MOE_REQUIRE(H % 512 == 0 && (I % 512 == 0 || I < 512), B200MOE_ERR_INVALID,
+                    "prepare_gate_up: reference storage needs H %% 512 == 0 and I %% 512 == 0 (or I < 512)");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200MOE_CUDA_OK(cudaMemsetAsync(sf_dev, 0, static_cast<size_t>(E) * b200moe_sf_bytes(2LL * I, H), st));
+  prepare_gate_up_kernel<<<grid_for(static_cast<int64_t>(E) * 2 * I * (H / 32), 256), 256, 0, st>>>(
+      static_cast<const uint8_t*>(w), scale, layout, E, H, I, w_dev, sf_dev);
+  B200MOE_LAUNCH_OK("prepare_gate_up_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_prepare_down(const void* w, const uint8_t* scale, int layout, int E, int H, int I,
+                                    uint8_t* w_dev, uint8_t* sf_dev, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(w && scale && w_dev && sf_dev, B200MOE_ERR_INVALID, "prepare_down: null pointer argument");
+  B200MOE_REQUIRE(layout == B200MOE_LAYOUT_ROWS || layout == B200MOE_LAYOUT_NKI_X4, B200MOE_ERR_INVALID,
+                  "prepare_down: unknown layout %d", layout);
+  B200MOE_REQUIRE(H % 32 == 0 && I % 32 == 0, B200MOE_ERR_INVALID, "prepare_down: H and I must be multiples of 32");
+  if (layout == B200MOE_LAYOUT_NKI_X4)
+    B200MOE_REQUIRE(I % 512 == 0 || I < 512, B200MOE_ERR_INVALID,
+                    "prepare_down: reference storage needs I %% 512 == 0 (or I < 512)");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200MOE_CUDA_OK(cudaMemsetAsync(sf_dev, 0, static_cast<size_t>(E) * b200moe_sf_bytes(H, I), st));
+  prepare_down_kernel<<<grid_for(static_cast<int64_t>(E) * H * (I / 32), 256), 256, 0, st>>>(
+      static_cast<const uint8_t*>(w), scale, layout, E, H, I, w_dev, sf_dev);
+  B200MOE_LAUNCH_OK("prepare_down_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_prepare_gate_up_bias(const void* bias, int dtype, int layout, int E, int I, float* bias_dev,
+                                            b200moe_stream_t stream) {
+  B200MOE_REQUIRE(bias && bias_dev, B200MOE_ERR_INVALID, "prepare_gate_up_bias: null pointer argument");
+  B200MOE_REQUIRE(dtype == B200MOE_F32 || dtype == B200MOE_BF16, B200MOE_ERR_INVALID,
+                  "prepare_gate_up_bias: bias must be fp32 or bf16");
+  prepare_bias_kernel<<<grid_for(static_cast<int64_t>(E) * 2 * I, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      bias, dtype, layout, E, I, bias_dev);
+  B200MOE_LAUNCH_OK("prepare_bias_kernel");
+  return B200MOE_OK;
+}

@@ -1,0 +1,124 @@
+"""One MoE layer = router_topk -> token grouping -> blockwise MXFP8 expert MLP -> combine.
+
+This is the call sequence the reference leaves to its caller for prefill
+(router and grouping sub-kernels, then ``moe_cte``) and fuses for decode in
+``moe_block_tkg`` (core/moe_block/moe_block_tkg.py:192-340, without the RMSNorm).
+All buffers are allocated once; a forward pass launches eight kernels on the
+current stream and never synchronises with the host.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib, pipeline
+from .core.moe.moe_cte.moe_cte_utils import get_n_blocks
+from .core.utils.common_types import ActFnType, RouterActFnType
+from .weights import ExpertWeights
+
+
+class MoELayer:
+    def __init__(self, router_w: torch.Tensor, weights: ExpertWeights, top_k: int, block_size: int,
+                 max_tokens: int, router_bias: Optional[torch.Tensor] = None,
+                 router_act: RouterActFnType = RouterActFnType.SOFTMAX, router_pre_norm: bool = True,
+                 norm_topk_prob: bool = True, act_fn: ActFnType = ActFnType.SiLU):
+        _lib.require_cuda(router_w, router_bias)
+        self.w = router_w.to(torch.bfloat16).contiguous()
+        self.bias = None if router_bias is None else router_bias.reshape(-1).to(torch.bfloat16).contiguous()
+        self.weights = weights
+        self.E, self.H, self.I = weights.E, weights.H, weights.I
+        _lib.kernel_assert(tuple(self.w.shape) == (self.H, self.E), "router weight must be [H, E]")
+        self.K, self.B, self.T = top_k, block_size, max_tokens
+        self.router_act, self.pre_norm, self.l1, self.act_fn = router_act, router_pre_norm, norm_topk_prob, act_fn
+        dev = self.w.device
+        T, E, K, B = max_tokens, self.E, top_k, block_size
+        self.N = get_n_blocks(T, K, E, B)
+        lib = _lib.load_library()
+        self.aff = torch.empty((T, E), dtype=torch.float32, device=dev)
+        self.idx = torch.empty((T, K), dtype=torch.int32, device=dev)
+        self.tpi = torch.empty(self.N * B, dtype=torch.int32, device=dev)
+        self.b2e = torch.empty(self.N, dtype=torch.int32, device=dev)
+        self.cond = torch.empty(self.N + 2, dtype=torch.int32, device=dev)
+        self.counts = torch.empty(E, dtype=torch.int32, device=dev)
+        self.inv = torch.empty((T, K), dtype=torch.int32, device=dev)
+        self.gstatus = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.gws = torch.empty(lib.b200moe_group_tokens_workspace_bytes(T, E), dtype=torch.uint8, device=dev)
+        self.ws = pipeline.BlockWorkspace(self.N * B, self.H, self.I, dev)
+        self.out = torch.empty((T, self.H), dtype=torch.bfloat16, device=dev)
+        self.kernels_per_forward = 8  # router, 3 grouping, quantise, 2 contractions, combine
+
+    def forward(self, hidden: torch.Tensor, timers: Optional[dict] = None) -> torch.Tensor:
+        """``hidden`` bf16 ``[T, H]`` on the device; returns the layer's bf16 ``[T, H]`` output buffer."""
+        T = hidden.shape[0]
+        _lib.kernel_assert(T == self.T and hidden.shape[1] == self.H and hidden.dtype == torch.bfloat16,
+                           "hidden must be bf16 [max_tokens, H]")
+        st = _lib.stream_ptr()
+        E, K, B, N, H, I = self.E, self.K, self.B, self.N, self.H, self.I
+        w, ws = self.weights, self.ws
+
+        def timed(name, fn):
+            if timers is None:
+                fn()
+                return
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            timers.setdefault(name, []).append((a, b))
+
+        timed("router_topk", lambda: _lib.call(
+            "b200moe_router_topk", _lib.ptr(hidden), 1, _lib.ptr(self.w), _lib.ptr(self.bias), T, H, E, K,
+            self.router_act.value, int(self.pre_norm), int(self.l1), None, _lib.F32, _lib.ptr(self.idx),
+            _lib.ptr(self.aff), _lib.F32, st))
+        timed("group_tokens", lambda: _lib.call(
+            "b200moe_group_tokens", _lib.ptr(self.idx), _lib.ROUTING_INDEX, _lib.I32, T, E, K, B, N, 1, 1,
+            _lib.ptr(self.tpi), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(self.counts), _lib.ptr(self.inv),
+            _lib.ptr(self.gstatus), _lib.ptr(self.gws), self.gws.numel(), st))
+        timed("gather_quantize", lambda: _lib.call(
+            "b200moe_gather_quantize_mxfp8", _lib.ptr(hidden), T, H, _lib.ptr(self.tpi), N * B,
+            int(w.h_packed_order), _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(ws.tile_flags), st))
+        nan = float("nan")
+        timed("gemm1_swiglu", lambda: _lib.call(
+            "b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(w.w1), _lib.ptr(w.w1_sf),
+            _lib.ptr(w.bias_gu), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(ws.tile_flags), N, B, E, H, I,
+            self.act_fn.value, nan, nan, nan, nan, _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(ws.status[1:]), 0, st))
+        timed("gemm2_scale", lambda: _lib.call(
+            "b200moe_grouped_gemm2_scale", _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(w.w2), _lib.ptr(w.w2_sf),
+            _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(ws.tile_flags), _lib.ptr(self.tpi),
+            T, N, B, E, H, I, _lib.ptr(self.aff), _lib.F32, _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), 0, st))
+        timed("combine", lambda: _lib.call(
+            "b200moe_combine", _lib.ptr(ws.y_pos), _lib.ptr(self.inv), T, K, H, _lib.ptr(self.out), st))
+        return self.out
+
+    def device_status(self) -> list:
+        """[grouping, gate/up contraction, down contraction] status words (0 = fine); synchronises."""
+        return [int(self.gstatus.item())] + self.ws.status.cpu().tolist()[1:3]
+
+
+def random_expert_weights(E: int, H: int, I: int, device, seed: int = 0, std: float = 0.02) -> ExpertWeights:
+    """Synthetic MXFP8 expert weights, generated and quantised on the device.
+
+    bf16 values ~ N(0, std) are pushed through the library's own MXFP8
+    quantiser (block-32 UE8M0 scales along the contraction axis), directly in
+    the feed layout; rows are i.i.d., so no relayout is needed.
+    """
+    lib = _lib.load_library()
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    w1 = torch.empty((E, 2 * I, H), dtype=torch.uint8, device=device)
+    w2 = torch.empty((E, H, I), dtype=torch.uint8, device=device)
+    sf1_e, sf2_e = lib.b200moe_sf_bytes(2 * I, H), lib.b200moe_sf_bytes(H, I)
+    w1_sf = torch.zeros(E * sf1_e, dtype=torch.uint8, device=device)
+    w2_sf = torch.zeros(E * sf2_e, dtype=torch.uint8, device=device)
+    st = _lib.stream_ptr()
+    for e in range(E):
+        a = (torch.randn((2 * I, H), device=device, generator=gen) * std).to(torch.bfloat16)
+        _lib.call("b200moe_gather_quantize_mxfp8", _lib.ptr(a), 2 * I, H, None, 2 * I, 0, _lib.ptr(w1[e]),
+                  _lib.ptr(w1_sf[e * sf1_e:]), None, st)
+        b = (torch.randn((H, I), device=device, generator=gen) * std).to(torch.bfloat16)
+        _lib.call("b200moe_gather_quantize_mxfp8", _lib.ptr(b), H, I, None, H, 0, _lib.ptr(w2[e]),
+                  _lib.ptr(w2_sf[e * sf2_e:]), None, st)
+        torch.cuda.synchronize()
+    return ExpertWeights(E, H, I, w1, w1_sf, w2, w2_sf, None, None, False)

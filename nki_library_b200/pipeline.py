@@ -1,0 +1,91 @@
+"""Launch sequence of the blockwise expert MLP on one GPU.
+
+gather + MXFP8 quantise -> grouped gate/up contraction (SwiGLU, re-quantise)
+-> grouped down contraction (bias, affinity) -> combine.  Everything runs on
+the current CUDA stream; no host synchronisation happens unless
+``check_status`` is requested.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .weights import ExpertWeights
+
+NAN = float("nan")
+
+
+def _clamp(v):
+    return NAN if v is None else float(v)
+
+
+class BlockWorkspace:
+    """Device scratch for one (n_pos, H, I) shape, reused across calls."""
+
+    def __init__(self, n_pos: int, H: int, I: int, device):
+        lib = _lib.load_library()
+        self.key = (n_pos, H, I, str(device))
+        self.xq = torch.empty((n_pos, H), dtype=torch.uint8, device=device)
+        self.x_sf = torch.zeros(lib.b200moe_sf_bytes(n_pos, H), dtype=torch.uint8, device=device)
+        self.tile_flags = torch.zeros(math.ceil(n_pos / 128), dtype=torch.int32, device=device)
+        self.mq = torch.empty((n_pos, I), dtype=torch.uint8, device=device)
+        self.m_sf = torch.zeros(lib.b200moe_sf_bytes(n_pos, I), dtype=torch.uint8, device=device)
+        self.y_pos = torch.empty((n_pos, H), dtype=torch.bfloat16, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+
+
+_workspaces: dict = {}
+
+
+def get_workspace(n_pos: int, H: int, I: int, device) -> BlockWorkspace:
+    key = (n_pos, H, I, str(device))
+    ws = _workspaces.get(key)
+    if ws is None:
+        if len(_workspaces) > 4:
+            _workspaces.clear()
+        ws = BlockWorkspace(n_pos, H, I, device)
+        _workspaces[key] = ws
+    return ws
+
+
+def run_blocks(hidden: torch.Tensor, hidden_rows: int, weights: ExpertWeights, token_position_to_id: torch.Tensor,
+               block_to_expert: torch.Tensor, conditions: Optional[torch.Tensor], block_size: int,
+               affinities: Optional[torch.Tensor], table: torch.Tensor, out: torch.Tensor, act_fn: int = 0,
+               gate_clamp=(None, None), up_clamp=(None, None), impl: int = 0, check_status: bool = False,
+               workspace: Optional[BlockWorkspace] = None) -> torch.Tensor:
+    """Run the four kernels.  ``table [rows_out, n_cand]`` lists, per output row, the positions to sum.
+
+    ``hidden`` bf16 ``[>= hidden_rows, H]``; ids outside ``[0, hidden_rows)`` in
+    ``token_position_to_id`` are pads.  ``affinities`` is the flat table addressed
+    ``token * E + expert`` (fp32 or bf16) or None.  ``out`` bf16 ``[rows_out, H]``.
+    """
+    E, H, I = weights.E, weights.H, weights.I
+    n_blocks = block_to_expert.numel()
+    n_pos = n_blocks * block_size
+    _lib.kernel_assert(block_size % 128 == 0, f"block_size ({block_size}) must be a multiple of 128")
+    _lib.kernel_assert(token_position_to_id.numel() == n_pos, "token_position_to_id must hold N * block_size ids")
+    _lib.kernel_assert(hidden.dtype == torch.bfloat16 and hidden.shape[1] == H and hidden.is_contiguous(),
+                       "hidden_states must be contiguous bf16 [rows, H]")
+    ws = workspace or get_workspace(n_pos, H, I, hidden.device)
+    st = _lib.stream_ptr()
+    _lib.call("b200moe_gather_quantize_mxfp8", _lib.ptr(hidden), hidden_rows, H, _lib.ptr(token_position_to_id), n_pos,
+              int(weights.h_packed_order), _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(ws.tile_flags), st)
+    _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(weights.w1),
+              _lib.ptr(weights.w1_sf), _lib.ptr(weights.bias_gu), _lib.ptr(block_to_expert), _lib.ptr(conditions),
+              _lib.ptr(ws.tile_flags), n_blocks, block_size, E, H, I, act_fn, _clamp(gate_clamp[0]),
+              _clamp(gate_clamp[1]), _clamp(up_clamp[0]), _clamp(up_clamp[1]), _lib.ptr(ws.mq), _lib.ptr(ws.m_sf),
+              _lib.ptr(ws.status[1:]), impl, st)
+    _lib.call("b200moe_grouped_gemm2_scale", _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(weights.w2),
+              _lib.ptr(weights.w2_sf), _lib.ptr(weights.bias_d), _lib.ptr(block_to_expert), _lib.ptr(conditions),
+              _lib.ptr(ws.tile_flags), _lib.ptr(token_position_to_id), hidden_rows, n_blocks, block_size, E, H, I,
+              _lib.ptr(affinities), _lib.F32 if affinities is None else _lib.dtype_code(affinities),
+              _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), impl, st)
+    _lib.call("b200moe_combine", _lib.ptr(ws.y_pos), _lib.ptr(table), out.shape[0], table.shape[1], H, _lib.ptr(out), st)
+    if check_status:
+        s = ws.status.cpu().tolist()
+        _lib.kernel_assert(s[1] == 0 and s[2] == 0, f"device-side wait expired in the expert contraction (status {s})")
+    return out

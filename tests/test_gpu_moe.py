@@ -1,0 +1,241 @@
+"""Grouped MXFP8 expert contractions, prefill (moe_cte) and decode (moe_tkg), against the CPU oracle.
+
+Output tolerance of this build: max|out - ref| / max|ref| <= 2e-2 on identical
+quantised inputs (the reference's own test bar for this path is 5e-2,
+test_moe_bwmm_mx_cte.py:287-288).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from moe_testlib import bf16_values, make_routing, make_rows_weights, max_rel, sf_atoms_to_rows
+from oracle import moe, mx, routing
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def _prep(m, w_np, bias_gu=None, bias_d=None):
+    t = [torch.from_numpy(a).cuda() for a in w_np]
+    return m.prepare_from_rows(*t, bias_gu=None if bias_gu is None else torch.from_numpy(bias_gu).cuda(),
+                               bias_d=None if bias_d is None else torch.from_numpy(bias_d).cuda())
+
+
+def _run_gemm1(m, weights, x_np, b2e_np, B, impl, act=0, clamps=(None,) * 4):
+    """Quantise rows x_np [n_pos, H] (identity gather) and run the gate/up contraction; returns m codes/scales."""
+    from nki_library_b200 import _lib, pipeline
+    n_pos, H = x_np.shape
+    ws = pipeline.BlockWorkspace(n_pos, H, weights.I, "cuda")
+    hidden = torch.from_numpy(x_np).to(torch.bfloat16).cuda()
+    b2e = torch.from_numpy(b2e_np.astype(np.int32)).cuda()
+    st = _lib.stream_ptr()
+    _lib.call("b200moe_gather_quantize_mxfp8", _lib.ptr(hidden), n_pos, H, None, n_pos, 0, _lib.ptr(ws.xq),
+              _lib.ptr(ws.x_sf), _lib.ptr(ws.tile_flags), st)
+    c = [pipeline._clamp(v) for v in clamps]
+    _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(weights.w1),
+              _lib.ptr(weights.w1_sf), _lib.ptr(weights.bias_gu), _lib.ptr(b2e), None, _lib.ptr(ws.tile_flags),
+              len(b2e_np), B, weights.E, H, weights.I, act, c[0], c[1], c[2], c[3], _lib.ptr(ws.mq), _lib.ptr(ws.m_sf),
+              _lib.ptr(ws.status[1:]), impl, st)
+    torch.cuda.synchronize()
+    assert ws.status.cpu().tolist()[1] == 0, "a device-side wait expired"
+    return ws.mq.cpu().numpy(), sf_atoms_to_rows(ws.m_sf.cpu().numpy(), n_pos, weights.I)
+
+
+@pytest.mark.parametrize("impl,tile_n", [(1, 256), (0, 256), (0, 128)])
+def test_gate_up_swiglu_requantise_vs_oracle(impl, tile_n):
+    import nki_library_b200 as m
+    from nki_library_b200 import _lib
+    _lib.call("b200moe_set_gemm_tile_n", tile_n)
+    try:
+        E, H, I, B = 3, 512, 384, 128
+        w_np = make_rows_weights(E, H, I, seed=1)
+        rng = np.random.default_rng(0)
+        bgu = rng.uniform(-1, 0.5, (E, 2, I)).astype(np.float32)
+        weights = _prep(m, w_np, bgu)
+        b2e = np.array([0, 2, 2, 1])
+        x = bf16_values(rng.standard_normal((len(b2e) * B, H)).astype(np.float32))
+        mq, ms = _run_gemm1(m, weights, x, b2e, B, impl, act=moe.SWISH, clamps=(-7.0, 7.0, -7.0, 7.0))
+        got = mx.dequantize_mx_rows(mq, ms)
+        for b, e in enumerate(b2e):
+            ew = moe.ExpertWeights(*w_np, e)
+            _, parts = moe.expert_mlp_rows(x[b * B:(b + 1) * B], ew, bgu[e], None, act=moe.SWISH,
+                                           gate_clamp=(-7, 7), up_clamp=(-7, 7), return_parts=True)
+            ref = mx.dequantize_mx_rows(parts["mq"], parts["ms"])
+            sl = slice(b * B, (b + 1) * B)
+            assert max_rel(got[sl], ref) <= TOL
+            # identical quantised inputs and fp32 accumulation: nearly every code and scale is identical
+            assert (ms[sl] == parts["ms"]).mean() > 0.99
+            assert (mq[sl] == parts["mq"]).mean() > 0.97
+    finally:
+        _lib.call("b200moe_set_gemm_tile_n", 256)
+
+
+def _cte_case(T, H, I, E, K, B, seed, bias, act, clamp, zipf=None):
+    hidden, _, _, idx, aff = make_routing(T, H, E, K, seed, zipf)
+    w_np = make_rows_weights(E, H, I, seed)
+    rng = np.random.default_rng(seed + 7)
+    bgu = rng.uniform(-2.0625, 0.52, (E, 2, I)).astype(np.float32) if bias else None
+    bd = rng.uniform(-1.632, 1.4375, (E, H)).astype(np.float32) if bias else None
+    return hidden, idx, aff, w_np, bgu, bd
+
+
+def _oracle_cte(hidden, aff, w_np, tpi, b2e, cond, B, bgu, bd, act, clamp, h_order=None):
+    g = (-clamp, clamp) if clamp else (None, None)
+    out = moe.moe_cte_rows(hidden, aff, *w_np, tpi, b2e, B, cond, bgu, bd, act, g, g, h_order=h_order)
+    return bf16_values(out)
+
+
+@pytest.mark.parametrize("impl", [1, 0])
+@pytest.mark.parametrize("variant", ["plain", "bias_clamp_swish"])
+def test_moe_cte_c1_rows_weights(impl, variant):
+    """BASELINE config 1: T=256, H=512, I=1024, E=4, top-2, B=128."""
+    import nki_library_b200 as m
+    T, H, I, E, K, B = 256, 512, 1024, 4, 2, 128
+    bias = variant != "plain"
+    act = moe.SWISH if bias else moe.SILU
+    clamp = 7.0 if bias else None
+    hidden, idx, aff, w_np, bgu, bd = _cte_case(T, H, I, E, K, B, 11, bias, act, clamp)
+    weights = _prep(m, w_np, bgu, bd)
+    N = m.get_n_blocks(T, K, E, B, 2)
+    g = m.moe_group_tokens(torch.from_numpy(idx).cuda(), E, B, N, check=True)
+    out = m.moe_cte(torch.from_numpy(hidden).to(torch.bfloat16).cuda(),
+                    torch.from_numpy(aff).to(torch.bfloat16).cuda().reshape(-1, 1), weights, None,
+                    g["token_position_to_id"], g["block_to_expert"], B,
+                    m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx), conditions=g["conditions"],
+                    activation_function=m.ActFnType(act), skip_dma=m.SkipMode(True, False),
+                    gate_clamp_upper_limit=clamp, gate_clamp_lower_limit=None if clamp is None else -clamp,
+                    up_clamp_upper_limit=clamp, up_clamp_lower_limit=None if clamp is None else -clamp,
+                    _impl=impl, _check_status=True)
+    ref = _oracle_cte(hidden, bf16_values(aff), w_np, g["token_position_to_id"].cpu().numpy(),
+                      g["block_to_expert"].cpu().numpy(), g["conditions"].cpu().numpy(), B, bgu, bd, act, clamp)
+    assert out.shape == (T, H) and out.dtype == torch.bfloat16
+    assert max_rel(out.float().cpu().numpy(), ref) <= TOL
+
+
+@pytest.mark.parametrize("skip_token", [True, False])
+def test_moe_cte_reference_storage_layout(skip_token):
+    """Weights in the reference's x4-packed storage, hidden in its logical order, pad id -1 or T."""
+    import nki_library_b200 as m
+    T, H, I, E, K, B = 200, 1024, 512, 4, 2, 128
+    hidden, idx, aff, w_np, bgu, bd = _cte_case(T, H, I, E, K, B, 21, True, moe.SILU, None)
+    gw, gs = mx.rows_to_ref_gate_up(w_np[0], w_np[1])
+    dw, ds = mx.rows_to_ref_down(w_np[2], w_np[3])
+    pI = 128 if I > 512 else I // 4
+    bref = np.ascontiguousarray(bgu.reshape(E, 2, I // (pI * 4), pI, 4).transpose(0, 3, 1, 2, 4))
+    N = m.get_n_blocks(T, K, E, B, 2)
+    g = m.moe_group_tokens(torch.from_numpy(idx).cuda(), E, B, N, skip_token=skip_token, check=True)
+    hid_t = torch.from_numpy(hidden).to(torch.bfloat16)
+    aff_t = torch.from_numpy(aff).to(torch.bfloat16)
+    if not skip_token:
+        hid_t = torch.cat([hid_t, torch.zeros(1, H, dtype=torch.bfloat16)])
+        aff_t = torch.cat([aff_t, torch.zeros(1, E, dtype=torch.bfloat16)])
+    out = m.moe_cte(hid_t.cuda(), aff_t.cuda().reshape(-1, 1), torch.from_numpy(gw.view(np.int32)).cuda(),
+                    torch.from_numpy(dw.view(np.int32)).cuda(), g["token_position_to_id"], g["block_to_expert"], B,
+                    m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx), conditions=g["conditions"],
+                    gate_and_up_proj_bias=torch.from_numpy(bref).cuda(), down_proj_bias=torch.from_numpy(bd).cuda(),
+                    quantization_config=m.QuantizationConfig(torch.from_numpy(gs).cuda(), torch.from_numpy(ds).cuda()),
+                    skip_dma=m.SkipMode(skip_token, False), compat_lnc_slabs=True, _check_status=True)
+    assert out.shape == (2, T + (0 if skip_token else 1), H) and not out[1].any()
+    tpi = g["token_position_to_id"].cpu().numpy()
+    ref = _oracle_cte(hidden, bf16_values(aff), w_np, tpi, g["block_to_expert"].cpu().numpy(),
+                      g["conditions"].cpu().numpy(), B, bgu, bd, moe.SILU, None, h_order=mx.hidden_packed_order(H))
+    assert max_rel(out[0, :T].float().cpu().numpy(), ref) <= TOL
+
+
+def test_moe_cte_conditions_stop_and_skew():
+    """Zipf-skewed routing with many partial blocks; blocks past the first zero condition contribute nothing."""
+    import nki_library_b200 as m
+    T, H, I, E, K, B = 512, 512, 256, 16, 4, 128
+    hidden, idx, aff, w_np, _, _ = _cte_case(T, H, I, E, K, B, 31, False, moe.SILU, None, zipf=1.2)
+    weights = _prep(m, w_np)
+    N = m.get_n_blocks(T, K, E, B)
+    g = m.moe_group_tokens(torch.from_numpy(idx).cuda(), E, B, N, check=True)
+    cond = g["conditions"].clone()
+    n_active = int(cond.sum().item())
+    cond[n_active - 2:] = 0  # cut the last two occupied blocks as well
+    out = m.moe_cte(torch.from_numpy(hidden).to(torch.bfloat16).cuda(), torch.from_numpy(aff).cuda().reshape(-1, 1),
+                    weights, None, g["token_position_to_id"], g["block_to_expert"], B,
+                    m.MoECTESpec(m.MoECTEImplementation.shard_on_i_mx), conditions=cond,
+                    skip_dma=m.SkipMode(True, False), _check_status=True)
+    ref = _oracle_cte(hidden, aff, w_np, g["token_position_to_id"].cpu().numpy(), g["block_to_expert"].cpu().numpy(),
+                      cond.cpu().numpy(), B, None, None, moe.SILU, None)
+    assert max_rel(out.float().cpu().numpy(), ref) <= TOL
+    out2 = m.moe_cte(torch.from_numpy(hidden).to(torch.bfloat16).cuda(), torch.from_numpy(aff).cuda().reshape(-1, 1),
+                     weights, None, g["token_position_to_id"], g["block_to_expert"], B,
+                     m.MoECTESpec(m.MoECTEImplementation.shard_on_i_mx), conditions=cond,
+                     skip_dma=m.SkipMode(True, False))
+    assert torch.equal(out, out2)  # deterministic: same bytes on a second run
+
+
+@pytest.mark.parametrize("mode", ["selective", "all_expert"])
+def test_moe_tkg_vs_oracle(mode):
+    """Decode: T=64 tokens, top-2 of 8 experts (BASELINE config 3 with H, I scaled down)."""
+    import nki_library_b200 as m
+    T, H, I, E, K = 64, 1024, 768, 8, 2
+    hidden, idx, aff, w_np, bgu, bd = _cte_case(T, H, I, E, K, 128, 41, True, moe.SILU, None)
+    weights = _prep(m, w_np, bgu, bd)
+    hid = torch.from_numpy(hidden).to(torch.bfloat16).cuda()
+    aff_t = torch.from_numpy(aff).cuda()
+    idx_t = torch.from_numpy(idx).cuda()
+    if mode == "selective":
+        out = m.moe_tkg(hid, weights, None, aff_t, idx_t, False,
+                        expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.POST_SCALE, _check_status=True)
+        ref = moe.moe_tkg_rows(hidden, aff, idx, *w_np, bias_gu=bgu, bias_d=bd)
+    else:
+        out = m.moe_tkg(hid, weights, None, aff_t, idx_t, True, rank_id=torch.zeros((1, 1), dtype=torch.int32, device="cuda"),
+                        mask_unselected_experts=True,
+                        expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.POST_SCALE, _check_status=True)
+        ref = moe.moe_tkg_rows(hidden, aff * routing.mask_from_index(idx, E), None, *w_np, bias_gu=bgu, bias_d=bd,
+                               is_all_expert=True)
+    assert out.shape == (T, H)
+    assert max_rel(out.float().cpu().numpy(), bf16_values(ref)) <= TOL
+    with pytest.raises(AssertionError):
+        m.moe_tkg(hid, weights, None, aff_t, idx_t, False,
+                  expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.PRE_SCALE)
+
+
+def test_moe_cte_properties_at_mixtral_block_shape():
+    """Size-independent checks at BASELINE config 2's block geometry (B=512, H=4096, K=2, E=8; I cut to 2048)."""
+    import nki_library_b200 as m
+    from nki_library_b200 import _lib, pipeline
+    T, H, I, E, K, B = 2048, 4096, 2048, 8, 2, 512
+    hidden, idx, aff, _, _, _ = _cte_case(T, 64, 32, E, K, B, 51, False, 0, None)  # routing only
+    rng = np.random.default_rng(5)
+    hid = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).to(torch.bfloat16).cuda()
+    # weights quantised on the device with the library's own quantiser (N(0, 0.02), feed layout)
+    lib = _lib.load_library()
+    def qw(rows, K_):
+        w = (torch.randn((rows, K_), device="cuda", generator=torch.Generator("cuda").manual_seed(rows)) * 0.02).to(torch.bfloat16)
+        codes = torch.empty((rows, K_), dtype=torch.uint8, device="cuda")
+        sf = torch.zeros(lib.b200moe_sf_bytes(rows, K_), dtype=torch.uint8, device="cuda")
+        _lib.call("b200moe_gather_quantize_mxfp8", _lib.ptr(w), rows, K_, None, rows, 0, _lib.ptr(codes), _lib.ptr(sf), None,
+                  _lib.stream_ptr())
+        return codes, sf
+    w1, w1_sf = qw(E * 2 * I, H)
+    w2, w2_sf = qw(E * H, I)
+    weights = m.ExpertWeights(E, H, I, w1.view(E, 2 * I, H), w1_sf, w2.view(E, H, I), w2_sf, None, None, False)
+    N = m.get_n_blocks(T, K, E, B)
+    g = m.moe_group_tokens(torch.from_numpy(idx).cuda(), E, B, N, check=True)
+    spec = m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx)
+    run = lambda h, a: m.moe_cte(h, a.reshape(-1, 1), weights, None, g["token_position_to_id"], g["block_to_expert"], B,
+                                 spec, conditions=g["conditions"], skip_dma=m.SkipMode(True, False), _check_status=True)
+    aff_t = torch.from_numpy(aff).cuda()
+    out = run(hid, aff_t)
+    assert torch.isfinite(out.float()).all() and out.float().abs().max() > 0
+    assert torch.equal(out, run(hid, aff_t))                                   # run-to-run determinism
+    assert torch.equal(run(hid, aff_t * 2).float(), out.float() * 2)           # exact linearity in the affinity (x2)
+    assert not run(hid, torch.zeros_like(aff_t)).any()                         # zero affinity -> zero output
+    # a sample of tokens against the oracle, weights dequantised from the device buffers
+    w1_np = w1.view(E, 2 * I, H).cpu().numpy()
+    w2_np = w2.view(E, H, I).cpu().numpy()
+    s1 = sf_atoms_to_rows(w1_sf.cpu().numpy(), E * 2 * I, H).reshape(E, 2 * I, H // 32)
+    s2 = sf_atoms_to_rows(w2_sf.cpu().numpy(), E * H, I).reshape(E, H, I // 32)
+    from moe_testlib import gate_up_dev_rows
+    rows = gate_up_dev_rows(I)
+    c1 = np.stack([w1_np[:, rows[0]], w1_np[:, rows[1]]], axis=1)
+    sc1 = np.stack([s1[:, rows[0]], s1[:, rows[1]]], axis=1)
+    sample = rng.choice(T, size=24, replace=False)
+    hid_np = hid.float().cpu().numpy()
+    ref = moe.moe_tkg_rows(hid_np[sample], aff[sample], idx[sample], c1, sc1, w2_np, s2)
+    assert max_rel(out[sample].float().cpu().numpy(), bf16_values(ref)) <= TOL
