@@ -198,6 +198,9 @@ def run_ours(args, cfg, name):
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
     T, H, I, E, K, B = (cfg[k] for k in "THIEKB")
+    if args.tile_n:
+        from nki_library_b200 import _lib
+        _lib.call("b200moe_set_gemm_tile_n", args.tile_n)
 
     # Experts are independent given the routing, so N GPUs run as N replicas of the
     # single-GPU layer on their own token batches (weak scaling, no data-path collective).
@@ -276,7 +279,8 @@ def run_ours(args, cfg, name):
                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                         "peak_source": f"{peaks['source']} copy bandwidth",
                         "layer_gbs": work["decode_bytes"] / (ms_step * 1e-3) / 1e9}
-        cpu = cpu_sample(cfg, 2, 1, os.cpu_count() or 1)
+        cpu = (dict(value=None, sample="skipped (--skip-cpu)") if args.skip_cpu
+               else cpu_sample(cfg, 2, 1, os.cpu_count() or 1))
         line = {
             "metric": "moe_layer_tokens_per_s", "value": world * T / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
@@ -306,6 +310,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mixtral_prefill", choices=sorted(WORKLOADS))
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    ap.add_argument("--tile-n", type=int, default=0, help="weight rows per GEMM tile (128/192/256; 0 = library default)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":

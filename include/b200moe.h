@@ -66,10 +66,13 @@ size_t b200moe_sf_bytes(int64_t rows, int64_t K);
  * (router_topk.py:515-547).  x is bf16 [T,H] (x_is_TH=1) or [H,T]; w bf16 [H,E];
  * w_bias bf16 [E] or NULL.  Outputs (each may be NULL to skip): router_logits
  * [T,E], expert_index uint32 [T,k], expert_affinities [T,E] (dense, zeros outside
- * the top-k when scattered).  E <= 512, k <= 8. */
+ * the top-k when scattered).  E <= 512, k <= 8.  workspace holds the split-K partial
+ * logits (b200moe_router_workspace_bytes). */
+size_t b200moe_router_workspace_bytes(int T, int H, int E);
 int b200moe_router_topk(const void* x, int x_is_TH, const void* w, const void* w_bias, int T, int H, int E, int k,
                         int act_fn, int router_pre_norm, int norm_topk_prob, void* router_logits, int logits_dtype,
-                        uint32_t* expert_index, void* expert_affinities, int aff_dtype, b200moe_stream_t stream);
+                        uint32_t* expert_index, void* expert_affinities, int aff_dtype, void* workspace,
+                        size_t workspace_bytes, b200moe_stream_t stream);
 
 /* ---- grouping ----------------------------------------------------------------
  * find_nonzero_indices (core/subkernels/find_nonzero_indices.py:34-40): per column
@@ -142,7 +145,8 @@ int b200moe_prepare_gate_up_bias(const void* bias, int dtype, int layout, int E,
 
 /* ---- grouped expert contractions -----------------------------------------------
  * Parameters common to both: block_to_expert [n_blocks]; conditions (NULL = all
- * blocks run; otherwise a block runs iff conditions[b] != 0); tile_flags (NULL = all
+ * blocks run; otherwise blocks run up to the first b with conditions[b] == 0, as in the
+ * reference's block loop); tile_flags (NULL = all
  * tiles run; see b200moe_gather_quantize_mxfp8); token_position_to_id [n_blocks*B] and
  * hidden_rows (ids outside [0, hidden_rows) are pads, their rows are not written); status: device
  * int32[1], set non-zero if a kernel-internal wait ran out; impl: 0 = tcgen05
@@ -173,7 +177,7 @@ int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, con
                                 int n_blocks, int B, int E, int H, int I, const void* affinities, int aff_dtype,
                                 void* y_pos_bf16, int32_t* status, int impl, b200moe_stream_t stream);
 
-/* Weight rows per tile of the tensor-core kernel: 256 (default) or 128.  Tuning knob
+/* Weight rows per tile of the tensor-core kernel: 256 (default), 192 or 128.  Tuning knob
  * with no counterpart in the reference. */
 int b200moe_set_gemm_tile_n(int block_n);
 

@@ -28,8 +28,9 @@ SIGNATURES = {
     "b200moe_last_error": (c_char_p, []),
     "b200moe_version": (c_int, []),
     "b200moe_sf_bytes": (c_size_t, [c_int64, c_int64]),
+    "b200moe_router_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "b200moe_router_topk": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                    c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+                                    c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "b200moe_find_nonzero_workspace_bytes": (c_size_t, [c_int, c_int]),
     "b200moe_find_nonzero_indices": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                              c_void_p, c_size_t, c_void_p]),

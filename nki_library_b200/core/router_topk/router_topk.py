@@ -68,11 +68,12 @@ def router_topk(
         _lib.kernel_assert(out is not None and tuple(out.shape) == shape and out.is_contiguous(),
                            f"output tensor must be contiguous with shape {shape}")
     _lib.kernel_assert(expert_index.dtype in (torch.int32, torch.uint32), "expert_index must be a 32-bit integer tensor")
+    ws = torch.empty(_lib.load_library().b200moe_router_workspace_bytes(T, H, E), dtype=torch.uint8, device=x.device)
     _lib.call(
         "b200moe_router_topk", _lib.ptr(x), x_is_TH, _lib.ptr(w), _lib.ptr(w_bias), T, H, E, k, act_fn.value,
         int(router_pre_norm), int(norm_topk_prob), _lib.ptr(router_logits), _lib.dtype_code(router_logits),
         None if skip_store_expert_index else _lib.ptr(expert_index), _lib.ptr(expert_affinities),
-        _lib.dtype_code(expert_affinities), _lib.stream_ptr())
+        _lib.dtype_code(expert_affinities), _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
     outs = [router_logits, expert_index, expert_affinities]
     if return_eager_affi:
         idx = expert_index.to(torch.int64)

@@ -12,10 +12,13 @@
 //                      thread), codes + scale atoms out
 //               EPI 1: + bias, x routing affinity, bf16 rows out
 // Tiles are (128 positions) x (BLOCK_N weight rows); a tile's expert comes from
-// block_to_expert, padded / inactive tiles are skipped.  The tile order walks
-// 16 consecutive position tiles per weight tile so CTAs running side by side
-// share a weight tile in L2.  Every mbarrier wait is bounded: on expiry the
-// kernel records a code in `status`, stops issuing work and tears down.
+// block_to_expert, padded / inactive tiles are skipped.  Tiles are enumerated
+// expert by expert, weight tile by weight tile, position tile fastest, so the
+// CTAs that run side by side read the same weight tile from L2 (a per-CTA
+// prologue derives each expert's position-tile range from block_to_expert).
+// Blocks run up to the first zero in `conditions`.  Every mbarrier wait is
+// bounded: on expiry the kernel records a code in `status`, stops issuing work
+// and tears down.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -26,6 +29,7 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 128;  // bytes (= e4m3 elements) per pipeline slab
 constexpr int kGroupM = 16;
+constexpr int kMaxExperts = 512;
 constexpr int kThreads = 192;
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
@@ -175,19 +179,78 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
-__device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, int& m_tile, int& n_tile, int& expert) {
-  const int per_group = kGroupM * p.n_tiles;
-  const int g = tile / per_group;
-  const int first_m = g * kGroupM;
-  const int gs = min(kGroupM, p.m_tiles_total - first_m);
-  const int within = tile - g * per_group;
-  m_tile = first_m + within % gs;
-  n_tile = within / gs;
-  const int block = m_tile / (p.B >> 7);
-  if (p.conditions != nullptr && p.conditions[block] == 0) return false;
+// Per-CTA tile schedule, built once in shared memory.
+struct Sched {
+  int tile_start[kMaxExperts + 1];  // tiles before expert e (expert-aligned order)
+  int mt_first[kMaxExperts];        // first 128-position tile of expert e
+  int mt_count[kMaxExperts];        // its number of position tiles among the active blocks
+  int runs[kMaxExperts];            // how many separate block runs expert e has (1 when sorted)
+  int n_active;                     // blocks before the first zero condition
+  int contiguous;                   // every expert's blocks are adjacent
+  int total;                        // number of tiles to walk
+};
+
+__device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s) {
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int sub = p.B >> 7;
+  if (tid == 0) { s.n_active = p.n_blocks; s.contiguous = 1; }
+  for (int e = tid; e < p.E; e += nthr) { s.mt_first[e] = 0; s.mt_count[e] = 0; s.runs[e] = 0; }
+  __syncthreads();
+  if (p.conditions != nullptr)
+    for (int b = tid; b < p.n_blocks; b += nthr)
+      if (p.conditions[b] == 0) atomicMin(&s.n_active, b);
+  __syncthreads();
+  const int n_active = s.n_active;
+  for (int b = tid; b < n_active; b += nthr) {
+    const int e = p.block_to_expert[b];
+    if (e < 0 || e >= p.E) continue;
+    if (b == 0 || p.block_to_expert[b - 1] != e) {
+      s.mt_first[e] = b * sub;
+      if (atomicAdd(&s.runs[e], 1) > 0) s.contiguous = 0;
+    }
+    atomicAdd(&s.mt_count[e], sub);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < p.E; ++e) {
+      s.tile_start[e] = run;
+      run += s.mt_count[e] * p.n_tiles;
+    }
+    s.tile_start[p.E] = run;
+    s.total = s.contiguous ? run : p.m_tiles_total * p.n_tiles;
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s, int tile, int& m_tile, int& n_tile,
+                                            int& expert) {
+  if (s.contiguous) {
+    int lo = 0, hi = p.E;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s.tile_start[mid] <= tile) lo = mid; else hi = mid;
+    }
+    expert = lo;
+    const int local = tile - s.tile_start[lo];
+    const int cnt = s.mt_count[lo];
+    m_tile = s.mt_first[lo] + local % cnt;
+    n_tile = local / cnt;
+  } else {
+    const int per_group = kGroupM * p.n_tiles;
+    const int g = tile / per_group;
+    const int first_m = g * kGroupM;
+    const int gs = min(kGroupM, p.m_tiles_total - first_m);
+    const int within = tile - g * per_group;
+    m_tile = first_m + within % gs;
+    n_tile = within / gs;
+    const int block = m_tile / (p.B >> 7);
+    if (block >= s.n_active) return false;
+    expert = p.block_to_expert[block];
+    if (expert < 0 || expert >= p.E) return false;
+  }
   if (p.tile_flags != nullptr && p.tile_flags[m_tile] == 0) return false;
-  expert = p.block_to_expert[block];
-  return expert >= 0 && expert < p.E;
+  return true;
 }
 
 template <int BLOCK_N, int STAGES>
@@ -195,13 +258,15 @@ struct SmemLayout {
   static constexpr int kA = kBlockM * kBlockK;
   static constexpr int kB = BLOCK_N * kBlockK;
   static constexpr int kSfa = 512;
-  static constexpr int kSfb = (BLOCK_N / 128) * 512;
+  static constexpr int kSfbAtoms = BLOCK_N > 128 ? 2 : 1;
+  static constexpr int kSfb = kSfbAtoms * 512;
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kOffA + STAGES * kA;
   static constexpr int kOffSfa = kOffB + STAGES * kB;
   static constexpr int kOffSfb = kOffSfa + STAGES * kSfa;
   static constexpr int kOffBar = kOffSfb + STAGES * kSfb;
-  static constexpr int kBytes = kOffBar + 512 + 1024;  // barriers + alignment slack
+  static constexpr int kOffSched = kOffBar + 256;
+  static constexpr int kBytes = kOffSched + static_cast<int>(sizeof(Sched)) + 1024;  // + alignment slack
 };
 
 template <int BLOCK_N, int STAGES, int EPI>
@@ -209,7 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const GemmParams p) {
   using L = SmemLayout<BLOCK_N, STAGES>;
-  constexpr int kAcc = (BLOCK_N <= 128) ? 2 : 1;
+  constexpr int kAcc = (BLOCK_N <= 192) ? 2 : 1;
   constexpr int kSfCol = kAcc * BLOCK_N;  // TMEM columns: accumulators, then SFA (4), then SFB
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kIdesc = make_idesc(kBlockM, BLOCK_N);
@@ -223,9 +288,11 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   uint64_t* tmem_empty = bars + 2 * STAGES + kAcc;
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * kAcc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+  Sched& sched = *reinterpret_cast<Sched*>(smem + L::kOffSched);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = p.m_tiles_total * p.n_tiles;
+  build_sched(p, sched);
+  const int total_tiles = sched.total;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -259,25 +326,23 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int m_tile, n_tile, e;
-        if (!decode_tile(p, tile, m_tile, n_tile, e)) continue;
+        if (!decode_tile(p, sched, tile, m_tile, n_tile, e)) continue;
         const uint8_t* sfa = p.a_sf + static_cast<int64_t>(m_tile) * p.k_blocks * 512;
         const uint8_t* sfb = p.b_sf + static_cast<int64_t>(e) * p.b_sf_expert_stride;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
-          uint32_t bytes = L::kA + L::kB + L::kSfa;
+          const int atom0 = (n_tile * BLOCK_N) >> 7;
           int n_sfb = 0;
 #pragma unroll
-          for (int j = 0; j < BLOCK_N / 128; ++j)
-            if (n_tile * (BLOCK_N / 128) + j < p.b_row_atoms) ++n_sfb;
-          bytes += n_sfb * 512;
-          mbar_expect_tx(&full[stage], bytes);
+          for (int j = 0; j < L::kSfbAtoms; ++j)
+            if (atom0 + j < p.b_row_atoms) ++n_sfb;
+          mbar_expect_tx(&full[stage], L::kA + L::kB + L::kSfa + n_sfb * 512);
           tma_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
           tma_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK, n_tile * BLOCK_N, e, &full[stage]);
           bulk_load(smem + L::kOffSfa + stage * L::kSfa, sfa + static_cast<int64_t>(kb) * 512, 512, &full[stage]);
           for (int j = 0; j < n_sfb; ++j)
             bulk_load(smem + L::kOffSfb + stage * L::kSfb + j * 512,
-                      sfb + (static_cast<int64_t>(n_tile * (BLOCK_N / 128) + j) * p.k_blocks + kb) * 512, 512,
-                      &full[stage]);
+                      sfb + (static_cast<int64_t>(atom0 + j) * p.k_blocks + kb) * 512, 512, &full[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -294,19 +359,20 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int m_tile, n_tile, e;
-        if (!decode_tile(p, tile, m_tile, n_tile, e)) continue;
+        if (!decode_tile(p, sched, tile, m_tile, n_tile, e)) continue;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
         const uint32_t sfa_tmem = tmem_base + kSfCol;
-        const uint32_t sfb_tmem = tmem_base + kSfCol + 4;
+        const uint32_t sfb_base = tmem_base + kSfCol + 4;
+        const uint32_t sfb_tmem = sfb_base + (((n_tile * BLOCK_N) & 127) >> 5);  // tile may start mid-atom
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
           tc_fence_after();
           tc_cp_sf(sfa_tmem, desc_sf(smem_u32(smem + L::kOffSfa + stage * L::kSfa)));
 #pragma unroll
-          for (int j = 0; j < BLOCK_N / 128; ++j)
-            tc_cp_sf(sfb_tmem + 4 * j, desc_sf(smem_u32(smem + L::kOffSfb + stage * L::kSfb + j * 512)));
+          for (int j = 0; j < L::kSfbAtoms; ++j)
+            tc_cp_sf(sfb_base + 4 * j, desc_sf(smem_u32(smem + L::kOffSfb + stage * L::kSfb + j * 512)));
           const uint64_t a_desc = desc_sw128(smem_u32(smem + L::kOffA + stage * L::kA));
           const uint64_t b_desc = desc_sw128(smem_u32(smem + L::kOffB + stage * L::kB));
 #pragma unroll
@@ -329,7 +395,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       int m_tile, n_tile, e;
-      if (!decode_tile(p, tile, m_tile, n_tile, e)) continue;
+      if (!decode_tile(p, sched, tile, m_tile, n_tile, e)) continue;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
@@ -337,6 +403,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       if constexpr (EPI == 0) {
         const int64_t k_atoms = (p.I + 127) >> 7;
         const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.n_total : nullptr;
+        const bool clamp = (p.gate_lo == p.gate_lo) || (p.gate_hi == p.gate_hi) || (p.up_lo == p.up_lo) ||
+                           (p.up_hi == p.up_hi);
+        const float g_lo = p.gate_lo == p.gate_lo ? p.gate_lo : -INFINITY, g_hi = p.gate_hi == p.gate_hi ? p.gate_hi : INFINITY;
+        const float u_lo = p.up_lo == p.up_lo ? p.up_lo : -INFINITY, u_hi = p.up_hi == p.up_hi ? p.up_hi : INFINITY;
 #pragma unroll 1
         for (int c = 0; c < BLOCK_N / 64; ++c) {
           float g[32], u[32];
@@ -345,25 +415,47 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           const int n0 = n_tile * BLOCK_N + c * 64;
           const int i0 = n0 >> 1;
           if (i0 >= p.I) continue;
-          uint32_t mx = 0;
+          if (bias != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float gv = g[j], uv = u[j];
-            if (bias) { gv += bias[n0 + j]; uv += bias[n0 + 32 + j]; }
-            if (p.gate_lo == p.gate_lo) gv = fmaxf(gv, p.gate_lo);
-            if (p.gate_hi == p.gate_hi) gv = fminf(gv, p.gate_hi);
-            if (p.up_lo == p.up_lo) uv = fmaxf(uv, p.up_lo);
-            if (p.up_hi == p.up_hi) uv = fminf(uv, p.up_hi);
-            const float m = __bfloat162float(__float2bfloat16_rn(apply_act(gv, p.act) * uv));
-            g[j] = m;
-            mx = max(mx, __float_as_uint(m) & 0x7fffffffu);
+            for (int j = 0; j < 32; ++j) { g[j] += bias[n0 + j]; u[j] += bias[n0 + 32 + j]; }
           }
-          float f1, f2;
-          mx_block_factors(mx, f1, f2);
-          uint32_t w[8];
+          if (clamp) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            w[j] = pack4_e4m3(g[4 * j] * f1 * f2, g[4 * j + 1] * f1 * f2, g[4 * j + 2] * f1 * f2, g[4 * j + 3] * f1 * f2);
+            for (int j = 0; j < 32; ++j) {
+              g[j] = fminf(fmaxf(g[j], g_lo), g_hi);
+              u[j] = fminf(fmaxf(u[j], u_lo), u_hi);
+            }
+          }
+          uint32_t mx = 0;
+          if (p.act == B200MOE_ACT_SILU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float sg = __fdividef(g[j], 1.0f + __expf(-g[j]));
+              const float m = __bfloat162float(__float2bfloat16_rn(sg * u[j]));
+              g[j] = m;
+              mx = max(mx, __float_as_uint(m) & 0x7fffffffu);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float m = __bfloat162float(__float2bfloat16_rn(apply_act(g[j], p.act) * u[j]));
+              g[j] = m;
+              mx = max(mx, __float_as_uint(m) & 0x7fffffffu);
+            }
+          }
+          uint32_t w[8];
+          const int e_max = static_cast<int>(mx >> 23);
+          if (e_max >= 9) {  // one exact power-of-two factor
+            const float f = __uint_as_float(static_cast<uint32_t>(135 - e_max + 127) << 23);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[j] = pack4_e4m3(g[4 * j] * f, g[4 * j + 1] * f, g[4 * j + 2] * f, g[4 * j + 3] * f);
+          } else {
+            float f1, f2;
+            mx_block_factors(mx, f1, f2);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              w[j] = pack4_e4m3(g[4 * j] * f1 * f2, g[4 * j + 1] * f1 * f2, g[4 * j + 2] * f1 * f2, g[4 * j + 3] * f1 * f2);
+          }
           uint4* dst = reinterpret_cast<uint4*>(p.m_codes + row * p.I + i0);
           dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
           dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
@@ -429,6 +521,13 @@ __device__ float mx_dot(const uint8_t* a, const uint8_t* a_sf, int64_t a_row, co
   return acc;
 }
 
+__device__ bool block_is_active(const GemmParams& p, int block) {
+  if (p.conditions == nullptr) return true;
+  for (int b = 0; b <= block; ++b)
+    if (p.conditions[b] == 0) return false;
+  return true;
+}
+
 __global__ void simt_gemm1_kernel(const uint8_t* x, const uint8_t* w, GemmParams p, int K) {
   // one thread per (position, 32-block of intermediates)
   const int blocks_i = p.I / 32;
@@ -439,7 +538,7 @@ __global__ void simt_gemm1_kernel(const uint8_t* x, const uint8_t* w, GemmParams
     const int64_t row = idx / blocks_i;
     const int m_tile = static_cast<int>(row >> 7);
     const int block = m_tile / (p.B >> 7);
-    if (p.conditions && p.conditions[block] == 0) continue;
+    if (!block_is_active(p, block)) continue;
     if (p.tile_flags && p.tile_flags[m_tile] == 0) continue;
     const int e = p.block_to_expert[block];
     if (e < 0 || e >= p.E) continue;
@@ -477,7 +576,7 @@ __global__ void simt_gemm2_kernel(const uint8_t* m, const uint8_t* w, GemmParams
     const int64_t row = idx / p.H_out;
     const int m_tile = static_cast<int>(row >> 7);
     const int block = m_tile / (p.B >> 7);
-    if (p.conditions && p.conditions[block] == 0) continue;
+    if (!block_is_active(p, block)) continue;
     if (p.tile_flags && p.tile_flags[m_tile] == 0) continue;
     const int e = p.block_to_expert[block];
     if (e < 0 || e >= p.E) continue;
@@ -539,12 +638,13 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
   return B200MOE_OK;
 }
 
-int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128 or 256)
+int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128, 192 or 256)
 
 int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, int impl, cudaStream_t st) {
   B200MOE_REQUIRE(p.B > 0 && p.B % 128 == 0, B200MOE_ERR_INVALID, "block size must be a multiple of 128, got %d", p.B);
   B200MOE_REQUIRE(K % 32 == 0 && K >= 32, B200MOE_ERR_INVALID, "contraction length must be a multiple of 32, got %d", K);
-  B200MOE_REQUIRE(p.n_blocks > 0 && p.E > 0, B200MOE_ERR_INVALID, "need at least one block and one expert");
+  B200MOE_REQUIRE(p.n_blocks > 0 && p.E > 0 && p.E <= kMaxExperts, B200MOE_ERR_INVALID,
+                  "need at least one block and between 1 and %d experts", kMaxExperts);
   B200MOE_REQUIRE(p.status != nullptr, B200MOE_ERR_INVALID, "status pointer must not be null");
   p.m_tiles_total = p.n_blocks * (p.B / 128);
   p.k_blocks = (K + kBlockK - 1) / kBlockK;
@@ -569,6 +669,7 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   rc = make_rows_map(&mb, b, K, p.n_total, p.E, bn);
   if (rc != B200MOE_OK) return rc;
   if (bn == 256) return epi == 0 ? launch_tc<256, 4, 0>(ma, mb, p, st) : launch_tc<256, 4, 1>(ma, mb, p, st);
+  if (bn == 192) return epi == 0 ? launch_tc<192, 5, 0>(ma, mb, p, st) : launch_tc<192, 5, 1>(ma, mb, p, st);
   return epi == 0 ? launch_tc<128, 6, 0>(ma, mb, p, st) : launch_tc<128, 6, 1>(ma, mb, p, st);
 }
 
@@ -578,7 +679,8 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
 using namespace b200moe;
 
 extern "C" int b200moe_set_gemm_tile_n(int block_n) {
-  B200MOE_REQUIRE(block_n == 128 || block_n == 256, B200MOE_ERR_INVALID, "tile width must be 128 or 256, got %d", block_n);
+  B200MOE_REQUIRE(block_n == 128 || block_n == 192 || block_n == 256, B200MOE_ERR_INVALID,
+                  "tile width must be 128, 192 or 256, got %d", block_n);
   g_block_n = block_n;
   return B200MOE_OK;
 }

@@ -218,10 +218,20 @@ __global__ void indexed_flatten_kernel(const int32_t* input, int E, int T, int f
 
 __global__ void position_table_kernel(const int32_t* tpi, const int32_t* block_to_expert, const int32_t* conditions,
                                       int64_t n_pos, int B, int T, int E, int32_t* table) {
+  // blocks run up to the first zero condition
+  __shared__ int s_n_active;
+  const int n_blocks = static_cast<int>(n_pos / B);
+  if (threadIdx.x == 0) s_n_active = n_blocks;
+  __syncthreads();
+  if (conditions != nullptr)
+    for (int b = threadIdx.x; b < n_blocks; b += blockDim.x)
+      if (conditions[b] == 0) atomicMin(&s_n_active, b);
+  __syncthreads();
+  const int n_active = s_n_active;
   for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < n_pos;
        p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int b = static_cast<int>(p / B);
-    if (conditions != nullptr && conditions[b] == 0) continue;
+    if (b >= n_active) continue;
     const int t = tpi[p];
     if (t < 0 || t >= T) continue;
     const int e = block_to_expert[b];

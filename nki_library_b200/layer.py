@@ -44,10 +44,11 @@ class MoELayer:
         self.counts = torch.empty(E, dtype=torch.int32, device=dev)
         self.inv = torch.empty((T, K), dtype=torch.int32, device=dev)
         self.gstatus = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.rws = torch.empty(lib.b200moe_router_workspace_bytes(T, self.H, E), dtype=torch.uint8, device=dev)
         self.gws = torch.empty(lib.b200moe_group_tokens_workspace_bytes(T, E), dtype=torch.uint8, device=dev)
         self.ws = pipeline.BlockWorkspace(self.N * B, self.H, self.I, dev)
         self.out = torch.empty((T, self.H), dtype=torch.bfloat16, device=dev)
-        self.kernels_per_forward = 8  # router, 3 grouping, quantise, 2 contractions, combine
+        self.kernels_per_forward = 9  # 2 router, 3 grouping, quantise, 2 contractions, combine
 
     def forward(self, hidden: torch.Tensor, timers: Optional[dict] = None) -> torch.Tensor:
         """``hidden`` bf16 ``[T, H]`` on the device; returns the layer's bf16 ``[T, H]`` output buffer."""
@@ -71,7 +72,7 @@ class MoELayer:
         timed("router_topk", lambda: _lib.call(
             "b200moe_router_topk", _lib.ptr(hidden), 1, _lib.ptr(self.w), _lib.ptr(self.bias), T, H, E, K,
             self.router_act.value, int(self.pre_norm), int(self.l1), None, _lib.F32, _lib.ptr(self.idx),
-            _lib.ptr(self.aff), _lib.F32, st))
+            _lib.ptr(self.aff), _lib.F32, _lib.ptr(self.rws), self.rws.numel(), st))
         timed("group_tokens", lambda: _lib.call(
             "b200moe_group_tokens", _lib.ptr(self.idx), _lib.ROUTING_INDEX, _lib.I32, T, E, K, B, N, 1, 1,
             _lib.ptr(self.tpi), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(self.counts), _lib.ptr(self.inv),

@@ -46,7 +46,8 @@ def test_router_topk_vs_reference_fixture(lib, name, x_layout):
                            router_pre_norm=pre_norm, norm_topk_prob=l1, use_indirect_dma_scatter=True)
     assert outs[0] is logits and outs[1] is idx and outs[2] is aff
     lg = logits.cpu().numpy()
-    np.testing.assert_allclose(lg, gold[name + "/logits"], rtol=0, atol=2e-5)
+    # bf16 products are exact in fp32; only the summation order (tensor-core tree, split-K) differs
+    np.testing.assert_allclose(lg, gold[name + "/logits"], rtol=0, atol=1e-4)
     # top-K and affinities are exact functions of the logits: the oracle on the GPU's own logits must agree bit for bit
     act_id = routing.SOFTMAX if act == "softmax" else routing.SIGMOID
     o_idx, o_aff = routing.router_from_logits(torch.from_numpy(lg), k, act_id, pre_norm, l1)
@@ -54,9 +55,9 @@ def test_router_topk_vs_reference_fixture(lib, name, x_layout):
     np.testing.assert_allclose(aff.cpu().numpy(), o_aff.numpy(), rtol=2e-6, atol=1e-7)
     # and against the stored reference outputs wherever the reference's own top-K margin exceeds the logit tolerance
     ref_lg = np.sort(gold[name + "/logits"], axis=1)[:, ::-1]
-    safe = (ref_lg[:, :k] - ref_lg[:, 1:k + 1]).min(axis=1) > 1e-4 if k < E else np.ones(T, bool)
+    safe = (ref_lg[:, :k] - ref_lg[:, 1:k + 1]).min(axis=1) > 4e-4 if k < E else np.ones(T, bool)
     assert np.array_equal(idx.cpu().numpy()[safe], gold[name + "/index"][safe])
-    np.testing.assert_allclose(aff.cpu().numpy(), gold[name + "/aff"], rtol=0, atol=2e-5)
+    np.testing.assert_allclose(aff.cpu().numpy()[safe], gold[name + "/aff"][safe], rtol=0, atol=1e-4)
 
 
 def test_router_bf16_outputs_and_eager(lib):
