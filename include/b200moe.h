@@ -108,6 +108,25 @@ int b200moe_group_tokens(const void* routing, int routing_mode, int routing_dtyp
                          int32_t* conditions, int32_t* counts, int32_t* inverse_map, int32_t* status, void* workspace,
                          size_t workspace_bytes, b200moe_stream_t stream);
 
+/* Same grouping for callers that must not allocate device memory -- code running
+ * inside a memory-pool or allocator callback, a plug-in whose host forbids
+ * cudaMalloc after start-up, or a real-time serving loop where an allocation
+ * could stall behind another thread's free.  No counterpart in the reference.
+ * The scratch is a 1 MiB device array built into the library (held by every GPU
+ * that loads it until the process exits), so the problem must satisfy
+ * b200moe_group_tokens_workspace_bytes(T, E) <= b200moe_group_tokens_static_max_bytes();
+ * larger problems are rejected with B200MOE_ERR_WORKSPACE.  Neither the call nor
+ * anything it runs allocates or frees memory.  The first call on each device looks
+ * up the array's device address (with that device current); make that first call
+ * outside any stream capture.  All calls share the one array: nothing in it needs
+ * clearing between calls (each call overwrites what it reads), but two calls that
+ * overlap on the GPU -- different streams without an ordering between them -- race. */
+size_t b200moe_group_tokens_static_max_bytes(void);
+int b200moe_group_tokens_static(const void* routing, int routing_mode, int routing_dtype, int T, int E, int K, int B,
+                                int N, int skip_token, int mx_conditions, int32_t* token_position_to_id,
+                                int32_t* block_to_expert, int32_t* conditions, int32_t* counts, int32_t* inverse_map,
+                                int32_t* status, b200moe_stream_t stream);
+
 /* position table for the combine when only token_position_to_id is known (moe_cte's
  * own argument list): pos_table[t*E + e] = position of token t in a block of expert e, else -1. */
 int b200moe_build_position_table(const int32_t* token_position_to_id, const int32_t* block_to_expert,

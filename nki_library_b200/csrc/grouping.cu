@@ -268,6 +268,32 @@ int run_grouping(const GroupArgs& a, int mode, int B, int N, int mx_conditions, 
   return B200MOE_OK;
 }
 
+
+// ---- grouping without any allocation --------------------------------------------
+// Scratch of b200moe_group_tokens_static.  It lives in the library image: every
+// GPU that loads the library keeps these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = 1u << 20;  // 1 MiB
+static __device__ __align__(256) unsigned char g_group_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices] = {};  // device address of g_group_scratch, per device ordinal
+
+// The array's name is only a host-side handle; kernels need the device address,
+// looked up once per device while that device is current.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  B200MOE_CUDA_OK(cudaGetDevice(&dev));
+  B200MOE_REQUIRE(dev >= 0 && dev < kMaxDevices, B200MOE_ERR_INVALID, "device ordinal %d is out of range", dev);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    B200MOE_CUDA_OK(cudaGetSymbolAddress(&p, g_group_scratch));
+    B200MOE_REQUIRE(p != nullptr, B200MOE_ERR_CUDA, "cudaGetSymbolAddress returned a null scratch address");
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return B200MOE_OK;
+}
+
 }  // namespace
 }  // namespace b200moe
 
@@ -349,4 +375,24 @@ extern "C" int b200moe_build_position_table(const int32_t* token_position_to_id,
                                               pos_table);
   B200MOE_LAUNCH_OK("position_table_kernel");
   return B200MOE_OK;
+}
+
+extern "C" size_t b200moe_group_tokens_static_max_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int b200moe_group_tokens_static(const void* routing, int routing_mode, int routing_dtype, int T, int E,
+                                           int K, int B, int N, int skip_token, int mx_conditions,
+                                           int32_t* token_position_to_id, int32_t* block_to_expert,
+                                           int32_t* conditions, int32_t* counts, int32_t* inverse_map, int32_t* status,
+                                           b200moe_stream_t stream) {
+  const size_t need = group_ws_bytes(T, E);
+  B200MOE_REQUIRE(T > 0 && E > 0 && need <= kStaticScratchBytes, B200MOE_ERR_WORKSPACE,
+                  "group_tokens_static: T=%d, E=%d needs %zu scratch bytes, the built-in scratch holds %zu; "
+                  "use b200moe_group_tokens with a caller workspace for larger problems",
+                  T, E, need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != B200MOE_OK) return rc;
+  return b200moe_group_tokens(routing, routing_mode, routing_dtype, T, E, K, B, N, skip_token, mx_conditions,
+                              token_position_to_id, block_to_expert, conditions, counts, inverse_map, status, scratch,
+                              kStaticScratchBytes, stream);
 }
