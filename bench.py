@@ -202,14 +202,50 @@ def run_ours(args, cfg, name):
         from nki_library_b200 import _lib
         _lib.call("b200moe_set_gemm_tile_n", args.tile_n)
 
-    # Experts are independent given the routing, so N GPUs run as N replicas of the
-    # single-GPU layer on their own token batches (weak scaling, no data-path collective).
-    weights = random_expert_weights(E, H, I, dev, seed=7)
     hidden_h, router_w, bias = make_inputs(cfg, dev, rank)
     hidden_pin = hidden_h.pin_memory()
     out_pin = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
     hidden_d = hidden_h.to(dev)
-    layer = MoELayer(router_w.to(dev), weights, K, B, T, None if bias is None else bias.to(dev))
+    bias_d = None if bias is None else bias.to(dev)
+    if world == 1:
+        weights = random_expert_weights(E, H, I, dev, seed=7)
+        layer = MoELayer(router_w.to(dev), weights, K, B, T, bias_d)
+        n_blocks = layer.N
+
+        def forward(h, timers=None):
+            return layer.forward(h, timers)
+
+        def device_status():
+            return layer.device_status()
+
+        def launches_per_step():
+            return layer.kernels_per_forward
+    else:
+        # Expert parallelism: every rank keeps its own T tokens (weak scaling) and E / world experts;
+        # token rows travel to the owning rank and back through NCCL all-to-all.
+        from nki_library_b200.ep import CudaOps, ExpertParallelMoE
+        if E % world != 0:
+            raise SystemExit(f"workload has {E} experts, not divisible by {world} ranks")
+        weights = random_expert_weights(E // world, H, I, dev, seed=7 + rank)
+        ops = CudaOps(router_w.to(dev), weights, E, K, B, bias_d)
+        ep = ExpertParallelMoE(ops, E)
+        n_blocks = None
+
+        def forward(h, timers=None):
+            ops.timers = timers
+            return ep.forward(h)
+
+        def device_status():
+            return pipeline_status()
+
+        def pipeline_status():
+            from nki_library_b200 import pipeline
+            return [int(v) for ws in pipeline._workspaces.values() for v in ws.status.cpu().tolist()[1:3]]
+
+        _count = {"n": 0}
+
+        def launches_per_step():
+            return _count["n"]
 
     def barrier():
         if world > 1:
@@ -217,9 +253,14 @@ def run_ours(args, cfg, name):
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
-        layer.forward(hidden_d)
+        forward(hidden_d)
     barrier()
-    status = layer.device_status()
+    if world > 1:
+        ops.launches = 0
+        forward(hidden_d)
+        _count["n"] = ops.launches
+        barrier()
+    status = device_status()
     if any(status):
         raise RuntimeError(f"device status after warm-up: {status}")
 
@@ -233,7 +274,7 @@ def run_ours(args, cfg, name):
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
     for _ in range(args.steps):
-        layer.forward(hidden_d, timers)
+        forward(hidden_d, timers)
     t_end.record()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
@@ -243,7 +284,7 @@ def run_ours(args, cfg, name):
     e_start.record()
     for _ in range(args.steps):
         hidden_d.copy_(hidden_pin, non_blocking=True)
-        out = layer.forward(hidden_d)
+        out = forward(hidden_d)
         out_pin.copy_(out, non_blocking=True)
     e_end.record()
     barrier()
@@ -254,13 +295,19 @@ def run_ours(args, cfg, name):
         t = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total, ms_e2e = t.tolist()
-    status = layer.device_status()
+    status = device_status()
     if any(status):
         raise RuntimeError(f"device status after timing: {status}")
 
     if rank == 0:
         work = algorithmic_work(cfg)
-        per_kernel = {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in timers.items()}
+        if world == 1:
+            per_kernel = {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in timers.items()}
+        else:
+            n = len(timers["t0"])
+            names = ("gather_quantize", "gemm1_swiglu", "gemm2_scale")
+            per_kernel = {nm: sum(timers[f"t{i}"][j].elapsed_time(timers[f"t{i + 1}"][j]) for j in range(n)) / n
+                          for i, nm in enumerate(names)}
         ms_step = ms_total / args.steps
         if cfg["kind"] == "prefill":
             dom = "gemm1_swiglu"
@@ -286,8 +333,9 @@ def run_ours(args, cfg, name):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8_e4m3",
             "data": "synthetic",
-            "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}, "n_blocks": layer.N,
-                       "parallelism": f"replicas x{world}" if world > 1 else "single",
+            "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}, "n_blocks": n_blocks,
+                       "tokens_per_gpu": T, "experts_per_gpu": E // world,
+                       "parallelism": f"ep{world} (NCCL all-to-all dispatch/combine)" if world > 1 else "single",
                        "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)" % (weights.nbytes() / 1e9)},
             "roofline": roofline,
             "kernel_ms": per_kernel,
@@ -295,7 +343,7 @@ def run_ours(args, cfg, name):
                              "sample": cpu["sample"]},
             "e2e": {"value": world * T / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2},
-            "gpu_launches": layer.kernels_per_forward * args.steps * 2,
+            "gpu_launches": launches_per_step() * args.steps * 2,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -187,14 +187,16 @@ int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_t* x_sf, co
 /* gemm2 = down_projection_mx + bias + affinity scaling of each row
  * (core/mlp/mlp_tkg/down_projection_mx_shard_H.py:212-387,
  *  core/moe/moe_cte/bwmm_shard_on_block_mx.py:1297-1317).  affinities is the flat
- * [(rows)*E] table addressed tok*E + e (core/moe/moe_cte/moe_cte_utils.py:544-636),
- * or NULL for no scaling.  Output: bf16 y_pos [n_blocks*B, H] (pad rows untouched). */
+ * [(rows)*E] table addressed tok*E + e (core/moe/moe_cte/moe_cte_utils.py:544-636) when
+ * aff_per_row == 0, a [rows] vector addressed tok when aff_per_row != 0 (rows that arrived
+ * through an expert-parallel dispatch carry their own affinity), or NULL for no scaling.  Output: bf16 y_pos [n_blocks*B, H] (pad rows untouched). */
 int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
                                 const uint8_t* w2_sf, const float* bias_d, const int32_t* block_to_expert,
                                 const int32_t* conditions, const int32_t* tile_flags,
                                 const int32_t* token_position_to_id, int hidden_rows,
                                 int n_blocks, int B, int E, int H, int I, const void* affinities, int aff_dtype,
-                                void* y_pos_bf16, int32_t* status, int impl, b200moe_stream_t stream);
+                                int aff_per_row, void* y_pos_bf16, int32_t* status, int impl,
+                                b200moe_stream_t stream);
 
 /* Weight rows per tile of the tensor-core kernel: 256 (default), 192 or 128.  Tuning knob
  * with no counterpart in the reference. */

@@ -56,7 +56,7 @@ SIGNATURES = {
                                              c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_grouped_gemm2_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                            c_int, c_void_p, c_void_p, c_int, c_void_p]),
+                                            c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_set_gemm_tile_n": (c_int, [c_int]),
     "b200moe_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
 }

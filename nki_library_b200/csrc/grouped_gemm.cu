@@ -53,6 +53,7 @@ struct GemmParams {
   int I;
   const void* aff;
   int aff_dtype;
+  int aff_per_row;  // 0: table [rows, E] addressed tok*E + e; 1: vector [rows] addressed tok
   __nv_bfloat16* y_pos;
   int H_out;
   int32_t* status;
@@ -465,7 +466,9 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const int tok = p.tpi ? p.tpi[row] : static_cast<int>(row);
         const bool valid = tok >= 0 && tok < p.hidden_rows;
         float aff = 1.0f;
-        if (valid && p.aff != nullptr) aff = load_as_float(p.aff, static_cast<int64_t>(tok) * p.E + e, p.aff_dtype);
+        if (valid && p.aff != nullptr)
+          aff = load_as_float(p.aff, p.aff_per_row ? static_cast<int64_t>(tok) : static_cast<int64_t>(tok) * p.E + e,
+                              p.aff_dtype);
         const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.H_out : nullptr;
 #pragma unroll 1
         for (int c = 0; c < BLOCK_N / 32; ++c) {
@@ -585,7 +588,9 @@ __global__ void simt_gemm2_kernel(const uint8_t* m, const uint8_t* w, GemmParams
     float y = mx_dot(m, p.a_sf, row, w + static_cast<int64_t>(e) * p.n_total * K,
                      p.b_sf + static_cast<int64_t>(e) * p.b_sf_expert_stride, h, K);
     if (p.bias) y += p.bias[static_cast<int64_t>(e) * p.H_out + h];
-    if (p.aff) y *= load_as_float(p.aff, static_cast<int64_t>(tok) * p.E + e, p.aff_dtype);
+    if (p.aff)
+      y *= load_as_float(p.aff, p.aff_per_row ? static_cast<int64_t>(tok) : static_cast<int64_t>(tok) * p.E + e,
+                         p.aff_dtype);
     p.y_pos[row * p.H_out + h] = __float2bfloat16_rn(y);
   }
 }
@@ -727,7 +732,8 @@ extern "C" int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t
                                            const int32_t* conditions, const int32_t* tile_flags,
                                            const int32_t* token_position_to_id, int hidden_rows, int n_blocks, int B,
                                            int E, int H, int I, const void* affinities, int aff_dtype,
-                                           void* y_pos_bf16, int32_t* status, int impl, b200moe_stream_t stream) {
+                                           int aff_per_row, void* y_pos_bf16, int32_t* status, int impl,
+                                           b200moe_stream_t stream) {
   B200MOE_REQUIRE(m_codes && m_sf && w2_dev && w2_sf && block_to_expert && y_pos_bf16, B200MOE_ERR_INVALID,
                   "grouped_gemm2: null pointer argument");
   B200MOE_REQUIRE(H % 32 == 0 && H > 0, B200MOE_ERR_INVALID, "grouped_gemm2: H must be a positive multiple of 32, got %d", H);
@@ -748,6 +754,7 @@ extern "C" int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t
   p.bias = bias_d;
   p.aff = affinities;
   p.aff_dtype = aff_dtype;
+  p.aff_per_row = aff_per_row;
   p.y_pos = static_cast<__nv_bfloat16*>(y_pos_bf16);
   p.H_out = H;
   p.I = I;

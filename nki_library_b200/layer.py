@@ -88,7 +88,7 @@ class MoELayer:
         timed("gemm2_scale", lambda: _lib.call(
             "b200moe_grouped_gemm2_scale", _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(w.w2), _lib.ptr(w.w2_sf),
             _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(ws.tile_flags), _lib.ptr(self.tpi),
-            T, N, B, E, H, I, _lib.ptr(self.aff), _lib.F32, _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), 0, st))
+            T, N, B, E, H, I, _lib.ptr(self.aff), _lib.F32, 0, _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), 0, st))
         timed("combine", lambda: _lib.call(
             "b200moe_combine", _lib.ptr(ws.y_pos), _lib.ptr(self.inv), T, K, H, _lib.ptr(self.out), st))
         return self.out

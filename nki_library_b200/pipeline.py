@@ -56,12 +56,14 @@ def run_blocks(hidden: torch.Tensor, hidden_rows: int, weights: ExpertWeights, t
                block_to_expert: torch.Tensor, conditions: Optional[torch.Tensor], block_size: int,
                affinities: Optional[torch.Tensor], table: torch.Tensor, out: torch.Tensor, act_fn: int = 0,
                gate_clamp=(None, None), up_clamp=(None, None), impl: int = 0, check_status: bool = False,
-               workspace: Optional[BlockWorkspace] = None) -> torch.Tensor:
+               workspace: Optional[BlockWorkspace] = None, aff_per_row: bool = False,
+               timers: Optional[dict] = None) -> torch.Tensor:
     """Run the four kernels.  ``table [rows_out, n_cand]`` lists, per output row, the positions to sum.
 
     ``hidden`` bf16 ``[>= hidden_rows, H]``; ids outside ``[0, hidden_rows)`` in
     ``token_position_to_id`` are pads.  ``affinities`` is the flat table addressed
-    ``token * E + expert`` (fp32 or bf16) or None.  ``out`` bf16 ``[rows_out, H]``.
+    ``token * E + expert`` (fp32 or bf16), a per-row vector addressed ``token``
+    when ``aff_per_row``, or None.  ``out`` bf16 ``[rows_out, H]``.
     """
     E, H, I = weights.E, weights.H, weights.I
     n_blocks = block_to_expert.numel()
@@ -72,18 +74,29 @@ def run_blocks(hidden: torch.Tensor, hidden_rows: int, weights: ExpertWeights, t
                        "hidden_states must be contiguous bf16 [rows, H]")
     ws = workspace or get_workspace(n_pos, H, I, hidden.device)
     st = _lib.stream_ptr()
+
+    def mark(name):
+        if timers is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            timers.setdefault(name, []).append(ev)
+
+    mark("t0")
     _lib.call("b200moe_gather_quantize_mxfp8", _lib.ptr(hidden), hidden_rows, H, _lib.ptr(token_position_to_id), n_pos,
               int(weights.h_packed_order), _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(ws.tile_flags), st)
+    mark("t1")
     _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(weights.w1),
               _lib.ptr(weights.w1_sf), _lib.ptr(weights.bias_gu), _lib.ptr(block_to_expert), _lib.ptr(conditions),
               _lib.ptr(ws.tile_flags), n_blocks, block_size, E, H, I, act_fn, _clamp(gate_clamp[0]),
               _clamp(gate_clamp[1]), _clamp(up_clamp[0]), _clamp(up_clamp[1]), _lib.ptr(ws.mq), _lib.ptr(ws.m_sf),
               _lib.ptr(ws.status[1:]), impl, st)
+    mark("t2")
     _lib.call("b200moe_grouped_gemm2_scale", _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(weights.w2),
               _lib.ptr(weights.w2_sf), _lib.ptr(weights.bias_d), _lib.ptr(block_to_expert), _lib.ptr(conditions),
               _lib.ptr(ws.tile_flags), _lib.ptr(token_position_to_id), hidden_rows, n_blocks, block_size, E, H, I,
               _lib.ptr(affinities), _lib.F32 if affinities is None else _lib.dtype_code(affinities),
-              _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), impl, st)
+              int(aff_per_row), _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), impl, st)
+    mark("t3")
     _lib.call("b200moe_combine", _lib.ptr(ws.y_pos), _lib.ptr(table), out.shape[0], table.shape[1], H, _lib.ptr(out), st)
     if check_status:
         s = ws.status.cpu().tolist()
