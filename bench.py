@@ -268,25 +268,51 @@ def run_ours(args, cfg, name):
     if rank == 0:
         sampler.start()
         time.sleep(0.2)
-    # -------- resident-input leg (value) with per-kernel events
-    timers = {}
+    # -------- resident-input leg (value): the captured launch sequence (single GPU) or eager steps (EP)
+    use_graph = world == 1 and not args.no_graph
+    if use_graph:
+        layer.capture(hidden_d)
+        layer.replay()
     barrier()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
     for _ in range(args.steps):
-        forward(hidden_d, timers)
+        if use_graph:
+            layer.replay()
+        else:
+            forward(hidden_d)
     t_end.record()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
+    # -------- the same steps again, eagerly, with CUDA events around every kernel (roofline input)
+    timers = {}
+    barrier()
+    for _ in range(args.steps):
+        forward(hidden_d, timers)
+    barrier()
     # -------- end-to-end leg: host buffers through the public layer call
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record()
-    for _ in range(args.steps):
-        hidden_d.copy_(hidden_pin, non_blocking=True)
-        out = forward(hidden_d)
-        out_pin.copy_(out, non_blocking=True)
-    e_end.record()
+    if use_graph:
+        from nki_library_b200.layer import HostPipeline
+        pipe = HostPipeline(layer)
+        out_pins = [out_pin, torch.empty_like(out_pin).pin_memory()]
+        pipe.submit(hidden_pin, out_pins[0])
+        pipe.drain()
+        pipe.step = 0
+        barrier()
+        e_start.record()
+        for i in range(args.steps):
+            pipe.submit(hidden_pin, out_pins[i & 1])
+        pipe.drain()
+        e_end.record()
+    else:
+        e_start.record()
+        for _ in range(args.steps):
+            hidden_d.copy_(hidden_pin, non_blocking=True)
+            out = forward(hidden_d)
+            out_pin.copy_(out, non_blocking=True)
+        e_end.record()
     barrier()
     ms_e2e = e_start.elapsed_time(e_end)
     clocks = sampler.stop() if rank == 0 else None
@@ -343,7 +369,9 @@ def run_ours(args, cfg, name):
                              "sample": cpu["sample"]},
             "e2e": {"value": world * T / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2},
-            "gpu_launches": launches_per_step() * args.steps * 2,
+            "gpu_launches": launches_per_step() * args.steps * 3,
+            "launch_mode": "cuda graph replay (value, e2e) + eager instrumented pass (kernel_ms)" if use_graph
+                           else "eager",
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -359,6 +387,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mixtral_prefill", choices=sorted(WORKLOADS))
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--tile-n", type=int, default=0, help="weight rows per GEMM tile (128/192/256; 0 = library default)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]

@@ -198,7 +198,7 @@ int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, con
                                 int aff_per_row, void* y_pos_bf16, int32_t* status, int impl,
                                 b200moe_stream_t stream);
 
-/* Weight rows per tile of the tensor-core kernel: 256 (default), 192 or 128.  Tuning knob
+/* Weight rows per tile of the tensor-core kernel: 256 (default) or 128.  Tuning knob
  * with no counterpart in the reference. */
 int b200moe_set_gemm_tile_n(int block_n);
 

@@ -6,7 +6,9 @@
 //               rows (both 128B-swizzled) and their UE8M0 scale atoms (bulk copies)
 //   warp 1      allocates TMEM and issues tcgen05.cp (scales -> TMEM) followed by
 //               four tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 each) per slab
-//   warps 2..5  epilogue: tcgen05.ld of the fp32 accumulator (one row per thread)
+//   warps 2..9  epilogue: two warps per TMEM lane quadrant, each thread pulls half of
+//               its accumulator row into registers with tcgen05.ld, hands the TMEM
+//               buffer back to the MMA warp at once, then works from registers
 //               EPI 0: + bias, clamp, act(gate) * up, bf16 rounding, MXFP8
 //                      re-quantisation (32 consecutive intermediates live in one
 //                      thread), codes + scale atoms out
@@ -30,7 +32,7 @@ constexpr int kBlockM = 128;
 constexpr int kBlockK = 128;  // bytes (= e4m3 elements) per pipeline slab
 constexpr int kGroupM = 16;
 constexpr int kMaxExperts = 512;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 struct GemmParams {
@@ -141,8 +143,9 @@ __device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint64_t a_desc, ui
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Asynchronous: the registers are valid only after tc_wait_ld().
+__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -153,9 +156,6 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 // K-major operand tile, rows of 128 bytes, 128B swizzle: 8-row groups 1024 B apart.
@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const GemmParams p) {
   using L = SmemLayout<BLOCK_N, STAGES>;
-  constexpr int kAcc = (BLOCK_N <= 192) ? 2 : 1;
+  constexpr int kAcc = (BLOCK_N <= 128) ? 2 : 1;
   constexpr int kSfCol = kAcc * BLOCK_N;  // TMEM columns: accumulators, then SFA (4), then SFB
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kIdesc = make_idesc(kBlockM, BLOCK_N);
@@ -302,7 +302,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     }
     for (int a = 0; a < kAcc; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], 8);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -390,32 +390,45 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     }
   } else {
     // ------------------------------------------------------------ epilogue
+    constexpr int kCW = BLOCK_N / 2;   // accumulator columns per thread
+    constexpr int kLd = kCW / 32;      // 32-column TMEM loads per thread
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row_in_tile = q * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
+    const bool clamp = (p.gate_lo == p.gate_lo) || (p.gate_hi == p.gate_hi) || (p.up_lo == p.up_lo) ||
+                       (p.up_hi == p.up_hi);
+    const float g_lo = p.gate_lo == p.gate_lo ? p.gate_lo : -INFINITY, g_hi = p.gate_hi == p.gate_hi ? p.gate_hi : INFINITY;
+    const float u_lo = p.up_lo == p.up_lo ? p.up_lo : -INFINITY, u_hi = p.up_hi == p.up_hi ? p.up_hi : INFINITY;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       int m_tile, n_tile, e;
       if (!decode_tile(p, sched, tile, m_tile, n_tile, e)) continue;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N + half * kCW;
       const int64_t row = static_cast<int64_t>(m_tile) * kBlockM + row_in_tile;
+      uint32_t raw[kLd][32];
+#pragma unroll
+      for (int l = 0; l < kLd; ++l) tc_ld32_nowait(taddr + l * 32, raw[l]);
+      tc_wait_ld();
+      // the accumulator now lives in registers: give the TMEM buffer back before doing the math
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
+
       if constexpr (EPI == 0) {
         const int64_t k_atoms = (p.I + 127) >> 7;
         const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.n_total : nullptr;
-        const bool clamp = (p.gate_lo == p.gate_lo) || (p.gate_hi == p.gate_hi) || (p.up_lo == p.up_lo) ||
-                           (p.up_hi == p.up_hi);
-        const float g_lo = p.gate_lo == p.gate_lo ? p.gate_lo : -INFINITY, g_hi = p.gate_hi == p.gate_hi ? p.gate_hi : INFINITY;
-        const float u_lo = p.up_lo == p.up_lo ? p.up_lo : -INFINITY, u_hi = p.up_hi == p.up_hi ? p.up_hi : INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 64; ++c) {
-          float g[32], u[32];
-          tc_ld32(taddr + c * 64, g);
-          tc_ld32(taddr + c * 64 + 32, u);
-          const int n0 = n_tile * BLOCK_N + c * 64;
+#pragma unroll
+        for (int c = 0; c < kLd / 2; ++c) {
+          const int n0 = n_tile * BLOCK_N + half * kCW + c * 64;
           const int i0 = n0 >> 1;
           if (i0 >= p.I) continue;
+          float g[32], u[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { g[j] = __uint_as_float(raw[2 * c][j]); u[j] = __uint_as_float(raw[2 * c + 1][j]); }
           if (bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) { g[j] += bias[n0 + j]; u[j] += bias[n0 + 32 + j]; }
@@ -470,16 +483,14 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           aff = load_as_float(p.aff, p.aff_per_row ? static_cast<int64_t>(tok) : static_cast<int64_t>(tok) * p.E + e,
                               p.aff_dtype);
         const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.H_out : nullptr;
-#pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 32; ++c) {
-          float v[32];
-          tc_ld32(taddr + c * 32, v);
-          const int col0 = n_tile * BLOCK_N + c * 32;
+#pragma unroll
+        for (int l = 0; l < kLd; ++l) {
+          const int col0 = n_tile * BLOCK_N + half * kCW + l * 32;
           if (col0 >= p.H_out || !valid) continue;
           uint32_t o[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            float a0 = v[2 * j], a1 = v[2 * j + 1];
+            float a0 = __uint_as_float(raw[l][2 * j]), a1 = __uint_as_float(raw[l][2 * j + 1]);
             if (bias) { a0 += bias[col0 + 2 * j]; a1 += bias[col0 + 2 * j + 1]; }
             const __nv_bfloat162 b2 = __floats2bfloat162_rn(a0 * aff, a1 * aff);
             o[j] = *reinterpret_cast<const uint32_t*>(&b2);
@@ -489,10 +500,6 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
     }
   }
 
@@ -643,7 +650,7 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
   return B200MOE_OK;
 }
 
-int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128, 192 or 256)
+int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128 or 256)
 
 int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, int impl, cudaStream_t st) {
   B200MOE_REQUIRE(p.B > 0 && p.B % 128 == 0, B200MOE_ERR_INVALID, "block size must be a multiple of 128, got %d", p.B);
@@ -674,7 +681,6 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   rc = make_rows_map(&mb, b, K, p.n_total, p.E, bn);
   if (rc != B200MOE_OK) return rc;
   if (bn == 256) return epi == 0 ? launch_tc<256, 4, 0>(ma, mb, p, st) : launch_tc<256, 4, 1>(ma, mb, p, st);
-  if (bn == 192) return epi == 0 ? launch_tc<192, 5, 0>(ma, mb, p, st) : launch_tc<192, 5, 1>(ma, mb, p, st);
   return epi == 0 ? launch_tc<128, 6, 0>(ma, mb, p, st) : launch_tc<128, 6, 1>(ma, mb, p, st);
 }
 
@@ -684,8 +690,8 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
 using namespace b200moe;
 
 extern "C" int b200moe_set_gemm_tile_n(int block_n) {
-  B200MOE_REQUIRE(block_n == 128 || block_n == 192 || block_n == 256, B200MOE_ERR_INVALID,
-                  "tile width must be 128, 192 or 256, got %d", block_n);
+  B200MOE_REQUIRE(block_n == 128 || block_n == 256, B200MOE_ERR_INVALID, "tile width must be 128 or 256, got %d",
+                  block_n);
   g_block_n = block_n;
   return B200MOE_OK;
 }

@@ -93,6 +93,21 @@ class MoELayer:
             "b200moe_combine", _lib.ptr(ws.y_pos), _lib.ptr(self.inv), T, K, H, _lib.ptr(self.out), st))
         return self.out
 
+    def capture(self, hidden: torch.Tensor) -> None:
+        """Record one forward pass on ``hidden`` (a fixed device buffer) into a CUDA graph.
+
+        Call after at least one eager ``forward`` (kernel attributes are set on first use).
+        ``replay()`` then re-runs the whole launch sequence with one submission.
+        """
+        self._graph_input = hidden
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self.forward(hidden)
+
+    def replay(self) -> torch.Tensor:
+        self._graph.replay()
+        return self.out
+
     def device_status(self) -> list:
         """[grouping, gate/up contraction, down contraction] status words (0 = fine); synchronises."""
         return [int(self.gstatus.item())] + self.ws.status.cpu().tolist()[1:3]
@@ -123,3 +138,56 @@ def random_expert_weights(E: int, H: int, I: int, device, seed: int = 0, std: fl
                   _lib.ptr(w2_sf[e * sf2_e:]), None, st)
         torch.cuda.synchronize()
     return ExpertWeights(E, H, I, w1, w1_sf, w2, w2_sf, None, None, False)
+
+
+class HostPipeline:
+    """Feeds a captured :class:`MoELayer` from host memory with copies overlapped with compute.
+
+    ``submit(host_in, host_out)`` enqueues: pinned host -> device staging (copy stream), the layer (compute
+    stream, CUDA graph), device -> pinned host (second copy stream).  Two staging buffers each way let step
+    i + 1's upload and step i - 1's download run while step i computes.  ``drain()`` waits for everything.
+    """
+
+    def __init__(self, layer: MoELayer):
+        dev = layer.out.device
+        self.layer = layer
+        self.hidden = torch.empty((layer.T, layer.H), dtype=torch.bfloat16, device=dev)
+        layer.forward(self.hidden)  # make sure every kernel attribute is set before capture
+        torch.cuda.synchronize()
+        layer.capture(self.hidden)
+        self.stage_in = [torch.empty_like(self.hidden) for _ in range(2)]
+        self.stage_out = [torch.empty_like(layer.out) for _ in range(2)]
+        self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]        # upload i finished
+        self.ev_in_free = [torch.cuda.Event() for _ in range(2)]   # compute consumed staging i
+        self.ev_out = [torch.cuda.Event() for _ in range(2)]       # result i staged
+        self.ev_out_free = [torch.cuda.Event() for _ in range(2)]  # download i finished
+        self.step = 0
+
+    def submit(self, host_in: torch.Tensor, host_out: torch.Tensor) -> None:
+        i = self.step & 1
+        first = self.step < 2
+        cur = torch.cuda.current_stream()
+        with torch.cuda.stream(self.s_in):
+            if not first:
+                self.s_in.wait_event(self.ev_in_free[i])
+            self.stage_in[i].copy_(host_in, non_blocking=True)
+            self.ev_in[i].record(self.s_in)
+        cur.wait_event(self.ev_in[i])
+        self.hidden.copy_(self.stage_in[i], non_blocking=True)
+        self.ev_in_free[i].record(cur)
+        self.layer.replay()
+        if not first:
+            cur.wait_event(self.ev_out_free[i])
+        self.stage_out[i].copy_(self.layer.out, non_blocking=True)
+        self.ev_out[i].record(cur)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_out[i])
+            host_out.copy_(self.stage_out[i], non_blocking=True)
+            self.ev_out_free[i].record(self.s_out)
+        self.step += 1
+
+    def drain(self) -> None:
+        self.s_in.synchronize()
+        self.s_out.synchronize()
+        torch.cuda.current_stream().synchronize()
