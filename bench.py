@@ -111,6 +111,30 @@ def algorithmic_work(cfg):
     }
 
 
+def library_mxfp8_tflops(M, N, K):
+    """cuBLASLt's dense MXFP8 GEMM of the gate/up projection's shape, for context next to the roofline (or None)."""
+    import torch
+    try:
+        a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+        b = (torch.randn(N, K, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+
+        def sf(rows):
+            n = ((rows + 127) // 128) * ((K // 32 + 3) // 4) * 512
+            return torch.full((n,), 127, dtype=torch.uint8, device="cuda").view(torch.float8_e8m0fnu)
+        sa, sb = sf(M), sf(N)
+        for _ in range(3):
+            torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(10):
+            torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+        e.record()
+        torch.cuda.synchronize()
+        return 2.0 * M * N * K / (s.elapsed_time(e) / 10 * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
 def make_inputs(cfg, device, seed):
     import torch
     g = torch.Generator()
@@ -201,6 +225,9 @@ def run_ours(args, cfg, name):
     if args.tile_n:
         from nki_library_b200 import _lib
         _lib.call("b200moe_set_gemm_tile_n", args.tile_n)
+    if args.cta_pair >= 0:
+        from nki_library_b200 import _lib
+        _lib.call("b200moe_set_gemm_cta_pair", args.cta_pair)
 
     hidden_h, router_w, bias = make_inputs(cfg, dev, rank)
     hidden_pin = hidden_h.pin_memory()
@@ -285,11 +312,18 @@ def run_ours(args, cfg, name):
     barrier()
     ms_total = t_start.elapsed_time(t_end)
     # -------- the same steps again, eagerly, with CUDA events around every kernel (roofline input)
+    from nki_library_b200 import _lib as _l
+    probe = torch.zeros(4, dtype=torch.int64, device=dev)
+    _l.call("b200moe_set_clock_probe", _l.ptr(probe))
     timers = {}
     barrier()
     for _ in range(args.steps):
         forward(hidden_d, timers)
     barrier()
+    _l.call("b200moe_set_clock_probe", None)
+    pr = probe.cpu().tolist()
+    kernel_sm_mhz = {"gemm1_swiglu": round(1e3 * pr[0] / pr[1], 1) if pr[1] else None,
+                     "gemm2_scale": round(1e3 * pr[2] / pr[3], 1) if pr[3] else None}
     # -------- end-to-end leg: host buffers through the public layer call
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -343,7 +377,9 @@ def run_ours(args, cfg, name):
                         "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                         "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s); "
                                        "dense fp8/mxfp8 issues at twice the bf16 rate",
-                        "layer_tflops": work["layer_flops"] / (ms_step * 1e-3) / 1e12}
+                        "layer_tflops": work["layer_flops"] / (ms_step * 1e-3) / 1e12,
+                        "library_dense_mxfp8_tflops": library_mxfp8_tflops(min(T * K, 8192), 2 * I, H)
+                        if world == 1 else None}
         else:
             dom = "gemm1_swiglu"
             peak = peaks["hbm_gbs"]
@@ -365,6 +401,7 @@ def run_ours(args, cfg, name):
                        "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)" % (weights.nbytes() / 1e9)},
             "roofline": roofline,
             "kernel_ms": per_kernel,
+            "kernel_sm_mhz": kernel_sm_mhz,
             "cpu_baseline": {"value": cpu["value"], "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
                              "sample": cpu["sample"]},
             "e2e": {"value": world * T / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
@@ -388,6 +425,7 @@ def main():
     ap.add_argument("--workload", default="mixtral_prefill", choices=sorted(WORKLOADS))
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--cta-pair", type=int, default=-1, help="1/0: force the cta_group::2 GEMM on/off (-1 = default)")
     ap.add_argument("--tile-n", type=int, default=0, help="weight rows per GEMM tile (128/192/256; 0 = library default)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]

@@ -201,6 +201,13 @@ int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, con
 /* Weight rows per tile of the tensor-core kernel: 256 (default) or 128.  Tuning knob
  * with no counterpart in the reference. */
 int b200moe_set_gemm_tile_n(int block_n);
+/* Run the contractions on CTA pairs (tcgen05 cta_group::2, 256 positions x 256 weight rows per pair)
+ * whenever the block size is a multiple of 256 (default: on).  Tuning knob with no counterpart in the reference. */
+int b200moe_set_gemm_cta_pair(int enable);
+/* Diagnostic: with a non-NULL device buffer of four 64-bit words, CTA 0 of the gate/up contraction writes
+ * {SM cycles, nanoseconds} to words 0-1 and the down contraction to words 2-3, which gives the SM clock
+ * the kernel really ran at (cycles / ns).  NULL switches it off.  No counterpart in the reference. */
+int b200moe_set_clock_probe(void* device_words);
 
 /* combine = the accumulate-and-scatter tail of the block loop
  * (core/moe/moe_cte/bwmm_shard_on_block_mx.py:1303-1347): out[t,:] = sum over the

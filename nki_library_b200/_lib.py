@@ -16,7 +16,8 @@ from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libb200moe.so")
+# B200MOE_LIBRARY lets a caller point at another build of the same C ABI (A/B timing of kernel variants)
+LIB_PATH = os.environ.get("B200MOE_LIBRARY") or os.path.join(_PKG, "libb200moe.so")
 ERROR_PREFIX = "[INTERNAL_ERROR] [NCC_INKI016] Kernel validation exception: "
 
 F32, BF16, I32 = 0, 1, 2
@@ -58,6 +59,8 @@ SIGNATURES = {
                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                             c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_set_gemm_tile_n": (c_int, [c_int]),
+    "b200moe_set_gemm_cta_pair": (c_int, [c_int]),
+    "b200moe_set_clock_probe": (c_int, [c_void_p]),
     "b200moe_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
 }
 

@@ -4,9 +4,12 @@
 //   warp 0      TMA producer: per 128-byte K slab, a [128 x 128B] tile of the
 //               activation rows, a [BLOCK_N x 128B] tile of the expert's weight
 //               rows (both 128B-swizzled) and their UE8M0 scale atoms (bulk copies)
-//   warp 1      allocates TMEM and issues tcgen05.cp (scales -> TMEM) followed by
-//               four tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 each) per slab
-//   warps 2..9  epilogue: two warps per TMEM lane quadrant, each thread pulls half of
+//   warp 1      allocates TMEM and issues four tcgen05.mma.kind::mxf8f6f4.block_scale
+//               (K = 32 each) per slab
+//   warps 4..7  move each slab's UE8M0 scale atoms shared memory -> registers -> TMEM
+//               (tcgen05.st, one TMEM lane quadrant per warp, one TMEM slot per pipeline
+//               stage) so the tensor pipe never spends time on tcgen05.cp
+//   warps 8..15 epilogue: two warps per TMEM lane quadrant, each thread pulls half of
 //               its accumulator row into registers with tcgen05.ld, hands the TMEM
 //               buffer back to the MMA warp at once, then works from registers
 //               EPI 0: + bias, clamp, act(gate) * up, bf16 rounding, MXFP8
@@ -23,6 +26,8 @@
 // and tears down.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -32,7 +37,7 @@ constexpr int kBlockM = 128;
 constexpr int kBlockK = 128;  // bytes (= e4m3 elements) per pipeline slab
 constexpr int kGroupM = 16;
 constexpr int kMaxExperts = 512;
-constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
+constexpr int kThreads = 512;  // warp 0 producer, 1 MMA, 4-7 scale-factor movers, 8-15 epilogue (2, 3 idle)
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 struct GemmParams {
@@ -59,6 +64,9 @@ struct GemmParams {
   __nv_bfloat16* y_pos;
   int H_out;
   int32_t* status;
+  unsigned long long* clock_probe;  // optional: CTA 0 writes {SM cycles, nanoseconds} spent in the kernel
+  int experiment;  // timing experiments only (builds with -DB200MOE_EXPERIMENT): bit 0 no loads, 1 no MMA,
+                   // 2 no scale copies, 3 no epilogue math; results are meaningless when non-zero
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -123,6 +131,67 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                : "memory");
 }
 
+// ---- thread-block-pair (cta_group::2) variants --------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of `bar` in the even CTA of the pair (bit 24 of a shared::cluster address is the CTA rank).
+__device__ __forceinline__ uint32_t leader_bar(const uint64_t* bar) { return smem_u32(bar) & 0xFEFFFFFFu; }
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(0));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+// Same without a cluster-scope release: the caller has already waited for its TMEM stores
+// (tcgen05.wait::st + tcgen05.fence::before_thread_sync), and a release at cluster scope per slab
+// was measured to cost more than the slab's MMAs.
+__device__ __forceinline__ void mbar_arrive_leader_relaxed(uint64_t* bar) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(0));
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+__device__ __forceinline__ void tma2_load_2d(void* dst, const CUtensorMap* map, int x, int y, const uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(leader_bar(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, const uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(leader_bar(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tc2_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(mask)
+               : "memory");
+}
+__device__ __forceinline__ void tc2_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc2_mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -143,6 +212,16 @@ __device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint64_t a_desc, ui
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
+__device__ __forceinline__ void tc_st4(uint32_t taddr, const uint4& v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Asynchronous: the registers are valid only after tc_wait_ld().
 __device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
@@ -191,7 +270,8 @@ struct Sched {
   int total;                        // number of tiles to walk
 };
 
-__device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s) {
+// `mg` = position tiles per scheduling unit (1, or 2 when a CTA pair shares a weight tile).
+__device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s, int mg) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int sub = p.B >> 7;
   if (tid == 0) { s.n_active = p.n_blocks; s.contiguous = 1; }
@@ -216,16 +296,20 @@ __device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s) {
     int run = 0;
     for (int e = 0; e < p.E; ++e) {
       s.tile_start[e] = run;
-      run += s.mt_count[e] * p.n_tiles;
+      run += (s.mt_count[e] / mg) * p.n_tiles;
     }
     s.tile_start[p.E] = run;
-    s.total = s.contiguous ? run : p.m_tiles_total * p.n_tiles;
+    s.total = s.contiguous ? run : (p.m_tiles_total / mg) * p.n_tiles;
   }
   __syncthreads();
 }
 
-__device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s, int tile, int& m_tile, int& n_tile,
-                                            int& expert) {
+// m_tile is the first position tile of the unit; with mg == 2 the pair's CTAs take m_tile and m_tile + 1.
+// k_shift: the slab a tile starts its K loop at (always 0: starting the units that share a weight
+// tile at spread-out slabs was measured slower than letting their identical requests merge in L2).
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s, int tile, int mg, int& m_tile,
+                                            int& n_tile, int& expert, int& k_shift) {
+  k_shift = 0;
   if (s.contiguous) {
     int lo = 0, hi = p.E;
     while (hi - lo > 1) {
@@ -234,30 +318,35 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s,
     }
     expert = lo;
     const int local = tile - s.tile_start[lo];
-    const int cnt = s.mt_count[lo];
-    m_tile = s.mt_first[lo] + local % cnt;
+    const int cnt = s.mt_count[lo] / mg;
+    m_tile = s.mt_first[lo] + (local % cnt) * mg;
     n_tile = local / cnt;
   } else {
+    const int units = p.m_tiles_total / mg;
     const int per_group = kGroupM * p.n_tiles;
     const int g = tile / per_group;
     const int first_m = g * kGroupM;
-    const int gs = min(kGroupM, p.m_tiles_total - first_m);
+    const int gs = min(kGroupM, units - first_m);
     const int within = tile - g * per_group;
-    m_tile = first_m + within % gs;
+    m_tile = (first_m + within % gs) * mg;
     n_tile = within / gs;
     const int block = m_tile / (p.B >> 7);
     if (block >= s.n_active) return false;
     expert = p.block_to_expert[block];
     if (expert < 0 || expert >= p.E) return false;
   }
-  if (p.tile_flags != nullptr && p.tile_flags[m_tile] == 0) return false;
+  if (p.tile_flags != nullptr) {
+    int any = 0;
+    for (int i = 0; i < mg; ++i) any |= p.tile_flags[m_tile + i];
+    if (any == 0) return false;
+  }
   return true;
 }
 
-template <int BLOCK_N, int STAGES>
+template <int BLOCK_N, int STAGES, int CTAS = 1>
 struct SmemLayout {
   static constexpr int kA = kBlockM * kBlockK;
-  static constexpr int kB = BLOCK_N * kBlockK;
+  static constexpr int kB = (BLOCK_N / CTAS) * kBlockK;  // a CTA pair splits the weight rows
   static constexpr int kSfa = 512;
   static constexpr int kSfbAtoms = BLOCK_N > 128 ? 2 : 1;
   static constexpr int kSfb = kSfbAtoms * 512;
@@ -270,15 +359,20 @@ struct SmemLayout {
   static constexpr int kBytes = kOffSched + static_cast<int>(sizeof(Sched)) + 1024;  // + alignment slack
 };
 
-template <int BLOCK_N, int STAGES, int EPI>
+template <int BLOCK_N, int STAGES, int EPI, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                           const GemmParams p) {
-  using L = SmemLayout<BLOCK_N, STAGES>;
+  // CTAS == 2: the two CTAs of a cluster form one tcgen05 cta_group::2 unit.  Each loads its own 128
+  // activation rows and half of the weight tile; the even CTA issues M = 256 MMAs that read both CTAs'
+  // shared memory and write both CTAs' TMEM, so a weight byte crosses L2 -> SM once per 256 rows.
+  using L = SmemLayout<BLOCK_N, STAGES, CTAS>;
   constexpr int kAcc = (BLOCK_N <= 128) ? 2 : 1;
   constexpr int kSfCol = kAcc * BLOCK_N;  // TMEM columns: accumulators, then SFA (4), then SFB
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kIdesc = make_idesc(kBlockM, BLOCK_N);
+  constexpr uint32_t kIdesc = make_idesc(kBlockM * CTAS, BLOCK_N);
+  constexpr uint32_t kStageBytes = CTAS * (L::kA + L::kB);  // operand bytes per stage (scale atoms: sf_full)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -287,63 +381,102 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   uint64_t* empty = bars + STAGES;
   uint64_t* tmem_full = bars + 2 * STAGES;
   uint64_t* tmem_empty = bars + 2 * STAGES + kAcc;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * kAcc);
+  uint64_t* sf_full = bars + 2 * STAGES + 2 * kAcc;             // scale atoms of a stage landed (per CTA)
+  uint64_t* sf_ready = bars + 3 * STAGES + 2 * kAcc;            // ... and sit in their TMEM slot (pair leader)
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 4 * STAGES + 2 * kAcc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
   Sched& sched = *reinterpret_cast<Sched*>(smem + L::kOffSched);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  build_sched(p, sched);
+  long long probe_c0 = 0;
+  unsigned long long probe_t0 = 0;
+  if (p.clock_probe != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    probe_c0 = clock64();
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(probe_t0));
+  }
+  const int cta_rank = CTAS == 2 ? static_cast<int>(cluster_cta_rank()) : 0;
+  const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;
+  build_sched(p, sched, CTAS);
   const int total_tiles = sched.total;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+      mbar_init(&sf_full[s], 1);
+      mbar_init(&sf_ready[s], 4 * CTAS);
     }
     for (int a = 0; a < kAcc; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 8);
+      mbar_init(&tmem_empty[a], 8 * CTAS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (CTAS == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
 
+  // Register budget per warpgroup (4 warps): the epilogue warps hold 128 accumulator values per thread,
+  // everyone else needs few.  512 threads x 128 at launch = 2 x 128 x 64 + 2 x 128 x 192.
+  if (warp < 4) {
+    reg_dec<64>();
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer (one per CTA)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int m_tile, n_tile, e;
-        if (!decode_tile(p, sched, tile, m_tile, n_tile, e)) continue;
-        const uint8_t* sfa = p.a_sf + static_cast<int64_t>(m_tile) * p.k_blocks * 512;
-        const uint8_t* sfb = p.b_sf + static_cast<int64_t>(e) * p.b_sf_expert_stride;
+      for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
+        int m_tile, n_tile, e, k_shift;
+        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, k_shift)) continue;
+        m_tile += cta_rank;
+        const int atom0 = (n_tile * BLOCK_N) >> 7;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
-          const int atom0 = (n_tile * BLOCK_N) >> 7;
-          int n_sfb = 0;
+#ifdef B200MOE_EXPERIMENT
+          if (p.experiment & 1) {
+            if (cta_rank == 0) mbar_arrive(&full[stage]);
+            mbar_arrive(&sf_full[stage]);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
+#endif
+          // scale atoms of this CTA's rows and of the whole weight tile -> this CTA's own barrier
+          // (rows past the end of the atom table read as zero and still count their bytes)
+          mbar_expect_tx(&sf_full[stage], L::kSfa + L::kSfb);
+          tma_load_2d(smem + L::kOffSfa + stage * L::kSfa, &tmap_sfa, 0, m_tile * p.k_blocks + kb, &sf_full[stage]);
 #pragma unroll
           for (int j = 0; j < L::kSfbAtoms; ++j)
-            if (atom0 + j < p.b_row_atoms) ++n_sfb;
-          mbar_expect_tx(&full[stage], L::kA + L::kB + L::kSfa + n_sfb * 512);
-          tma_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
-          tma_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK, n_tile * BLOCK_N, e, &full[stage]);
-          bulk_load(smem + L::kOffSfa + stage * L::kSfa, sfa + static_cast<int64_t>(kb) * 512, 512, &full[stage]);
-          for (int j = 0; j < n_sfb; ++j)
-            bulk_load(smem + L::kOffSfb + stage * L::kSfb + j * 512,
-                      sfb + (static_cast<int64_t>(atom0 + j) * p.k_blocks + kb) * 512, 512, &full[stage]);
+            tma_load_2d(smem + L::kOffSfb + stage * L::kSfb + j * 512, &tmap_sfb, 0,
+                        (e * p.b_row_atoms + atom0 + j) * p.k_blocks + kb, &sf_full[stage]);
+          if constexpr (CTAS == 2) {
+            // operand tiles of both CTAs complete on the even CTA's barrier
+            if (cta_rank == 0) mbar_expect_tx(&full[stage], kStageBytes);
+            tma2_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
+            tma2_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK,
+                         n_tile * BLOCK_N + cta_rank * (BLOCK_N / 2), e, &full[stage]);
+          } else {
+            mbar_expect_tx(&full[stage], kStageBytes);
+            tma_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
+            tma_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK, n_tile * BLOCK_N, e, &full[stage]);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -353,47 +486,93 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (even CTA only when paired)
+    if (lane == 0 && cta_rank == 0) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int m_tile, n_tile, e;
-        if (!decode_tile(p, sched, tile, m_tile, n_tile, e)) continue;
+      for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
+        int m_tile, n_tile, e, k_shift;
+        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, k_shift)) continue;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-        const uint32_t sfa_tmem = tmem_base + kSfCol;
-        const uint32_t sfb_base = tmem_base + kSfCol + 4;
-        const uint32_t sfb_tmem = sfb_base + (((n_tile * BLOCK_N) & 127) >> 5);  // tile may start mid-atom
+        const uint32_t sfb_off = ((n_tile * BLOCK_N) & 127) >> 5;  // a tile may start mid-atom
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
+          if (!mbar_wait(&sf_ready[stage], phase, abort_flag, p.status, 5)) { ok = false; break; }
           tc_fence_after();
-          tc_cp_sf(sfa_tmem, desc_sf(smem_u32(smem + L::kOffSfa + stage * L::kSfa)));
-#pragma unroll
-          for (int j = 0; j < L::kSfbAtoms; ++j)
-            tc_cp_sf(sfb_base + 4 * j, desc_sf(smem_u32(smem + L::kOffSfb + stage * L::kSfb + j * 512)));
+          const uint32_t sfa_tmem = tmem_base + kSfCol + stage * 16;
+          const uint32_t sfb_tmem = sfa_tmem + 4 + sfb_off;
           const uint64_t a_desc = desc_sw128(smem_u32(smem + L::kOffA + stage * L::kA));
           const uint64_t b_desc = desc_sw128(smem_u32(smem + L::kOffB + stage * L::kB));
+#ifdef B200MOE_EXPERIMENT
+          if (!(p.experiment & 2))
+#endif
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t idesc = kIdesc | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
-            tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (CTAS == 2)
+              tc2_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
+            else
+              tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(&empty[stage]);
+          if constexpr (CTAS == 2) tc2_commit_pair(&empty[stage]);
+          else tc_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit(&tmem_full[acc]);
+        if (ok) {
+          if constexpr (CTAS == 2) tc2_commit_pair(&tmem_full[acc]);
+          else tc_commit(&tmem_full[acc]);
+        }
         if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
       }
     }
+  }
+  } else if (warp < 8) {
+    reg_dec<64>();
+    // ------------------------------------------------------------ scale-factor movers (one TMEM lane quadrant each)
+    // Lane l of a quadrant owns rows l, l+32, l+64, l+96 of every atom: the 16 bytes at l*16 are the four
+    // 32-bit TMEM cells (4 scale bytes each) the block-scaled MMA expects in that lane.
+    const int q = warp & 3;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
+      int m_tile, n_tile, e, k_shift;
+      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, k_shift)) continue;
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait(&sf_full[stage], phase, abort_flag, p.status, 6)) { ok = false; break; }
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kSfCol + stage * 16;
+#ifdef B200MOE_EXPERIMENT
+        if (!(p.experiment & 4))
+#endif
+        {
+          const uint4 va = *reinterpret_cast<const uint4*>(smem + L::kOffSfa + stage * L::kSfa + lane * 16);
+          tc_st4(taddr, va);
+#pragma unroll
+          for (int j = 0; j < L::kSfbAtoms; ++j) {
+            const uint4 vb = *reinterpret_cast<const uint4*>(smem + L::kOffSfb + stage * L::kSfb + j * 512 + lane * 16);
+            tc_st4(taddr + 4 + 4 * j, vb);
+          }
+          tc_wait_st();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CTAS == 2 && cta_rank != 0) mbar_arrive_leader_relaxed(&sf_ready[stage]);
+          else mbar_arrive(&sf_ready[stage]);
+        }
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
   } else {
-    // ------------------------------------------------------------ epilogue
+    reg_inc<192>();
+    // ------------------------------------------------------------ epilogue (every CTA drains its own TMEM)
     constexpr int kCW = BLOCK_N / 2;   // accumulator columns per thread
     constexpr int kLd = kCW / 32;      // 32-column TMEM loads per thread
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 8) >> 2;
     const int row_in_tile = q * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -401,9 +580,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                        (p.up_hi == p.up_hi);
     const float g_lo = p.gate_lo == p.gate_lo ? p.gate_lo : -INFINITY, g_hi = p.gate_hi == p.gate_hi ? p.gate_hi : INFINITY;
     const float u_lo = p.up_lo == p.up_lo ? p.up_lo : -INFINITY, u_hi = p.up_hi == p.up_hi ? p.up_hi : INFINITY;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      int m_tile, n_tile, e;
-      if (!decode_tile(p, sched, tile, m_tile, n_tile, e)) continue;
+    for (int tile = unit; tile < total_tiles; tile += n_units) {
+      int m_tile, n_tile, e, k_shift;
+      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, k_shift)) continue;
+      m_tile += cta_rank;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N + half * kCW;
@@ -415,8 +595,14 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       // the accumulator now lives in registers: give the TMEM buffer back before doing the math
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if (CTAS == 2 && cta_rank != 0) mbar_arrive_leader(&tmem_empty[acc]);
+        else mbar_arrive(&tmem_empty[acc]);
+      }
       if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
+#ifdef B200MOE_EXPERIMENT
+      if (p.experiment & 8) continue;
+#endif
 
       if constexpr (EPI == 0) {
         const int64_t k_atoms = (p.I + 127) >> 7;
@@ -505,9 +691,19 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 
   tc_fence_before();
   __syncthreads();
+  if (p.clock_probe != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    p.clock_probe[0] = static_cast<unsigned long long>(clock64() - probe_c0);
+    p.clock_probe[1] = t1 - probe_t0;
+  }
+  if constexpr (CTAS == 2) cluster_sync_all();  // the peer may still read this CTA's shared memory until here
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if constexpr (CTAS == 2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -634,23 +830,58 @@ int make_rows_map(CUtensorMap* map, const void* base, int64_t K, int64_t rows, i
   return B200MOE_OK;
 }
 
-template <int BLOCK_N, int STAGES, int EPI>
-int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
-  using L = SmemLayout<BLOCK_N, STAGES>;
-  auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI>;
+int make_atoms_map(CUtensorMap* map, const void* base, int64_t n_atoms) {
+  // scale atoms as rows of 128 32-bit words, one atom per TMA box
+  EncodeTiledFn enc = get_encode_fn();
+  B200MOE_REQUIRE(enc != nullptr, B200MOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(n_atoms)};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, 1};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200MOE_REQUIRE(r == CUDA_SUCCESS, B200MOE_ERR_CUDA, "cuTensorMapEncodeTiled (scale atoms) failed with code %d",
+                  static_cast<int>(r));
+  return B200MOE_OK;
+}
+
+template <int BLOCK_N, int STAGES, int EPI, int CTAS>
+int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa, const CUtensorMap& msb,
+              const GemmParams& p, cudaStream_t st) {
+  using L = SmemLayout<BLOCK_N, STAGES, CTAS>;
+  auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI, CTAS>;
   static bool attr_set = false;
   if (!attr_set) {
     B200MOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     attr_set = true;
   }
-  const int total = p.m_tiles_total * p.n_tiles;
-  const int grid = total < sm_count() ? total : sm_count();
-  kern<<<grid, kThreads, L::kBytes, st>>>(ma, mb, p);
+  const int total = (p.m_tiles_total / CTAS) * p.n_tiles;
+  int grid = (total < sm_count() / CTAS ? total : sm_count() / CTAS) * CTAS;
+  if constexpr (CTAS == 2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = L::kBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200MOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, msa, msb, p));
+  } else {
+    kern<<<grid, kThreads, L::kBytes, st>>>(ma, mb, msa, msb, p);
+  }
   B200MOE_LAUNCH_OK("grouped_mxfp8_gemm_kernel");
   return B200MOE_OK;
 }
 
 int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128 or 256)
+unsigned long long* g_clock_probe = nullptr;  // device buffer of 4 words: {cycles, ns} per projection
+int g_cta_pair = 1;   // 1: run 256-position x 256-row tiles on CTA pairs (cta_group::2) when blocks allow
 
 int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, int impl, cudaStream_t st) {
   B200MOE_REQUIRE(p.B > 0 && p.B % 128 == 0, B200MOE_ERR_INVALID, "block size must be a multiple of 128, got %d", p.B);
@@ -659,6 +890,10 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
                   "need at least one block and between 1 and %d experts", kMaxExperts);
   B200MOE_REQUIRE(p.status != nullptr, B200MOE_ERR_INVALID, "status pointer must not be null");
   p.m_tiles_total = p.n_blocks * (p.B / 128);
+  p.clock_probe = g_clock_probe ? g_clock_probe + 2 * epi : nullptr;
+#ifdef B200MOE_EXPERIMENT
+  if (const char* ev = getenv("B200MOE_EXPERIMENT")) p.experiment = atoi(ev);
+#endif
   p.k_blocks = (K + kBlockK - 1) / kBlockK;
   p.b_row_atoms = (p.n_total + 127) / 128;
   p.b_sf_expert_stride = static_cast<int64_t>(p.b_row_atoms) * p.k_blocks * 512;
@@ -675,19 +910,37 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   B200MOE_REQUIRE(K % 16 == 0, B200MOE_ERR_INVALID, "TMA needs row pitches that are multiples of 16 bytes");
   const int bn = g_block_n;
   p.n_tiles = (p.n_total + bn - 1) / bn;
-  CUtensorMap ma, mb;
+  const bool pair = g_cta_pair && bn == 256 && (p.B % 256 == 0) && (sm_count() % 2 == 0);
+  CUtensorMap ma, mb, msa, msb;
   int rc = make_rows_map(&ma, a, K, static_cast<int64_t>(p.m_tiles_total) * 128, 0, kBlockM);
   if (rc != B200MOE_OK) return rc;
-  rc = make_rows_map(&mb, b, K, p.n_total, p.E, bn);
+  rc = make_rows_map(&mb, b, K, p.n_total, p.E, pair ? bn / 2 : bn);
   if (rc != B200MOE_OK) return rc;
-  if (bn == 256) return epi == 0 ? launch_tc<256, 4, 0>(ma, mb, p, st) : launch_tc<256, 4, 1>(ma, mb, p, st);
-  return epi == 0 ? launch_tc<128, 6, 0>(ma, mb, p, st) : launch_tc<128, 6, 1>(ma, mb, p, st);
+  rc = make_atoms_map(&msa, p.a_sf, static_cast<int64_t>(p.m_tiles_total) * p.k_blocks);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_atoms_map(&msb, p.b_sf, static_cast<int64_t>(p.E) * p.b_row_atoms * p.k_blocks);
+  if (rc != B200MOE_OK) return rc;
+  if (pair)
+    return epi == 0 ? launch_tc<256, 6, 0, 2>(ma, mb, msa, msb, p, st) : launch_tc<256, 6, 1, 2>(ma, mb, msa, msb, p, st);
+  if (bn == 256)
+    return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb, msa, msb, p, st) : launch_tc<256, 4, 1, 1>(ma, mb, msa, msb, p, st);
+  return epi == 0 ? launch_tc<128, 6, 0, 1>(ma, mb, msa, msb, p, st) : launch_tc<128, 6, 1, 1>(ma, mb, msa, msb, p, st);
 }
 
 }  // namespace
 }  // namespace b200moe
 
 using namespace b200moe;
+
+extern "C" int b200moe_set_clock_probe(void* device_words) {
+  g_clock_probe = static_cast<unsigned long long*>(device_words);
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_set_gemm_cta_pair(int enable) {
+  g_cta_pair = enable ? 1 : 0;
+  return B200MOE_OK;
+}
 
 extern "C" int b200moe_set_gemm_tile_n(int block_n) {
   B200MOE_REQUIRE(block_n == 128 || block_n == 256, B200MOE_ERR_INVALID, "tile width must be 128 or 256, got %d",

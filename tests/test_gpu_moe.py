@@ -113,6 +113,34 @@ def test_moe_cte_c1_rows_weights(impl, variant):
     assert max_rel(out.float().cpu().numpy(), ref) <= TOL
 
 
+@pytest.mark.parametrize("B,T", [(256, 700), (512, 1500)])
+def test_moe_cte_cta_pair_mode(B, T):
+    """The cta_group::2 kernel (two CTAs share a weight tile) against the oracle and the single-CTA kernel."""
+    import nki_library_b200 as m
+    from nki_library_b200 import _lib
+    H, I, E, K = 512, 512, 4, 2
+    hidden, idx, aff, w_np, bgu, bd = _cte_case(T, H, I, E, K, B, 61, True, moe.SILU, None)
+    weights = _prep(m, w_np, bgu, bd)
+    N = m.get_n_blocks(T, K, E, B)
+    g = m.moe_group_tokens(torch.from_numpy(idx).cuda(), E, B, N, check=True)
+    args = (torch.from_numpy(hidden).to(torch.bfloat16).cuda(), torch.from_numpy(aff).cuda().reshape(-1, 1), weights,
+            None, g["token_position_to_id"], g["block_to_expert"], B,
+            m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx))
+    kw = dict(conditions=g["conditions"], skip_dma=m.SkipMode(True, False), _check_status=True)
+    _lib.call("b200moe_set_gemm_cta_pair", 0)
+    try:
+        single = m.moe_cte(*args, **kw)
+    finally:
+        _lib.call("b200moe_set_gemm_cta_pair", 1)
+    paired = m.moe_cte(*args, **kw)
+    paired2 = m.moe_cte(*args, **kw)
+    ref = _oracle_cte(hidden, aff, w_np, g["token_position_to_id"].cpu().numpy(), g["block_to_expert"].cpu().numpy(),
+                      g["conditions"].cpu().numpy(), B, bgu, bd, moe.SILU, None)
+    assert max_rel(paired.float().cpu().numpy(), ref) <= TOL
+    assert torch.equal(paired, paired2)
+    assert max_rel(paired.float().cpu().numpy(), single.float().cpu().numpy()) <= 1e-2
+
+
 @pytest.mark.parametrize("skip_token", [True, False])
 def test_moe_cte_reference_storage_layout(skip_token):
     """Weights in the reference's x4-packed storage, hidden in its logical order, pad id -1 or T."""
