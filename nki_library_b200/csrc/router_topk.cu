@@ -4,7 +4,7 @@
 // Two launches.  (1) A split-K bf16 tensor-core GEMM (mma.sync m16n8k16, fp32
 // accumulate): the grid is (token tiles) x (hidden-axis splits) so that even a
 // 64-token decode batch spreads over every SM; x and w slabs are staged through
-// shared memory with cp.async double buffering and each split writes its own
+// shared memory with a 2- or 3-deep cp.async ring and each split writes its own
 // partial-logit slab (no atomics, so the sum order is fixed).  (2) One warp per
 // token adds the partials in split order plus the bias, keeps E/32 logits per
 // lane and reduces a (value, lowest index) arg-max with shuffles K times.
@@ -13,7 +13,7 @@
 namespace b200moe {
 namespace {
 
-constexpr int kKC = 32;           // hidden slab per pipeline stage
+constexpr int kKC = 64;           // hidden slab per pipeline stage
 constexpr int kXPad = 8;          // halfs of padding per smem row (bank spread)
 constexpr int kMaxEPerLane = 16;  // E <= 512
 
@@ -23,6 +23,7 @@ struct LogitArgs {
   int x_is_TH, T, H, E;
   int mw, nw;        // warps along tokens / experts (mw * nw == 8)
   int h_per_split;   // multiple of kKC
+  int stages;        // cp.async ring depth (2 or 3)
   float* partial;    // [splits][T][E]
 };
 
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(256) router_logits_kernel(LogitArgs a) {
   const int x_rows = a.x_is_TH ? TM : kKC;
   const int w_stride = EN + kXPad;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* ws = xs + 2 * x_rows * x_stride;
+  __nv_bfloat16* ws = xs + a.stages * x_rows * x_stride;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp / a.nw, wn = warp % a.nw;
   const int t0 = blockIdx.x * TM;
@@ -125,15 +126,18 @@ __global__ void __launch_bounds__(256) router_logits_kernel(LogitArgs a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
 
-  if (n_chunks > 0) load_chunk(0, 0);
+  // ring of `stages` slabs; one commit group per loop step (possibly empty) keeps the wait count fixed
+  for (int c = 0; c < a.stages - 1; ++c) {
+    if (c < n_chunks) load_chunk(c, c);
+    else cp_async_commit();
+  }
   for (int ch = 0; ch < n_chunks; ++ch) {
-    const int buf = ch & 1;
-    if (ch + 1 < n_chunks) {
-      load_chunk(ch + 1, buf ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    const int buf = ch % a.stages;
+    const int nxt = ch + a.stages - 1;
+    if (nxt < n_chunks) load_chunk(nxt, nxt % a.stages);
+    else cp_async_commit();
+    if (a.stages == 3) cp_async_wait<2>();
+    else cp_async_wait<1>();
     __syncthreads();
     const __nv_bfloat16* xb = xs + buf * x_rows * x_stride;
     const __nv_bfloat16* wb = ws + buf * kKC * w_stride;
@@ -313,7 +317,7 @@ __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
 }
 
 struct RouterPlan {
-  int mw, nw, tm, splits, h_per_split;
+  int mw, nw, tm, splits, h_per_split, stages;
   size_t smem;
 };
 
@@ -335,7 +339,9 @@ RouterPlan plan_router(int T, int H, int E, int x_is_TH) {
   const int EN = 64 * p.nw;
   const int x_rows = x_is_TH ? p.tm : kKC;
   const int x_stride = x_is_TH ? (kKC + kXPad) : (p.tm + kXPad);
-  p.smem = sizeof(__nv_bfloat16) * (2 * static_cast<size_t>(x_rows) * x_stride + 2 * static_cast<size_t>(kKC) * (EN + kXPad));
+  const size_t per_stage = sizeof(__nv_bfloat16) * (static_cast<size_t>(x_rows) * x_stride + static_cast<size_t>(kKC) * (EN + kXPad));
+  p.stages = 3 * per_stage <= 160 * 1024 ? 3 : 2;
+  p.smem = p.stages * per_stage;
   return p;
 }
 
@@ -371,11 +377,11 @@ extern "C" int b200moe_router_topk(const void* x, int x_is_TH, const void* w, co
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   static bool attr_set = false;
   if (!attr_set) {
-    B200MOE_CUDA_OK(cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    B200MOE_CUDA_OK(cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024));
     attr_set = true;
   }
   LogitArgs la{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), x_is_TH, T, H, E,
-               p.mw, p.nw, p.h_per_split, static_cast<float*>(workspace)};
+               p.mw, p.nw, p.h_per_split, p.stages, static_cast<float*>(workspace)};
   dim3 grid((T + p.tm - 1) / p.tm, p.splits);
   router_logits_kernel<<<grid, 256, p.smem, st>>>(la);
   B200MOE_LAUNCH_OK("router_logits_kernel");
