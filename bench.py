@@ -36,6 +36,14 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
+# profiles/ (one capture per workload; null where none was taken).
+NCU_TRAFFIC_BYTES = {
+    "mixtral_prefill": 1.906486e9 + 137.900544e6,
+    "mixtral_decode": 976.613888e6 + 18.093824e6,
+}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -374,7 +382,8 @@ def run_ours(args, cfg, name):
             peak = 2.0 * peaks["bf16_tflops"]
             achieved = work["gemm1_flops"] / (per_kernel[dom] * 1e-3) / 1e12
             roofline = {"bound": "tensor", "kernel": "grouped_mxfp8_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
-                        "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                        "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                        "traffic": NCU_TRAFFIC_BYTES.get(name) if world == 1 else None,
                         "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s); "
                                        "dense fp8/mxfp8 issues at twice the bf16 rate",
                         "layer_tflops": work["layer_flops"] / (ms_step * 1e-3) / 1e12,
@@ -385,7 +394,8 @@ def run_ours(args, cfg, name):
             peak = peaks["hbm_gbs"]
             achieved = work["gemm1_weight_bytes"] / (per_kernel[dom] * 1e-3) / 1e9
             roofline = {"bound": "hbm", "kernel": "grouped_mxfp8_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
-                        "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                        "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                        "traffic": NCU_TRAFFIC_BYTES.get(name) if world == 1 else None,
                         "peak_source": f"{peaks['source']} copy bandwidth",
                         "layer_gbs": work["decode_bytes"] / (ms_step * 1e-3) / 1e9}
         cpu = (dict(value=None, sample="skipped (--skip-cpu)") if args.skip_cpu
