@@ -187,6 +187,8 @@ struct RankArgs {
   int aff_dtype;
 };
 
+// NPL = experts per lane (E <= 32 * NPL); instantiated for 1, 2, 4, 8, 16 so small expert counts do not pay for 512.
+template <int NPL>
 __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -194,10 +196,10 @@ __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
   const int E = a.E;
   const int n_per_lane = (E + 31) / 32;
 
-  float v[kMaxEPerLane];
+  float v[NPL];
   float row_max = -INFINITY;
 #pragma unroll
-  for (int j = 0; j < kMaxEPerLane; ++j) {
+  for (int j = 0; j < NPL; ++j) {
     const int e = lane + 32 * j;
     float s = -INFINITY;
     if (j < n_per_lane && e < E) {
@@ -213,12 +215,12 @@ __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
   for (int o = 16; o > 0; o >>= 1) row_max = fmaxf(row_max, __shfl_xor_sync(0xffffffffu, row_max, o));
 
   // activation over the full row (pre-norm pipelines)
-  float full[kMaxEPerLane];
+  float full[NPL];
   if (a.pre_norm) {
     if (a.act == B200MOE_ROUTER_SOFTMAX) {
       float s = 0.f;
 #pragma unroll
-      for (int j = 0; j < kMaxEPerLane; ++j) {
+      for (int j = 0; j < NPL; ++j) {
         full[j] = (v[j] == -INFINITY) ? 0.f : expf(v[j] - row_max);
         s += full[j];
       }
@@ -226,10 +228,10 @@ __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
       const float inv = 1.0f / s;
 #pragma unroll
-      for (int j = 0; j < kMaxEPerLane; ++j) full[j] *= inv;
+      for (int j = 0; j < NPL; ++j) full[j] *= inv;
     } else {
 #pragma unroll
-      for (int j = 0; j < kMaxEPerLane; ++j) full[j] = 1.0f / (1.0f + expf(-v[j]));
+      for (int j = 0; j < NPL; ++j) full[j] = 1.0f / (1.0f + expf(-v[j]));
     }
   }
 
@@ -244,7 +246,7 @@ __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
     float bv = -INFINITY;
     int be = 0x7fffffff;
 #pragma unroll
-    for (int j = 0; j < kMaxEPerLane; ++j) {
+    for (int j = 0; j < NPL; ++j) {
       const int e = lane + 32 * j;
       if (j < n_per_lane && e < E && !((taken >> j) & 1u)) {
         if (v[j] > bv || (v[j] == bv && e < be)) { bv = v[j]; be = e; }
@@ -262,7 +264,7 @@ __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
       taken |= 1u << (be >> 5);
       if (a.pre_norm) {
 #pragma unroll
-        for (int j = 0; j < kMaxEPerLane; ++j)
+        for (int j = 0; j < NPL; ++j)
           if (j == (be >> 5)) sel_a = full[j];
       }
     }
@@ -283,7 +285,7 @@ __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
 
   if (a.pre_norm && !a.l1) {
 #pragma unroll
-    for (int j = 0; j < kMaxEPerLane; ++j) {
+    for (int j = 0; j < NPL; ++j) {
       const int e = lane + 32 * j;
       if (j < n_per_lane && e < E) store_from_float(a.aff_out, static_cast<int64_t>(t) * E + e, a.aff_dtype, full[j]);
     }
@@ -304,7 +306,7 @@ __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
   }
   const bool normalise = a.pre_norm || a.act == B200MOE_ROUTER_SOFTMAX;
 #pragma unroll
-  for (int j = 0; j < kMaxEPerLane; ++j) {
+  for (int j = 0; j < NPL; ++j) {
     const int e = lane + 32 * j;
     if (j < n_per_lane && e < E) {
       float out = 0.f;
@@ -388,7 +390,12 @@ extern "C" int b200moe_router_topk(const void* x, int x_is_TH, const void* w, co
   RankArgs ra{static_cast<const float*>(workspace), p.splits, static_cast<const __nv_bfloat16*>(w_bias), T, E, k,
               act_fn, router_pre_norm, norm_topk_prob, router_logits, logits_dtype, expert_index, expert_affinities,
               aff_dtype};
-  router_rank_kernel<<<(T + 7) / 8, 256, 0, st>>>(ra);
+  const dim3 rgrid((T + 7) / 8);
+  if (E <= 32) router_rank_kernel<1><<<rgrid, 256, 0, st>>>(ra);
+  else if (E <= 64) router_rank_kernel<2><<<rgrid, 256, 0, st>>>(ra);
+  else if (E <= 128) router_rank_kernel<4><<<rgrid, 256, 0, st>>>(ra);
+  else if (E <= 256) router_rank_kernel<8><<<rgrid, 256, 0, st>>>(ra);
+  else router_rank_kernel<16><<<rgrid, 256, 0, st>>>(ra);
   B200MOE_LAUNCH_OK("router_rank_kernel");
   return B200MOE_OK;
 }

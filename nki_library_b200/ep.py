@@ -40,10 +40,9 @@ def dispatch_plan(counts: torch.Tensor, recv_counts: torch.Tensor, world: int, e
     [world, E_L]``: rows each source rank sends to each of this rank's experts.
     Rows arrive source-major and, inside a source, in expert order.
     """
-    send = counts.view(world, experts_local).sum(dim=1)
-    recv = recv_counts.sum(dim=1)
-    in_splits = [int(v) for v in send.tolist()]
-    out_splits = [int(v) for v in recv.tolist()]
+    both = torch.stack([counts.view(world, experts_local).sum(dim=1), recv_counts.sum(dim=1)]).tolist()  # one sync
+    in_splits = [int(v) for v in both[0]]
+    out_splits = [int(v) for v in both[1]]
     local_ids = torch.arange(experts_local, dtype=torch.int32, device=recv_counts.device).repeat(world)
     row_expert = torch.repeat_interleave(local_ids, recv_counts.reshape(-1).to(torch.int64),
                                          output_size=sum(out_splits))
