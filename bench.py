@@ -258,29 +258,41 @@ def run_ours(args, cfg, name):
     else:
         # Expert parallelism: every rank keeps its own T tokens (weak scaling) and E / world experts;
         # token rows travel to the owning rank and back through NCCL all-to-all.
-        from nki_library_b200.ep import CudaOps, ExpertParallelMoE
+        from nki_library_b200.ep import CudaOps, ExpertParallelMoE, PeerExpertParallelMoE
         if E % world != 0:
             raise SystemExit(f"workload has {E} experts, not divisible by {world} ranks")
         weights = random_expert_weights(E // world, H, I, dev, seed=7 + rank)
-        ops = CudaOps(router_w.to(dev), weights, E, K, B, bias_d)
-        ep = ExpertParallelMoE(ops, E)
         n_blocks = None
+        if args.ep_backend == "peer":
+            # dispatch / combine by this library's own kernels storing into peer GPUs' memory (NVLink)
+            layer = PeerExpertParallelMoE(router_w.to(dev), weights, E, K, B, T, router_bias=bias_d,
+                                          capacity_factor=args.capacity_factor)
 
-        def forward(h, timers=None):
-            ops.timers = timers
-            return ep.forward(h)
+            def forward(h, timers=None):
+                layer.timers = timers
+                return layer.forward(h)
 
-        def device_status():
-            return pipeline_status()
+            def device_status():
+                return layer.device_status()
 
-        def pipeline_status():
-            from nki_library_b200 import pipeline
-            return [int(v) for ws in pipeline._workspaces.values() for v in ws.status.cpu().tolist()[1:3]]
+            def launches_per_step():
+                return layer.kernels_per_forward
+        else:
+            ops = CudaOps(router_w.to(dev), weights, E, K, B, bias_d)
+            ep = ExpertParallelMoE(ops, E)
 
-        _count = {"n": 0}
+            def forward(h, timers=None):
+                ops.timers = timers
+                return ep.forward(h)
 
-        def launches_per_step():
-            return _count["n"]
+            def device_status():
+                from nki_library_b200 import pipeline
+                return [int(v) for ws in pipeline._workspaces.values() for v in ws.status.cpu().tolist()[1:3]]
+
+            _count = {"n": 0}
+
+            def launches_per_step():
+                return _count["n"]
 
     def barrier():
         if world > 1:
@@ -290,7 +302,7 @@ def run_ours(args, cfg, name):
     for _ in range(max(args.warmup, 3)):
         forward(hidden_d)
     barrier()
-    if world > 1:
+    if world > 1 and args.ep_backend != "peer":
         ops.launches = 0
         forward(hidden_d)
         _count["n"] = ops.launches
@@ -304,7 +316,7 @@ def run_ours(args, cfg, name):
         sampler.start()
         time.sleep(0.2)
     # -------- resident-input leg (value): the captured launch sequence (single GPU) or eager steps (EP)
-    use_graph = world == 1 and not args.no_graph
+    use_graph = (world == 1 or args.ep_backend == "peer") and not args.no_graph
     if use_graph:
         layer.capture(hidden_d)
         layer.replay()
@@ -332,6 +344,15 @@ def run_ours(args, cfg, name):
     pr = probe.cpu().tolist()
     kernel_sm_mhz = {"gemm1_swiglu": round(1e3 * pr[0] / pr[1], 1) if pr[1] else None,
                      "gemm2_scale": round(1e3 * pr[2] / pr[3], 1) if pr[3] else None}
+    if world == 1:
+        per_kernel = {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in timers.items()}
+    else:
+        n = len(timers["t0"])
+        names = ("dispatch" if args.ep_backend == "peer" else "gather_quantize", "gemm1_swiglu", "gemm2_scale")
+        per_kernel = {nm: sum(timers[f"t{i}"][j].elapsed_time(timers[f"t{i + 1}"][j]) for j in range(n)) / n
+                      for i, nm in enumerate(names)}
+    forward(hidden_d)  # drops the event hooks again
+    barrier()
     # -------- end-to-end leg: host buffers through the public layer call
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -369,13 +390,6 @@ def run_ours(args, cfg, name):
 
     if rank == 0:
         work = algorithmic_work(cfg)
-        if world == 1:
-            per_kernel = {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in timers.items()}
-        else:
-            n = len(timers["t0"])
-            names = ("gather_quantize", "gemm1_swiglu", "gemm2_scale")
-            per_kernel = {nm: sum(timers[f"t{i}"][j].elapsed_time(timers[f"t{i + 1}"][j]) for j in range(n)) / n
-                          for i, nm in enumerate(names)}
         ms_step = ms_total / args.steps
         if cfg["kind"] == "prefill":
             dom = "gemm1_swiglu"
@@ -407,7 +421,9 @@ def run_ours(args, cfg, name):
             "data": "synthetic",
             "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}, "n_blocks": n_blocks,
                        "tokens_per_gpu": T, "experts_per_gpu": E // world,
-                       "parallelism": f"ep{world} (NCCL all-to-all dispatch/combine)" if world > 1 else "single",
+                       "parallelism": "single" if world == 1 else
+                       (f"ep{world} (peer-memory dispatch/combine kernels over NVLink)" if args.ep_backend == "peer"
+                        else f"ep{world} (NCCL all-to-all dispatch/combine)"),
                        "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)" % (weights.nbytes() / 1e9)},
             "roofline": roofline,
             "kernel_ms": per_kernel,
@@ -434,6 +450,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mixtral_prefill", choices=sorted(WORKLOADS))
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    ap.add_argument("--ep-backend", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel exchange for --gpus > 1: peer-memory kernels (default) or NCCL all-to-all")
+    ap.add_argument("--capacity-factor", type=float, default=2.5,
+                    help="receive-buffer size of the peer-memory exchange, in multiples of a rank's fair share")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cta-pair", type=int, default=-1, help="1/0: force the cta_group::2 GEMM on/off (-1 = default)")
     ap.add_argument("--tile-n", type=int, default=0, help="weight rows per GEMM tile (128/192/256; 0 = library default)")

@@ -2,7 +2,7 @@
  * b200moe.h -- C ABI of the B200 (sm_100a) MoE expert hot path.
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream, never
- * allocates or frees user-visible memory, never synchronises the stream, and
+ * allocates or frees device memory, never synchronises the stream, and
  * returns 0 on success or a negative B200MOE_ERR_* code (details through
  * b200moe_last_error()).  Scratch memory is supplied by the caller; its size
  * comes from the matching *_workspace_bytes query.
@@ -215,6 +215,41 @@ int b200moe_set_clock_probe(void* device_words);
  * one bf16 rounding.  table is inverse_map [T,K] or a position table [T,E]. */
 int b200moe_combine(const void* y_pos_bf16, const int32_t* table, int T, int n_cand, int H, void* out_bf16,
                     b200moe_stream_t stream);
+
+/* ---- expert parallelism over peer memory -------------------------------------------------------
+ * One process per GPU.  The reference's expert-parallel mode slices experts by rank_id
+ * (core/moe/moe_tkg/moe_tkg.py:100-101) and leaves the token exchange to an external all_to_all_v
+ * (experimental/collectives/topk_reduce.py:15); these entry points are that exchange, done by kernels
+ * that store straight into the peer GPUs' buffers (NVLink), with no host synchronisation.
+ *
+ * b200moe_ipc_export / _open / _close share a device buffer between the ranks' processes with CUDA IPC
+ * (64-byte handle + byte offset inside the exported allocation).  Peer tables passed below are host
+ * arrays of `world` device pointers, entry r = that buffer on rank r (own rank: the local pointer).
+ * Flag tables are int32 [4][8], zero-initialised; epoch_dev is a zero-initialised device int32 that
+ * exchange_counts bumps once per step (so a recorded CUDA graph of a step can be replayed).
+ *
+ * Step order on every rank's stream: exchange_counts -> dispatch_quantize -> signal_wait(slot 1) ->
+ * plan -> grouped_gemm1 / grouped_gemm2 (token_position_to_id = row_valid, hidden_rows = cap_rows,
+ * per-row affinities) -> return_rows -> signal_wait(slot 2) -> combine.  A wait that runs out
+ * (about two seconds) or a receive buffer that is too small sets *status non-zero. */
+int b200moe_ipc_export(const void* dev_ptr, void* handle_out_64, int64_t* offset_out);
+int b200moe_ipc_open(const void* handle_64, int64_t offset, void** dev_ptr_out);
+int b200moe_ipc_close(void* dev_ptr, int64_t offset);
+int b200moe_ep_exchange_counts(const int32_t* counts, void* const* count_tables, void* const* flag_tables, int rank,
+                               int world, int E, int32_t* epoch_dev, int32_t* status, b200moe_stream_t stream);
+int b200moe_ep_signal_wait(void* const* flag_tables, int rank, int world, int slot, const int32_t* epoch_dev,
+                           int32_t* status, b200moe_stream_t stream);
+int b200moe_ep_plan(const int32_t* counts_all, int rank, int world, int E, int B, int n_blocks_cap,
+                    int32_t* block_to_expert, int32_t* conditions, int32_t* row_valid, int32_t* tile_flags,
+                    int32_t* status, b200moe_stream_t stream);
+int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32_t* pair_token, const int32_t* pair_expert,
+                                 const float* affinities, const int32_t* counts_all, int T, int K, int H, int E, int B,
+                                 int rank, int world, int h_packed_order, void* const* xq_peers, void* const* sf_peers,
+                                 void* const* aff_peers, void* const* src_peers, int64_t cap_rows,
+                                 b200moe_stream_t stream);
+int b200moe_ep_return_rows(const void* y_pos_bf16, const int32_t* row_valid, const int32_t* row_src,
+                           void* const* back_peers, int world, int64_t cap_rows, int H, int64_t back_rows,
+                           b200moe_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -62,6 +62,19 @@ SIGNATURES = {
     "b200moe_set_gemm_cta_pair": (c_int, [c_int]),
     "b200moe_set_clock_probe": (c_int, [c_void_p]),
     "b200moe_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200moe_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "b200moe_ipc_open": (c_int, [c_void_p, c_int64, c_void_p]),
+    "b200moe_ipc_close": (c_int, [c_void_p, c_int64]),
+    "b200moe_ep_exchange_counts": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                           c_void_p]),
+    "b200moe_ep_signal_wait": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p]),
+    "b200moe_ep_dispatch_quantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_int64, c_void_p]),
+    "b200moe_ep_return_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int64,
+                                       c_void_p]),
 }
 
 _lib = None

@@ -155,3 +155,193 @@ class ExpertParallelMoE:
         back = torch.empty_like(send)
         dist.all_to_all_single(back, y, in_splits, out_splits, group=self.group)
         return ops.combine(back, inv)
+
+
+# --------------------------------------------------------------------------------------------------
+# Peer-memory expert parallelism: the exchange is done by this library's own kernels, which store
+# straight into the other GPUs' buffers over NVLink.  No collective call and no host synchronisation
+# happens inside a step; torch.distributed is only used once, to hand the CUDA IPC handles around.
+# --------------------------------------------------------------------------------------------------
+import ctypes  # noqa: E402
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class PeerArena:
+    """One zero-initialised device allocation per rank, carved into named views and shared with every peer."""
+
+    def __init__(self, layout: dict, device, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.offsets, off = {}, 0
+        for name, (nbytes, _dtype) in layout.items():
+            self.offsets[name] = off
+            off += _align(nbytes)
+        self.arena = torch.zeros(max(off, 1 << 21), dtype=torch.uint8, device=device)
+        self.views = {name: self.arena[self.offsets[name]:self.offsets[name] + nbytes].view(dtype)
+                      for name, (nbytes, dtype) in layout.items()}
+        lib = _lib.load_library()
+        handle = ctypes.create_string_buffer(64)
+        offset = ctypes.c_int64(0)
+        _lib.call("b200moe_ipc_export", _lib.ptr(self.arena), handle, ctypes.byref(offset))
+        mine = (bytes(handle.raw), int(offset.value))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self.bases = []
+        for r, (h, o) in enumerate(everyone):
+            if r == self.rank:
+                self.bases.append(self.arena.data_ptr())
+            else:
+                out = ctypes.c_void_p(0)
+                _lib.call("b200moe_ipc_open", ctypes.create_string_buffer(h, 64), o, ctypes.byref(out))
+                self.bases.append(int(out.value))
+        del lib
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def peers(self, name: str):
+        """Host array of ``world`` device pointers: view ``name`` on every rank."""
+        arr = (ctypes.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.bases[r] + self.offsets[name]
+        return arr
+
+
+class PeerExpertParallelMoE:
+    """Expert-parallel MoE layer whose dispatch and combine are peer-memory kernels (see ``csrc/ep.cu``).
+
+    Each rank's receive buffers hold ``capacity_factor`` times its fair share of (token, k) pairs; if the routing
+    sends it more than that, ``device_status()[0]`` becomes 21 and the surplus rows are dropped.
+    """
+
+    def __init__(self, router_w, weights: ExpertWeights, num_experts: int, top_k: int, block_size: int,
+                 tokens_per_rank: int, group=None, router_bias=None, capacity_factor: float = 2.5,
+                 router_act=RouterActFnType.SOFTMAX, router_pre_norm=True, norm_topk_prob=True,
+                 act_fn=ActFnType.SiLU):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        _lib.kernel_assert(num_experts % self.world == 0,
+                           f"num_experts ({num_experts}) must be divisible by the number of ranks ({self.world})")
+        _lib.kernel_assert(self.world <= 8, "peer-memory expert parallelism supports at most 8 ranks")
+        self.ops = CudaOps(router_w, weights, num_experts, top_k, block_size, router_bias, router_act, router_pre_norm,
+                           norm_topk_prob, act_fn)
+        self.E, self.E_L, self.K, self.B = num_experts, num_experts // self.world, top_k, block_size
+        self.T, self.H, self.I = tokens_per_rank, weights.H, weights.I
+        _lib.kernel_assert(weights.E == self.E_L, "weights must hold this rank's experts only")
+        dev = router_w.device
+        lib = _lib.load_library()
+        pairs = self.T * self.K
+        self.n_blocks_cap = get_n_blocks(int(capacity_factor * pairs) + 1, 1, self.E_L, self.B)
+        self.cap_rows = self.n_blocks_cap * self.B
+        layout = {
+            "flags": (4 * 8 * 4, torch.int32),
+            "counts": (self.world * self.E * 4, torch.int32),
+            "row_aff": (self.cap_rows * 4, torch.float32),
+            "row_src": (self.cap_rows * 4, torch.int32),
+            "sf": (lib.b200moe_sf_bytes(self.cap_rows, self.H), torch.uint8),
+            "xq": (self.cap_rows * self.H, torch.uint8),
+            "back": (pairs * self.H * 2, torch.bfloat16),
+        }
+        self.mem = PeerArena(layout, dev, group)
+        v = self.mem.views
+        self.counts_all, self.row_aff, self.row_src = v["counts"], v["row_aff"], v["row_src"]
+        self.xq, self.sf, self.back = v["xq"], v["sf"], v["back"].view(pairs, self.H)
+        self.p_flags, self.p_counts = self.mem.peers("flags"), self.mem.peers("counts")
+        self.p_xq, self.p_sf = self.mem.peers("xq"), self.mem.peers("sf")
+        self.p_aff, self.p_src, self.p_back = self.mem.peers("row_aff"), self.mem.peers("row_src"), self.mem.peers("back")
+        # receiver-side plan and scratch (local)
+        self.b2e = torch.zeros(self.n_blocks_cap, dtype=torch.int32, device=dev)
+        self.cond = torch.zeros(self.n_blocks_cap + 2, dtype=torch.int32, device=dev)
+        self.row_valid = torch.full((self.cap_rows,), -1, dtype=torch.int32, device=dev)
+        self.tile_flags = torch.zeros(self.cap_rows // 128, dtype=torch.int32, device=dev)
+        self.mq = torch.empty((self.cap_rows, self.I), dtype=torch.uint8, device=dev)
+        self.m_sf = torch.zeros(lib.b200moe_sf_bytes(self.cap_rows, self.I), dtype=torch.uint8, device=dev)
+        self.y_pos = torch.empty((self.cap_rows, self.H), dtype=torch.bfloat16, device=dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.out = torch.empty((self.T, self.H), dtype=torch.bfloat16, device=dev)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        # routing / pair-sort buffers (fixed shapes, so a step is a fixed launch sequence)
+        self.aff = torch.empty((self.T, self.E), dtype=torch.float32, device=dev)
+        self.idx = torch.empty((self.T, self.K), dtype=torch.int32, device=dev)
+        self.rws = torch.empty(lib.b200moe_router_workspace_bytes(self.T, self.H, self.E), dtype=torch.uint8, device=dev)
+        self.pair_token = torch.empty(pairs, dtype=torch.int32, device=dev)
+        self.pair_expert = torch.empty(pairs, dtype=torch.int32, device=dev)
+        self.pair_cond = torch.empty(pairs + 2, dtype=torch.int32, device=dev)
+        self.counts = torch.empty(self.E, dtype=torch.int32, device=dev)
+        self.inv = torch.empty((self.T, self.K), dtype=torch.int32, device=dev)
+        self.gstatus = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.gws = torch.empty(lib.b200moe_group_tokens_workspace_bytes(self.T, self.E), dtype=torch.uint8, device=dev)
+        self.timers = None
+        self.kernels_per_forward = 2 + 3 + 1 + 1 + 1 + 1 + 2 + 1 + 1 + 1
+        self._graph = None
+
+    def forward(self, hidden: torch.Tensor) -> torch.Tensor:
+        """``hidden [tokens_per_rank, H]`` bf16 -> bf16 ``[tokens_per_rank, H]`` (this rank's tokens).
+
+        Fourteen launches of this library's kernels on the current stream, nothing else: no allocation, no
+        collective call, no host synchronisation.  Every rank of the group must call it the same number of times.
+        """
+        _lib.kernel_assert(tuple(hidden.shape) == (self.T, self.H) and hidden.dtype == torch.bfloat16,
+                           "hidden must be bf16 [tokens_per_rank, H]")
+        ops, w, st = self.ops, self.ops.weights, _lib.stream_ptr()
+        G, E, E_L, K, B, H, I, T = self.world, self.E, self.E_L, self.K, self.B, self.H, self.I, self.T
+        status, epoch = _lib.ptr(self.status), _lib.ptr(self.epoch)
+        nan = float("nan")
+
+        def mark(name):
+            if self.timers is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                self.timers.setdefault(name, []).append(ev)
+
+        _lib.call("b200moe_router_topk", _lib.ptr(hidden), 1, _lib.ptr(ops.w), _lib.ptr(ops.bias), T, H, E, K,
+                  ops.router_act.value, int(ops.pre_norm), int(ops.l1), None, _lib.F32, _lib.ptr(self.idx),
+                  _lib.ptr(self.aff), _lib.F32, _lib.ptr(self.rws), self.rws.numel(), st)
+        # block size 1 turns the grouping kernel into "sort the (token, k) pairs by expert, stable in the token id"
+        _lib.call("b200moe_group_tokens", _lib.ptr(self.idx), _lib.ROUTING_INDEX, _lib.I32, T, E, K, 1, T * K, 1, 1,
+                  _lib.ptr(self.pair_token), _lib.ptr(self.pair_expert), _lib.ptr(self.pair_cond), _lib.ptr(self.counts),
+                  _lib.ptr(self.inv), _lib.ptr(self.gstatus), _lib.ptr(self.gws), self.gws.numel(), st)
+        _lib.call("b200moe_ep_exchange_counts", _lib.ptr(self.counts), self.p_counts, self.p_flags, self.rank, G, E,
+                  epoch, status, st)
+        mark("t0")
+        _lib.call("b200moe_ep_dispatch_quantize", _lib.ptr(hidden), _lib.ptr(self.pair_token), _lib.ptr(self.pair_expert),
+                  _lib.ptr(self.aff), _lib.ptr(self.counts_all), T, K, H, E, B, self.rank, G, int(w.h_packed_order),
+                  self.p_xq, self.p_sf, self.p_aff, self.p_src, self.cap_rows, st)
+        _lib.call("b200moe_ep_signal_wait", self.p_flags, self.rank, G, 1, epoch, status, st)
+        _lib.call("b200moe_ep_plan", _lib.ptr(self.counts_all), self.rank, G, E, B, self.n_blocks_cap,
+                  _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(self.row_valid), _lib.ptr(self.tile_flags),
+                  status, st)
+        mark("t1")
+        _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(self.xq), _lib.ptr(self.sf), _lib.ptr(w.w1),
+                  _lib.ptr(w.w1_sf), _lib.ptr(w.bias_gu), _lib.ptr(self.b2e), _lib.ptr(self.cond),
+                  _lib.ptr(self.tile_flags), self.n_blocks_cap, B, E_L, H, I, ops.act_fn.value, nan, nan, nan, nan,
+                  _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(self.status[1:]), 0, st)
+        mark("t2")
+        _lib.call("b200moe_grouped_gemm2_scale", _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(w.w2),
+                  _lib.ptr(w.w2_sf), _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond),
+                  _lib.ptr(self.tile_flags), _lib.ptr(self.row_valid), self.cap_rows, self.n_blocks_cap, B, E_L, H, I,
+                  _lib.ptr(self.row_aff), _lib.F32, 1, _lib.ptr(self.y_pos), _lib.ptr(self.status[2:]), 0, st)
+        mark("t3")
+        _lib.call("b200moe_ep_return_rows", _lib.ptr(self.y_pos), _lib.ptr(self.row_valid), _lib.ptr(self.row_src),
+                  self.p_back, G, self.cap_rows, H, T * K, st)
+        _lib.call("b200moe_ep_signal_wait", self.p_flags, self.rank, G, 2, epoch, status, st)
+        _lib.call("b200moe_combine", _lib.ptr(self.back), _lib.ptr(self.inv), T, K, H, _lib.ptr(self.out), st)
+        return self.out
+
+    def capture(self, hidden: torch.Tensor) -> None:
+        """Record one step on ``hidden`` (a fixed device buffer) into a CUDA graph; call after one eager step."""
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self.forward(hidden)
+
+    def replay(self) -> torch.Tensor:
+        self._graph.replay()
+        return self.out
+
+    def device_status(self) -> list:
+        """[exchange / capacity, gate-up contraction, down contraction] status words (0 = fine); synchronises."""
+        return self.status.cpu().tolist()[:3]

@@ -141,14 +141,15 @@ def random_expert_weights(E: int, H: int, I: int, device, seed: int = 0, std: fl
 
 
 class HostPipeline:
-    """Feeds a captured :class:`MoELayer` from host memory with copies overlapped with compute.
+    """Feeds a captured layer (:class:`MoELayer` or the peer-memory expert-parallel layer) from host memory
+    with copies overlapped with compute.
 
     ``submit(host_in, host_out)`` enqueues: pinned host -> device staging (copy stream), the layer (compute
     stream, CUDA graph), device -> pinned host (second copy stream).  Two staging buffers each way let step
     i + 1's upload and step i - 1's download run while step i computes.  ``drain()`` waits for everything.
     """
 
-    def __init__(self, layer: MoELayer):
+    def __init__(self, layer):
         dev = layer.out.device
         self.layer = layer
         self.hidden = torch.empty((layer.T, layer.H), dtype=torch.bfloat16, device=dev)

@@ -27,28 +27,69 @@ def _inputs(rank):
     return hidden, router_w, make_rows_weights(E, H, I, seed=9)
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, results, backend):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import nki_library_b200 as m
-        from nki_library_b200.ep import CudaOps, ExpertParallelMoE
+        from nki_library_b200.ep import CudaOps, ExpertParallelMoE, PeerExpertParallelMoE
         hidden, router_w, w_np = _inputs(rank)
         e_l = E // world
         local = m.prepare_from_rows(*(torch.from_numpy(np.ascontiguousarray(a[rank * e_l:(rank + 1) * e_l])).cuda()
                                       for a in w_np))
-        layer = ExpertParallelMoE(CudaOps(torch.from_numpy(router_w).cuda(), local, E, K, B), E)
-        out = layer.forward(torch.from_numpy(hidden).to(torch.bfloat16).cuda())
-        out2 = layer.forward(torch.from_numpy(hidden).to(torch.bfloat16).cuda())
+        x = torch.from_numpy(hidden).to(torch.bfloat16).cuda()
+        if backend == "nccl":
+            layer = ExpertParallelMoE(CudaOps(torch.from_numpy(router_w).cuda(), local, E, K, B), E)
+            out = layer.forward(x).clone()
+            out2 = layer.forward(x).clone()
+            rows = layer.last_rows_received
+        else:
+            layer = PeerExpertParallelMoE(torch.from_numpy(router_w).cuda(), local, E, K, B, T_LOCAL)
+            out = layer.forward(x).clone()
+            out2 = layer.forward(x).clone()
+            out3 = layer.forward(x).clone()
+            assert layer.device_status() == [0, 0, 0], layer.device_status()
+            assert torch.equal(out2, out3)
+            rows = int((layer.row_valid >= 0).sum().item())
         torch.cuda.synchronize()
-        results[rank] = (out.float().cpu().numpy(), bool(torch.equal(out, out2)), layer.last_rows_received)
+        results[rank] = (out.float().cpu().numpy(), bool(torch.equal(out, out2)), rows)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_memory_exchange_single_rank():
+    """World size 1: every 'peer' is this GPU, so the dispatch / plan / return kernels run without a second device."""
+    import nki_library_b200 as m
+    from moe_testlib import bf16_values, max_rel
+    from nki_library_b200.ep import PeerExpertParallelMoE
+    from nki_library_b200.layer import MoELayer
+    from oracle import moe, routing
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29733")
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        hidden, router_w, w_np = _inputs(0)
+        full = m.prepare_from_rows(*(torch.from_numpy(a).cuda() for a in w_np))
+        x = torch.from_numpy(hidden).to(torch.bfloat16).cuda()
+        layer = PeerExpertParallelMoE(torch.from_numpy(router_w).cuda(), full, E, K, B, T_LOCAL)
+        out = layer.forward(x).clone()
+        out2 = layer.forward(x).clone()
+        assert layer.device_status() == [0, 0, 0], layer.device_status()
+        assert torch.equal(out, out2)
+        assert int((layer.row_valid >= 0).sum().item()) == T_LOCAL * K
+        ref_gpu = MoELayer(torch.from_numpy(router_w).cuda(), full, K, B, T_LOCAL).forward(x)
+        assert max_rel(out.float().cpu().numpy(), ref_gpu.float().cpu().numpy()) <= 1e-2
+        _, idx, aff = routing.router_topk(torch.from_numpy(hidden), torch.from_numpy(router_w), None, K,
+                                          routing.SOFTMAX, True, True)
+        ref = moe.moe_tkg_rows(hidden, aff.numpy(), idx.numpy(), *w_np)
+        assert max_rel(out.float().cpu().numpy(), bf16_values(ref)) <= 2e-2
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_two_gpus_matches_oracle_and_single_gpu():
+@pytest.mark.parametrize("backend", ["nccl", "peer"])
+def test_expert_parallel_two_gpus_matches_oracle_and_single_gpu(backend):
     import nki_library_b200 as m
     from moe_testlib import bf16_values, max_rel
     from nki_library_b200.layer import MoELayer
@@ -56,7 +97,7 @@ def test_expert_parallel_two_gpus_matches_oracle_and_single_gpu():
     world = 2
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(world, 29711, results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, 29711 if backend == "nccl" else 29712, results, backend), nprocs=world, join=True)
     rows = 0
     for rank in range(world):
         hidden, router_w, w_np = _inputs(rank)
