@@ -216,6 +216,14 @@ int b200moe_set_clock_probe(void* device_words);
 int b200moe_combine(const void* y_pos_bf16, const int32_t* table, int T, int n_cand, int H, void* out_bf16,
                     b200moe_stream_t stream);
 
+/* ---- RMSNorm in front of the decode MoE block -------------------------------------------------
+ * rmsnorm_tkg as used by moe_block_tkg (core/moe_block/moe_block_tkg.py:192-232; CPU definition
+ * core/subkernels/rmsnorm_torch.py:22-51): out = x / sqrt(sum(x^2) / count + eps) * gamma with fp32
+ * statistics, count = hidden_actual if > 0 else H.  With a residual, x = bf16(inp + residual) and is
+ * also written to residual_out (may be NULL).  gamma [H] fp32 / bf16 or NULL. */
+int b200moe_rmsnorm(const void* inp_bf16, const void* residual_bf16, const void* gamma, int gamma_dtype, int T, int H,
+                    int hidden_actual, float eps, void* out_bf16, void* residual_out_bf16, b200moe_stream_t stream);
+
 /* ---- expert parallelism over peer memory -------------------------------------------------------
  * One process per GPU.  The reference's expert-parallel mode slices experts by rank_id
  * (core/moe/moe_tkg/moe_tkg.py:100-101) and leaves the token exchange to an external all_to_all_v

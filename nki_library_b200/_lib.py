@@ -62,6 +62,8 @@ SIGNATURES = {
     "b200moe_set_gemm_cta_pair": (c_int, [c_int]),
     "b200moe_set_clock_probe": (c_int, [c_void_p]),
     "b200moe_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200moe_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                                c_void_p]),
     "b200moe_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
     "b200moe_ipc_open": (c_int, [c_void_p, c_int64, c_void_p]),
     "b200moe_ipc_close": (c_int, [c_void_p, c_int64]),

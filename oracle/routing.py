@@ -66,6 +66,19 @@ def router_topk(x, w, w_bias, k, act_fn=SOFTMAX, router_pre_norm=True, norm_topk
     return logits, idx, aff
 
 
+def rms_norm(x: torch.Tensor, gamma=None, eps: float = 1e-6, hidden_actual=None) -> torch.Tensor:
+    """fp32 RMSNorm (core/subkernels/rmsnorm_torch.py:22-51)."""
+    x = x.float()
+    if hidden_actual is not None:
+        rms = (x.square().sum(dim=-1, keepdim=True) / hidden_actual + eps).sqrt()
+    else:
+        rms = (x.square().mean(dim=-1, keepdim=True) + eps).sqrt()
+    y = x * rms.reciprocal()
+    if gamma is not None:
+        y = y * gamma.float().reshape(1, -1)
+    return y
+
+
 # --------------------------------------------------------------------------
 # grouping
 # --------------------------------------------------------------------------

@@ -267,3 +267,32 @@ def test_moe_cte_properties_at_mixtral_block_shape():
     hid_np = hid.float().cpu().numpy()
     ref = moe.moe_tkg_rows(hid_np[sample], aff[sample], idx[sample], c1, sc1, w2_np, s2)
     assert max_rel(out[sample].float().cpu().numpy(), bf16_values(ref)) <= TOL
+
+
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_moe_block_tkg_vs_oracle(with_residual):
+    """RMSNorm -> router -> decode experts, against the composite of the reference's torch references."""
+    import nki_library_b200 as m
+    Bt, S, H, I, E, K = 4, 8, 1024, 512, 8, 2
+    T = Bt * S
+    rng = np.random.default_rng(71)
+    inp = bf16_values(rng.standard_normal((Bt, S, H)).astype(np.float32) * 2.0)
+    res = bf16_values(rng.standard_normal((Bt, S, H)).astype(np.float32)) if with_residual else None
+    gamma = bf16_values(rng.uniform(0.5, 1.5, (1, H)).astype(np.float32))
+    rw = bf16_values((rng.standard_normal((H, E)) * 0.05).astype(np.float32))
+    w_np = make_rows_weights(E, H, I, 72)
+    weights = _prep(m, w_np)
+    to = lambda a: None if a is None else torch.from_numpy(a).to(torch.bfloat16).cuda()
+    outs = m.moe_block_tkg(to(inp), to(gamma), to(rw), weights, None, top_k=K,
+                           router_act_fn=m.RouterActFnType.SOFTMAX, router_pre_norm=True, norm_topk_prob=True,
+                           expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.POST_SCALE, residual=to(res))
+    assert len(outs) == (3 if with_residual else 2)
+    x = inp.reshape(T, H) if res is None else bf16_values(inp.reshape(T, H) + res.reshape(T, H))
+    if with_residual:
+        assert np.array_equal(outs[2].float().cpu().numpy(), x)
+    normed = bf16_values(routing.rms_norm(torch.from_numpy(x), torch.from_numpy(gamma)).numpy())
+    logits, idx, aff = routing.router_topk(torch.from_numpy(normed), torch.from_numpy(rw), None, K, routing.SOFTMAX,
+                                           True, True)
+    np.testing.assert_allclose(outs[1].cpu().numpy(), logits.numpy(), rtol=0, atol=2e-2 * np.abs(logits.numpy()).max())
+    ref = moe.moe_tkg_rows(normed, aff.numpy(), idx.numpy(), *w_np)
+    assert max_rel(outs[0].float().cpu().numpy(), bf16_values(ref)) <= 3e-2  # bf16 RMSNorm rounding can move a row
