@@ -55,54 +55,63 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and throttle reasons through NVML every few milliseconds while a region runs
+    (read-only queries; falls back to one nvidia-smi query if NVML is unavailable)."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
     def __init__(self, gpu_index: int):
-        self.rows = []
-        self.proc = None
         self.gpu = gpu_index
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self.thread = None
+        self.handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[gpu_index]) if visible and visible.split(",")[gpu_index].isdigit() else gpu_index
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.handle = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                for name, bit in self.REASONS:
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.003)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
             self.thread.start()
-        except Exception:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            sm = self.samples
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                    "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(sm),
+                    "source": "NVML, 3 ms period, over the timed regions"}
         try:
-            self.proc.wait(timeout=5)
+            out = subprocess.run(["nvidia-smi", f"--id={self.gpu}", "--query-gpu=clocks.sm,clocks.max.sm",
+                                  "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=10).stdout
+            cur, mx = (float(v) for v in out.strip().split(","))
+            return {"sm_mhz": cur, "sm_max_mhz": mx, "reasons": [], "samples": 1, "source": "nvidia-smi after the run"}
         except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        for r in self.rows:
-            try:
-                sm.append(float(r[1]))
-                mx.append(float(r[2]))
-            except Exception:
-                continue
-            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
-                              ("sw_power_cap", 8)):
-                if len(r) > col and r[col].lower().startswith("active"):
-                    reasons.add(name)
-        busy = [s for s in sm if s > 0.5 * max(sm)] if sm else []
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock query unavailable"], "samples": 0}
 
 
 def algorithmic_work(cfg):
@@ -214,6 +223,38 @@ def run_reference(args, cfg, name):
 
 
 # ------------------------------------------------------------------ GPU leg
+def decode_leg(weights, peaks, device):
+    """Mixtral decode workload (BASELINE config 3) on the prefill run's expert weights: tokens/s and HBM fraction."""
+    import torch
+
+    from nki_library_b200.layer import MoELayer
+    cfg = WORKLOADS["mixtral_decode"]
+    T, H, E, K, B = cfg["T"], cfg["H"], cfg["E"], cfg["K"], cfg["B"]
+    hidden, router_w, _ = make_inputs(cfg, device, 99)
+    layer = MoELayer(router_w.to(device), weights, K, B, T)
+    x = hidden.to(device)
+    for _ in range(3):
+        layer.forward(x)
+    torch.cuda.synchronize()
+    layer.capture(x)
+    layer.replay()
+    steps = 100
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(steps):
+        layer.replay()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / steps
+    if any(layer.device_status()):
+        return {"error": f"device status {layer.device_status()}"}
+    gbs = algorithmic_work(cfg)["decode_bytes"] / (ms * 1e-3) / 1e9
+    return {"workload": "mixtral_decode", "T": T, "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3),
+            "algorithmic_gb_per_s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
+            "steps": steps, "launch_mode": "cuda graph replay"}
+
+
 def run_ours(args, cfg, name):
     import torch
     import torch.distributed as dist
@@ -314,7 +355,6 @@ def run_ours(args, cfg, name):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.2)
     # -------- resident-input leg (value): the captured launch sequence (single GPU) or eager steps (EP)
     use_graph = (world == 1 or args.ep_backend == "peer") and not args.no_graph
     if use_graph:
@@ -414,6 +454,7 @@ def run_ours(args, cfg, name):
                         "layer_gbs": work["decode_bytes"] / (ms_step * 1e-3) / 1e9}
         cpu = (dict(value=None, sample="skipped (--skip-cpu)") if args.skip_cpu
                else cpu_sample(cfg, 2, 1, os.cpu_count() or 1))
+        decode = decode_leg(weights, peaks, dev) if (world == 1 and name == "mixtral_prefill") else None
         line = {
             "metric": "moe_layer_tokens_per_s", "value": world * T / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
@@ -426,6 +467,7 @@ def run_ours(args, cfg, name):
                         else f"ep{world} (NCCL all-to-all dispatch/combine)"),
                        "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)" % (weights.nbytes() / 1e9)},
             "roofline": roofline,
+            "decode": decode,
             "kernel_ms": per_kernel,
             "kernel_sm_mhz": kernel_sm_mhz,
             "cpu_baseline": {"value": cpu["value"], "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
