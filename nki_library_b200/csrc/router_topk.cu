@@ -235,43 +235,48 @@ __global__ void __launch_bounds__(256) router_rank_kernel(RankArgs a) {
     }
   }
 
-  // K rounds of arg-max with lowest-index tie break
+  // K rounds of arg-max with lowest-index tie break.  Logits become order-preserving 32-bit keys, so a
+  // round is one warp-wide integer max (the winning value) and one integer min (the lowest expert holding
+  // it) instead of a shuffle tree over (value, index) pairs.  Key 0 marks "nothing left in this lane".
+  uint32_t key[NPL];
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) {
+    uint32_t u = __float_as_uint(v[j]);
+    if (u == 0x80000000u) u = 0u;  // -0 ranks with +0
+    const int e = lane + 32 * j;
+    key[j] = (j < n_per_lane && e < E) ? ((u & 0x80000000u) ? ~u : (u | 0x80000000u)) : 0u;
+  }
   float top_v[8];
   int top_e[8];
   float top_a[8];  // activated value of the selected expert (pre-norm)
-  uint32_t taken = 0;
 #pragma unroll
   for (int r = 0; r < 8; ++r) {
     if (r >= a.k) break;
-    float bv = -INFINITY;
+    uint32_t bk = 0;
     int be = 0x7fffffff;
 #pragma unroll
-    for (int j = 0; j < NPL; ++j) {
-      const int e = lane + 32 * j;
-      if (j < n_per_lane && e < E && !((taken >> j) & 1u)) {
-        if (v[j] > bv || (v[j] == bv && e < be)) { bv = v[j]; be = e; }
-      }
-    }
-    if (be == 0x7fffffff) bv = -INFINITY;
+    for (int j = 0; j < NPL; ++j)
+      if (key[j] > bk) { bk = key[j]; be = lane + 32 * j; }
+    const uint32_t mk = __reduce_max_sync(0xffffffffu, bk);
+    const int win = static_cast<int>(__reduce_min_sync(0xffffffffu, static_cast<uint32_t>(bk == mk ? be : 0x7fffffff)));
+    if ((win & 31) == lane) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-      if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+      for (int j = 0; j < NPL; ++j)
+        if (j == (win >> 5)) key[j] = 0u;
     }
-    float sel_a = 0.f;
-    if (be != 0x7fffffff && (be & 31) == lane) {
-      taken |= 1u << (be >> 5);
-      if (a.pre_norm) {
+    top_v[r] = __uint_as_float((mk & 0x80000000u) ? (mk & 0x7fffffffu) : ~mk);
+    top_e[r] = win;
+  }
 #pragma unroll
-        for (int j = 0; j < NPL; ++j)
-          if (j == (be >> 5)) sel_a = full[j];
-      }
+  for (int r = 0; r < 8; ++r) {
+    top_a[r] = 0.f;
+    if (r < a.k && a.pre_norm) {
+      float mine = 0.f;
+#pragma unroll
+      for (int j = 0; j < NPL; ++j)
+        if (j == (top_e[r] >> 5)) mine = full[j];
+      top_a[r] = __shfl_sync(0xffffffffu, mine, top_e[r] & 31);
     }
-    sel_a = __shfl_sync(0xffffffffu, sel_a, be & 31);
-    top_v[r] = bv;
-    top_e[r] = be;
-    top_a[r] = sel_a;
   }
 
   if (a.index_out != nullptr && lane < a.k) {
