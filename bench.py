@@ -114,17 +114,21 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock query unavailable"], "samples": 0}
 
 
-def algorithmic_work(cfg):
+W_FORMATS = {"e4m3": 0, "e5m2": 1, "e2m1": 5}
+
+
+def algorithmic_work(cfg, w_format="e4m3"):
     """Figures used for roofline.achieved: useful work only, no padding rows, no re-reads."""
     T, H, I, E, K = cfg["T"], cfg["H"], cfg["I"], cfg["E"], cfg["K"]
+    wb = (0.5 if w_format == "e2m1" else 1.0) + 1 / 32  # bytes per weight element incl. its share of the scale
     return {
         "gemm1_flops": 4.0 * T * K * H * I,
         "gemm2_flops": 2.0 * T * K * H * I,
         "layer_flops": 6.0 * T * K * H * I,
         # decode: every expert's weights and scales once, tokens in and out, router weight
-        "decode_bytes": E * 3.0 * H * I * (1 + 1 / 32) + 2.0 * T * H * 2 + H * E * 2,
-        "gemm1_weight_bytes": E * 2.0 * H * I * (1 + 1 / 32),
-        "gemm2_weight_bytes": E * 1.0 * H * I * (1 + 1 / 32),
+        "decode_bytes": E * 3.0 * H * I * wb + 2.0 * T * H * 2 + H * E * 2,
+        "gemm1_weight_bytes": E * 2.0 * H * I * wb,
+        "gemm2_weight_bytes": E * 1.0 * H * I * wb,
     }
 
 
@@ -223,8 +227,8 @@ def run_reference(args, cfg, name):
 
 
 # ------------------------------------------------------------------ GPU leg
-def decode_leg(weights, peaks, device):
-    """Mixtral decode workload (BASELINE config 3) on the prefill run's expert weights: tokens/s and HBM fraction."""
+def decode_leg(weights, peaks, device, w_format="e4m3"):
+    """Mixtral decode workload (BASELINE config 3) on the given expert weights: tokens/s and HBM fraction."""
     import torch
 
     from nki_library_b200.layer import MoELayer
@@ -249,8 +253,8 @@ def decode_leg(weights, peaks, device):
     ms = s.elapsed_time(e) / steps
     if any(layer.device_status()):
         return {"error": f"device status {layer.device_status()}"}
-    gbs = algorithmic_work(cfg)["decode_bytes"] / (ms * 1e-3) / 1e9
-    return {"workload": "mixtral_decode", "T": T, "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3),
+    gbs = algorithmic_work(cfg, w_format)["decode_bytes"] / (ms * 1e-3) / 1e9
+    return {"workload": "mixtral_decode", "weight_format": w_format, "T": T, "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3),
             "algorithmic_gb_per_s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
             "steps": steps, "launch_mode": "cuda graph replay"}
 
@@ -284,7 +288,7 @@ def run_ours(args, cfg, name):
     hidden_d = hidden_h.to(dev)
     bias_d = None if bias is None else bias.to(dev)
     if world == 1:
-        weights = random_expert_weights(E, H, I, dev, seed=7)
+        weights = random_expert_weights(E, H, I, dev, seed=7, w_format=W_FORMATS[args.weight_format])
         layer = MoELayer(router_w.to(dev), weights, K, B, T, bias_d)
         n_blocks = layer.N
 
@@ -302,7 +306,7 @@ def run_ours(args, cfg, name):
         from nki_library_b200.ep import CudaOps, ExpertParallelMoE, PeerExpertParallelMoE
         if E % world != 0:
             raise SystemExit(f"workload has {E} experts, not divisible by {world} ranks")
-        weights = random_expert_weights(E // world, H, I, dev, seed=7 + rank)
+        weights = random_expert_weights(E // world, H, I, dev, seed=7 + rank, w_format=W_FORMATS[args.weight_format])
         n_blocks = None
         if args.ep_backend == "peer":
             # dispatch / combine by this library's own kernels storing into peer GPUs' memory (NVLink)
@@ -429,7 +433,7 @@ def run_ours(args, cfg, name):
         raise RuntimeError(f"device status after timing: {status}")
 
     if rank == 0:
-        work = algorithmic_work(cfg)
+        work = algorithmic_work(cfg, args.weight_format)
         ms_step = ms_total / args.steps
         if cfg["kind"] == "prefill":
             dom = "gemm1_swiglu"
@@ -454,13 +458,21 @@ def run_ours(args, cfg, name):
                         "layer_gbs": work["decode_bytes"] / (ms_step * 1e-3) / 1e9}
         cpu = (dict(value=None, sample="skipped (--skip-cpu)") if args.skip_cpu
                else cpu_sample(cfg, 2, 1, os.cpu_count() or 1))
-        decode = decode_leg(weights, peaks, dev) if (world == 1 and name == "mixtral_prefill") else None
+        decode = decode_mxfp4 = None
+        if world == 1 and name == "mixtral_prefill":
+            decode = decode_leg(weights, peaks, dev, args.weight_format)
+            if args.weight_format == "e4m3":
+                # the same decode step with MXFP4 (e2m1) expert weights: half the bytes to stream
+                w4 = random_expert_weights(E, H, I, dev, seed=8, w_format=W_FORMATS["e2m1"])
+                decode_mxfp4 = decode_leg(w4, peaks, dev, "e2m1")
+                del w4
         line = {
             "metric": "moe_layer_tokens_per_s", "value": world * T / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8_e4m3",
             "data": "synthetic",
             "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}, "n_blocks": n_blocks,
+                       "weight_format": args.weight_format,
                        "tokens_per_gpu": T, "experts_per_gpu": E // world,
                        "parallelism": "single" if world == 1 else
                        (f"ep{world} (peer-memory dispatch/combine kernels over NVLink)" if args.ep_backend == "peer"
@@ -468,6 +480,7 @@ def run_ours(args, cfg, name):
                        "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)" % (weights.nbytes() / 1e9)},
             "roofline": roofline,
             "decode": decode,
+            "decode_mxfp4_weights": decode_mxfp4,
             "kernel_ms": per_kernel,
             "kernel_sm_mhz": kernel_sm_mhz,
             "cpu_baseline": {"value": cpu["value"], "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
@@ -492,6 +505,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mixtral_prefill", choices=sorted(WORKLOADS))
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    ap.add_argument("--weight-format", default="e4m3", choices=sorted(W_FORMATS),
+                    help="element type of the expert weights (activations are always MXFP8 e4m3)")
     ap.add_argument("--ep-backend", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel exchange for --gpus > 1: peer-memory kernels (default) or NCCL all-to-all")
     ap.add_argument("--capacity-factor", type=float, default=2.5,

@@ -49,6 +49,11 @@ enum { B200MOE_ACT_SILU = 0, B200MOE_ACT_GELU = 1, B200MOE_ACT_GELU_TANH = 2, B2
 enum { B200MOE_ROUTER_SIGMOID = 0, B200MOE_ROUTER_SOFTMAX = 1 };
 /* weight source layouts accepted by the prepare functions */
 enum { B200MOE_LAYOUT_ROWS = 0, B200MOE_LAYOUT_NKI_X4 = 1 };
+/* element formats of expert weights (activations are always e4m3): the OCP MX element types the
+ * reference's weights come in -- float8_e4m3fn_x4, float8_e5m2_x4 and float4_e2m1fn_x4
+ * (core/utils/mx_torch_common.py:31-133, core/moe/moe_cte/moe_cte_mx_utils.py:58-107).  e2m1 packs two
+ * elements per byte (element 2j in the low nibble), so a weight row of K elements is K/2 bytes. */
+enum { B200MOE_W_E4M3 = 0, B200MOE_W_E5M2 = 1, B200MOE_W_E2M1 = 5 };
 /* routing source accepted by b200moe_group_tokens */
 enum { B200MOE_ROUTING_INDEX = 0, B200MOE_ROUTING_MASK = 1 };
 
@@ -154,11 +159,16 @@ int b200moe_gather_quantize_mxfp8(const void* hidden_bf16, int hidden_rows, int 
  * gate_up [E,128,2,H/512,I] x4 + scale [E,16,2,H/512,I],
  * down [E,p_I,ceil(I/512),H] x4 + scale [E,p_I/8,ceil(I/512),H]
  * (core/moe/moe_cte/bwmm_shard_on_block_mx.py:70-230).
+ * w_format is one of B200MOE_W_*: 8-bit elements are one byte each (x4 = 32 bits), e2m1 elements are
+ * nibbles (x4 = 16 bits, so every byte count above halves); e2m1 needs contraction lengths that are
+ * multiples of 128.  The prepared arrays hold b200moe_weight_bytes(rows, K, w_format) bytes per expert.
  * Bias sources: gate_up [E,2,I] fp32 (ROWS) or [E,p_I,2,ceil(I/512),4] (NKI_X4), any of F32/BF16. */
-int b200moe_prepare_gate_up(const void* w, const uint8_t* scale, int layout, int E, int H, int I, uint8_t* w_dev,
-                            uint8_t* sf_dev, b200moe_stream_t stream);
-int b200moe_prepare_down(const void* w, const uint8_t* scale, int layout, int E, int H, int I, uint8_t* w_dev,
-                         uint8_t* sf_dev, b200moe_stream_t stream);
+int b200moe_prepare_gate_up(const void* w, const uint8_t* scale, int layout, int w_format, int E, int H, int I,
+                            uint8_t* w_dev, uint8_t* sf_dev, b200moe_stream_t stream);
+int b200moe_prepare_down(const void* w, const uint8_t* scale, int layout, int w_format, int E, int H, int I,
+                         uint8_t* w_dev, uint8_t* sf_dev, b200moe_stream_t stream);
+/* Bytes of `rows` prepared weight rows of K elements in the given format (no reference counterpart). */
+int64_t b200moe_weight_bytes(int64_t rows, int64_t K, int w_format);
 int b200moe_prepare_gate_up_bias(const void* bias, int dtype, int layout, int E, int I, float* bias_dev,
                                  b200moe_stream_t stream);
 
@@ -178,7 +188,8 @@ int b200moe_prepare_gate_up_bias(const void* bias, int dtype, int layout, int E,
  *  core/mlp/mlp_tkg/down_projection_mx_shard_H.py:73-78).  Clamp limits are
  * ignored when NaN.  Output: codes [n_blocks*B, I] + scale atoms. */
 int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_t* x_sf, const uint8_t* w1_dev,
-                                 const uint8_t* w1_sf, const float* bias_gu_dev, const int32_t* block_to_expert,
+                                 const uint8_t* w1_sf, int w_format, const float* bias_gu_dev,
+                                 const int32_t* block_to_expert,
                                  const int32_t* conditions, const int32_t* tile_flags,
                                  int n_blocks, int B, int E, int H, int I, int act_fn, float gate_lo, float gate_hi,
                                  float up_lo, float up_hi, uint8_t* m_codes, uint8_t* m_sf, int32_t* status, int impl,
@@ -191,7 +202,7 @@ int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_t* x_sf, co
  * aff_per_row == 0, a [rows] vector addressed tok when aff_per_row != 0 (rows that arrived
  * through an expert-parallel dispatch carry their own affinity), or NULL for no scaling.  Output: bf16 y_pos [n_blocks*B, H] (pad rows untouched). */
 int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
-                                const uint8_t* w2_sf, const float* bias_d, const int32_t* block_to_expert,
+                                const uint8_t* w2_sf, int w_format, const float* bias_d, const int32_t* block_to_expert,
                                 const int32_t* conditions, const int32_t* tile_flags,
                                 const int32_t* token_position_to_id, int hidden_rows,
                                 int n_blocks, int B, int E, int H, int I, const void* affinities, int aff_dtype,

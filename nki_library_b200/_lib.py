@@ -22,6 +22,7 @@ ERROR_PREFIX = "[INTERNAL_ERROR] [NCC_INKI016] Kernel validation exception: "
 
 F32, BF16, I32 = 0, 1, 2
 LAYOUT_ROWS, LAYOUT_NKI_X4 = 0, 1
+W_E4M3, W_E5M2, W_E2M1 = 0, 1, 5  # weight element formats (B200MOE_W_*)
 ROUTING_INDEX, ROUTING_MASK = 0, 1
 
 # name -> (restype, argtypes); must list every symbol of include/b200moe.h
@@ -49,13 +50,15 @@ SIGNATURES = {
                                              c_void_p]),
     "b200moe_gather_quantize_mxfp8": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p,
                                               c_void_p, c_void_p]),
-    "b200moe_prepare_gate_up": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
-    "b200moe_prepare_down": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200moe_prepare_gate_up": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                        c_void_p]),
+    "b200moe_prepare_down": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200moe_weight_bytes": (c_int64, [c_int64, c_int64, c_int]),
     "b200moe_prepare_gate_up_bias": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "b200moe_grouped_gemm1_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    "b200moe_grouped_gemm1_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
                                              c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
-    "b200moe_grouped_gemm2_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    "b200moe_grouped_gemm2_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                             c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_set_gemm_tile_n": (c_int, [c_int]),

@@ -65,6 +65,8 @@ struct GemmParams {
   int H_out;
   int32_t* status;
   unsigned long long* clock_probe;  // optional: CTA 0 writes {SM cycles, nanoseconds} spent in the kernel
+  int w_format;     // element format of the weight operand (B200MOE_W_*); activations are e4m3
+  uint32_t b_tx;    // bytes one weight-tile copy reports to its mbarrier
   int experiment;  // timing experiments only (builds with -DB200MOE_EXPERIMENT): bit 0 no loads, 1 no MMA,
                    // 2 no scale copies, 3 no epilogue math; results are meaningless when non-zero
 };
@@ -253,7 +255,8 @@ __device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
   d |= static_cast<uint64_t>(1) << 46;
   return d;
 }
-// kind::mxf8f6f4 block-scaled instruction descriptor: e4m3 x e4m3, UE8M0 scales, K-major A and B.
+// kind::mxf8f6f4 block-scaled instruction descriptor: e4m3 activations (A format, bits 7-9 = 0), UE8M0
+// scales, K-major A and B.  The weight format (bits 10-12: 0 e4m3, 1 e5m2, 5 e2m1) is or-ed in at run time.
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
   return (0u << 7) | (0u << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (1u << 23) |
          (static_cast<uint32_t>(M >> 4) << 24);
@@ -372,7 +375,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   constexpr int kSfCol = kAcc * BLOCK_N;  // TMEM columns: accumulators, then SFA (4), then SFB
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kIdesc = make_idesc(kBlockM * CTAS, BLOCK_N);
-  constexpr uint32_t kStageBytes = CTAS * (L::kA + L::kB);  // operand bytes per stage (scale atoms: sf_full)
+  // operand bytes per stage (scale atoms report to sf_full); 4-bit weights land in the same padded
+  // 128-byte rows, so the count is a launch parameter rather than a constant of the tile shape
+  const uint32_t stage_bytes = CTAS * (L::kA + p.b_tx);
+  const uint32_t idesc_base = kIdesc | (static_cast<uint32_t>(p.w_format) << 10);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -468,12 +474,23 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                         (e * p.b_row_atoms + atom0 + j) * p.k_blocks + kb, &sf_full[stage]);
           if constexpr (CTAS == 2) {
             // operand tiles of both CTAs complete on the even CTA's barrier
-            if (cta_rank == 0) mbar_expect_tx(&full[stage], kStageBytes);
+#ifdef B200MOE_EXPERIMENT
+            const bool skip_a = (p.experiment & 16) && (kb & 1), skip_b = (p.experiment & 32) && (kb & 1);
+            if (cta_rank == 0)
+              mbar_expect_tx(&full[stage], stage_bytes - (skip_a ? 2 * L::kA : 0) - (skip_b ? 2 * p.b_tx : 0));
+            if (!skip_a)
+              tma2_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
+            if (!skip_b)
+              tma2_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK,
+                           n_tile * BLOCK_N + cta_rank * (BLOCK_N / 2), e, &full[stage]);
+#else
+            if (cta_rank == 0) mbar_expect_tx(&full[stage], stage_bytes);
             tma2_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
             tma2_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK,
                          n_tile * BLOCK_N + cta_rank * (BLOCK_N / 2), e, &full[stage]);
+#endif
           } else {
-            mbar_expect_tx(&full[stage], kStageBytes);
+            mbar_expect_tx(&full[stage], stage_bytes);
             tma_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
             tma_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK, n_tile * BLOCK_N, e, &full[stage]);
           }
@@ -511,7 +528,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #endif
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint32_t idesc = kIdesc | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
+            const uint32_t idesc = idesc_base | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
             if constexpr (CTAS == 2)
               tc2_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
             else
@@ -713,14 +730,33 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t c) {
   return __half2float(*reinterpret_cast<const __half*>(&h));
 }
 
+__device__ __forceinline__ int64_t weight_offset(int64_t rows, int K, int w_format) {
+  return w_format == B200MOE_W_E2M1 ? rows * K / 2 : rows * K;
+}
+// Weight element k of a row of K elements in any of the supported formats.
+__device__ __forceinline__ float weight_to_float(const uint8_t* row, int k, int w_format) {
+  if (w_format == B200MOE_W_E2M1) {
+    const uint32_t nib = (row[k >> 1] >> ((k & 1) * 4)) & 0xFu;
+    const uint32_t ex = (nib >> 1) & 3u, man = nib & 1u;
+    const float mag = ex == 0 ? 0.5f * man : (1.0f + 0.5f * man) * static_cast<float>(1u << (ex - 1));
+    return (nib & 8u) ? -mag : mag;
+  }
+  if (w_format == B200MOE_W_E5M2) {
+    const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(row[k]), __NV_E5M2);
+    return __half2float(*reinterpret_cast<const __half*>(&h));
+  }
+  return e4m3_to_float(row[k]);
+}
+
 __device__ float mx_dot(const uint8_t* a, const uint8_t* a_sf, int64_t a_row, const uint8_t* b, const uint8_t* b_sf,
-                        int64_t b_row, int K) {
+                        int64_t b_row, int K, int w_format) {
   const int64_t k_atoms = (K + 127) >> 7;
+  const uint8_t* brow = b + b_row * (w_format == B200MOE_W_E2M1 ? K / 2 : K);
   float acc = 0.f;
   for (int kb = 0; kb < K / 32; ++kb) {
     float part = 0.f;
     for (int j = 0; j < 32; ++j)
-      part += e4m3_to_float(a[a_row * K + kb * 32 + j]) * e4m3_to_float(b[b_row * K + kb * 32 + j]);
+      part += e4m3_to_float(a[a_row * K + kb * 32 + j]) * weight_to_float(brow, kb * 32 + j, w_format);
     const int sa = a_sf[sf_atom_offset(a_row, kb, k_atoms)], sb = b_sf[sf_atom_offset(b_row, kb, k_atoms)];
     acc += part * exp2f(static_cast<float>(sa - 127)) * exp2f(static_cast<float>(sb - 127));
   }
@@ -748,15 +784,15 @@ __global__ void simt_gemm1_kernel(const uint8_t* x, const uint8_t* w, GemmParams
     if (p.tile_flags && p.tile_flags[m_tile] == 0) continue;
     const int e = p.block_to_expert[block];
     if (e < 0 || e >= p.E) continue;
-    const uint8_t* we = w + static_cast<int64_t>(e) * p.n_total * K;
+    const uint8_t* we = w + weight_offset(static_cast<int64_t>(e) * p.n_total, K, p.w_format);
     const uint8_t* wsf = p.b_sf + static_cast<int64_t>(e) * p.b_sf_expert_stride;
     const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.n_total : nullptr;
     float m[32];
     uint32_t mx = 0;
     for (int j = 0; j < 32; ++j) {
       const int n_g = ib * 64 + j, n_u = n_g + 32;
-      float gv = mx_dot(x, p.a_sf, row, we, wsf, n_g, K);
-      float uv = mx_dot(x, p.a_sf, row, we, wsf, n_u, K);
+      float gv = mx_dot(x, p.a_sf, row, we, wsf, n_g, K, p.w_format);
+      float uv = mx_dot(x, p.a_sf, row, we, wsf, n_u, K, p.w_format);
       if (bias) { gv += bias[n_g]; uv += bias[n_u]; }
       if (p.gate_lo == p.gate_lo) gv = fmaxf(gv, p.gate_lo);
       if (p.gate_hi == p.gate_hi) gv = fminf(gv, p.gate_hi);
@@ -788,8 +824,8 @@ __global__ void simt_gemm2_kernel(const uint8_t* m, const uint8_t* w, GemmParams
     if (e < 0 || e >= p.E) continue;
     const int tok = p.tpi ? p.tpi[row] : static_cast<int>(row);
     if (tok < 0 || tok >= p.hidden_rows) continue;
-    float y = mx_dot(m, p.a_sf, row, w + static_cast<int64_t>(e) * p.n_total * K,
-                     p.b_sf + static_cast<int64_t>(e) * p.b_sf_expert_stride, h, K);
+    float y = mx_dot(m, p.a_sf, row, w + weight_offset(static_cast<int64_t>(e) * p.n_total, K, p.w_format),
+                     p.b_sf + static_cast<int64_t>(e) * p.b_sf_expert_stride, h, K, p.w_format);
     if (p.bias) y += p.bias[static_cast<int64_t>(e) * p.H_out + h];
     if (p.aff)
       y *= load_as_float(p.aff, p.aff_per_row ? static_cast<int64_t>(tok) : static_cast<int64_t>(tok) * p.E + e,
@@ -815,15 +851,21 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-int make_rows_map(CUtensorMap* map, const void* base, int64_t K, int64_t rows, int64_t batch, int box_rows) {
+// Rows of K elements, one byte each, or (nibbles) two per byte: the 4-bit map type expands every 8 packed
+// bytes to a 16-byte shared-memory chunk, which is the padded form the f8f6f4 MMA reads 4-bit operands in,
+// so a 128-element slab still occupies a 128-byte swizzled row.
+int make_rows_map(CUtensorMap* map, const void* base, int64_t K, int64_t rows, int64_t batch, int box_rows,
+                  bool nibbles = false) {
   EncodeTiledFn enc = get_encode_fn();
   B200MOE_REQUIRE(enc != nullptr, B200MOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint32_t rank = batch > 0 ? 3 : 2;
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch > 0 ? batch : 1)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(K) * static_cast<cuuint64_t>(rows)};
+  const cuuint64_t pitch = static_cast<cuuint64_t>(nibbles ? K / 2 : K);
+  cuuint64_t strides[2] = {pitch, pitch * static_cast<cuuint64_t>(rows)};
   cuuint32_t box[3] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows), 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims, strides, box, estr,
+  const CUresult r = enc(map, nibbles ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, rank,
+                         const_cast<void*>(base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   B200MOE_REQUIRE(r == CUDA_SUCCESS, B200MOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
@@ -889,6 +931,11 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   B200MOE_REQUIRE(p.n_blocks > 0 && p.E > 0 && p.E <= kMaxExperts, B200MOE_ERR_INVALID,
                   "need at least one block and between 1 and %d experts", kMaxExperts);
   B200MOE_REQUIRE(p.status != nullptr, B200MOE_ERR_INVALID, "status pointer must not be null");
+  B200MOE_REQUIRE(p.w_format == B200MOE_W_E4M3 || p.w_format == B200MOE_W_E5M2 || p.w_format == B200MOE_W_E2M1,
+                  B200MOE_ERR_INVALID, "unknown weight format %d", p.w_format);
+  const bool nibbles = p.w_format == B200MOE_W_E2M1;
+  B200MOE_REQUIRE(!nibbles || K % 128 == 0, B200MOE_ERR_INVALID,
+                  "e2m1 weights need a contraction length that is a multiple of 128, got %d", K);
   p.m_tiles_total = p.n_blocks * (p.B / 128);
   p.clock_probe = g_clock_probe ? g_clock_probe + 2 * epi : nullptr;
 #ifdef B200MOE_EXPERIMENT
@@ -914,7 +961,9 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   CUtensorMap ma, mb, msa, msb;
   int rc = make_rows_map(&ma, a, K, static_cast<int64_t>(p.m_tiles_total) * 128, 0, kBlockM);
   if (rc != B200MOE_OK) return rc;
-  rc = make_rows_map(&mb, b, K, p.n_total, p.E, pair ? bn / 2 : bn);
+  rc = make_rows_map(&mb, b, K, p.n_total, p.E, pair ? bn / 2 : bn, nibbles);
+  // the copy reports the bytes it read from global memory: a 4-bit slab is 64 bytes per row there
+  p.b_tx = static_cast<uint32_t>((pair ? bn / 2 : bn) * (nibbles ? kBlockK / 2 : kBlockK));
   if (rc != B200MOE_OK) return rc;
   rc = make_atoms_map(&msa, p.a_sf, static_cast<int64_t>(p.m_tiles_total) * p.k_blocks);
   if (rc != B200MOE_OK) return rc;
@@ -950,7 +999,7 @@ extern "C" int b200moe_set_gemm_tile_n(int block_n) {
 }
 
 extern "C" int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_t* x_sf, const uint8_t* w1_dev,
-                                            const uint8_t* w1_sf, const float* bias_gu_dev,
+                                            const uint8_t* w1_sf, int w_format, const float* bias_gu_dev,
                                             const int32_t* block_to_expert, const int32_t* conditions,
                                             const int32_t* tile_flags, int n_blocks, int B, int E, int H, int I,
                                             int act_fn, float gate_lo, float gate_hi, float up_lo, float up_hi,
@@ -963,6 +1012,7 @@ extern "C" int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_
   GemmParams p{};
   p.a_sf = x_sf;
   p.b_sf = w1_sf;
+  p.w_format = w_format;
   p.block_to_expert = block_to_expert;
   p.conditions = conditions;
   p.tile_flags = tile_flags;
@@ -987,7 +1037,8 @@ extern "C" int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_
 }
 
 extern "C" int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
-                                           const uint8_t* w2_sf, const float* bias_d, const int32_t* block_to_expert,
+                                           const uint8_t* w2_sf, int w_format, const float* bias_d,
+                                           const int32_t* block_to_expert,
                                            const int32_t* conditions, const int32_t* tile_flags,
                                            const int32_t* token_position_to_id, int hidden_rows, int n_blocks, int B,
                                            int E, int H, int I, const void* affinities, int aff_dtype,
@@ -1001,6 +1052,7 @@ extern "C" int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t
   GemmParams p{};
   p.a_sf = m_sf;
   p.b_sf = w2_sf;
+  p.w_format = w_format;
   p.block_to_expert = block_to_expert;
   p.conditions = conditions;
   p.tile_flags = tile_flags;

@@ -5,6 +5,8 @@
 // 32 code bytes + 1 scale byte out).  In packed-order mode the 32 elements of
 // block (t, g) are four 8-element runs at h = q*(H/4) + t*128 + 8g (q = 0..3),
 // interleaved as p*4 + q; otherwise they are 32 consecutive columns.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -87,14 +89,47 @@ __device__ __forceinline__ int nki_logical_i(int j, int I) {
   return tile * rows + (r & 3) * (rows >> 2) + (r >> 2);
 }
 
+// The relayout kernels move one 32-element block per thread: 32 bytes of 8-bit codes (x4 words of 32 bits)
+// or, for e2m1 weights (FP4), 16 bytes of nibbles (x4 words of 16 bits).
+template <bool FP4>
+struct BlockWords {
+  using Word = typename std::conditional<FP4, uint16_t, uint32_t>::type;
+  static constexpr int kBytes = FP4 ? 16 : 32;
+  Word c[8];
+  __device__ __forceinline__ void load_contiguous(const uint8_t* src) {
+    if constexpr (FP4) {
+      const uint4 a = *reinterpret_cast<const uint4*>(src);
+      const uint32_t v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { c[2 * i] = static_cast<uint16_t>(v[i] & 0xffffu); c[2 * i + 1] = static_cast<uint16_t>(v[i] >> 16); }
+    } else {
+      const uint4 a = reinterpret_cast<const uint4*>(src)[0], b = reinterpret_cast<const uint4*>(src)[1];
+      c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+    }
+  }
+  __device__ __forceinline__ void store(uint8_t* dst) const {
+    if constexpr (FP4) {
+      *reinterpret_cast<uint4*>(dst) =
+          make_uint4(c[0] | (static_cast<uint32_t>(c[1]) << 16), c[2] | (static_cast<uint32_t>(c[3]) << 16),
+                     c[4] | (static_cast<uint32_t>(c[5]) << 16), c[6] | (static_cast<uint32_t>(c[7]) << 16));
+    } else {
+      reinterpret_cast<uint4*>(dst)[0] = make_uint4(c[0], c[1], c[2], c[3]);
+      reinterpret_cast<uint4*>(dst)[1] = make_uint4(c[4], c[5], c[6], c[7]);
+    }
+  }
+};
+
+template <bool FP4>
 __global__ void prepare_gate_up_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ scale, int layout, int E,
                                        int H, int I, uint8_t* __restrict__ w_dev, uint8_t* __restrict__ sf_dev) {
-  // one thread per (e, s, j, 32-block of H): copies 32 code bytes and 1 scale byte
+  // one thread per (e, s, j, 32-block of H): copies the block's codes and 1 scale byte
+  using BW = BlockWords<FP4>;
   const int kblocks = H >> 5;
   const int64_t k_atoms = (H + 127) >> 7;
   const int64_t sf_per_expert = ((2LL * I + 127) >> 7) * k_atoms * 512;
   const int64_t total = static_cast<int64_t>(E) * 2 * I * kblocks;
   const int nt = H >> 9;
+  const int64_t row_bytes = static_cast<int64_t>(kblocks) * BW::kBytes;
   for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int kb = static_cast<int>(idx % kblocks);
@@ -103,66 +138,61 @@ __global__ void prepare_gate_up_kernel(const uint8_t* __restrict__ w, const uint
     r /= I;
     const int s = static_cast<int>(r & 1);
     const int e = static_cast<int>(r >> 1);
-    uint32_t c[8];
+    BW blk;
     uint8_t sc;
     if (layout == B200MOE_LAYOUT_ROWS) {
-      const uint4* src = reinterpret_cast<const uint4*>(w + ((static_cast<int64_t>(e) * 2 + s) * I + j) * H + kb * 32);
-      const uint4 a = src[0], b = src[1];
-      c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+      blk.load_contiguous(w + ((static_cast<int64_t>(e) * 2 + s) * I + j) * row_bytes + kb * BW::kBytes);
       sc = scale[((static_cast<int64_t>(e) * 2 + s) * I + j) * kblocks + kb];
     } else {
       // source word (e, p, s, t, i) holds q = 0..3; block kb = 16 t + g covers p in [8g, 8g+8)
       const int i = nki_logical_i(j, I);
       const int t = kb >> 4, g = kb & 15;
-      const uint32_t* w32 = reinterpret_cast<const uint32_t*>(w);
+      const typename BW::Word* wx = reinterpret_cast<const typename BW::Word*>(w);
 #pragma unroll
       for (int pp = 0; pp < 8; ++pp)
-        c[pp] = w32[(((static_cast<int64_t>(e) * 128 + (g * 8 + pp)) * 2 + s) * nt + t) * I + i];
+        blk.c[pp] = wx[(((static_cast<int64_t>(e) * 128 + (g * 8 + pp)) * 2 + s) * nt + t) * I + i];
       sc = scale[(((static_cast<int64_t>(e) * 16 + g) * 2 + s) * nt + t) * I + i];
     }
     const int64_t row = gate_up_dev_row(s, j);
-    uint4* dst = reinterpret_cast<uint4*>(w_dev + (static_cast<int64_t>(e) * 2 * I + row) * H + kb * 32);
-    dst[0] = make_uint4(c[0], c[1], c[2], c[3]);
-    dst[1] = make_uint4(c[4], c[5], c[6], c[7]);
+    blk.store(w_dev + (static_cast<int64_t>(e) * 2 * I + row) * row_bytes + kb * BW::kBytes);
     sf_dev[e * sf_per_expert + sf_atom_offset(row, kb, k_atoms)] = sc;
   }
 }
 
+template <bool FP4>
 __global__ void prepare_down_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ scale, int layout, int E,
                                     int H, int I, uint8_t* __restrict__ w_dev, uint8_t* __restrict__ sf_dev) {
   // one thread per (e, h, 32-block of I)
+  using BW = BlockWords<FP4>;
   const int kblocks = I >> 5;
   const int64_t k_atoms = (I + 127) >> 7;
   const int64_t sf_per_expert = ((static_cast<int64_t>(H) + 127) >> 7) * k_atoms * 512;
   const int64_t total = static_cast<int64_t>(E) * H * kblocks;
   const int pI = I > 512 ? 128 : I / 4;
   const int n_tiles = I > 512 ? I / 512 : 1;
+  const int64_t row_bytes = static_cast<int64_t>(kblocks) * BW::kBytes;
   for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int kb = static_cast<int>(idx % kblocks);
     int64_t r = idx / kblocks;
     const int h = static_cast<int>(r % H);
     const int e = static_cast<int>(r / H);
-    uint32_t c[8];
+    BW blk;
     uint8_t sc;
     if (layout == B200MOE_LAYOUT_ROWS) {
-      const uint4* src = reinterpret_cast<const uint4*>(w + (static_cast<int64_t>(e) * H + h) * I + kb * 32);
-      const uint4 a = src[0], b = src[1];
-      c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+      blk.load_contiguous(w + (static_cast<int64_t>(e) * H + h) * row_bytes + kb * BW::kBytes);
       sc = scale[(static_cast<int64_t>(e) * H + h) * kblocks + kb];
     } else {
       // packed position j = tile*(pI*4) + p*4 + q; block kb covers p in [8g, 8g+8) of one tile
       const int blocks_per_tile = pI >> 3;
       const int tile = kb / blocks_per_tile, g = kb - tile * blocks_per_tile;
-      const uint32_t* w32 = reinterpret_cast<const uint32_t*>(w);
+      const typename BW::Word* wx = reinterpret_cast<const typename BW::Word*>(w);
 #pragma unroll
       for (int pp = 0; pp < 8; ++pp)
-        c[pp] = w32[((static_cast<int64_t>(e) * pI + (g * 8 + pp)) * n_tiles + tile) * H + h];
+        blk.c[pp] = wx[((static_cast<int64_t>(e) * pI + (g * 8 + pp)) * n_tiles + tile) * H + h];
       sc = scale[((static_cast<int64_t>(e) * (pI >> 3) + g) * n_tiles + tile) * H + h];
     }
-    uint4* dst = reinterpret_cast<uint4*>(w_dev + (static_cast<int64_t>(e) * H + h) * I + kb * 32);
-    dst[0] = make_uint4(c[0], c[1], c[2], c[3]);
-    dst[1] = make_uint4(c[4], c[5], c[6], c[7]);
+    blk.store(w_dev + (static_cast<int64_t>(e) * H + h) * row_bytes + kb * BW::kBytes);
     sf_dev[e * sf_per_expert + sf_atom_offset(h, kb, k_atoms)] = sc;
   }
 }
@@ -224,8 +254,16 @@ extern "C" int b200moe_gather_quantize_mxfp8(const void* hidden_bf16, int hidden
   return B200MOE_OK;
 }
 
-extern "C" int b200moe_prepare_gate_up(const void* w, const uint8_t* scale, int layout, int E, int H, int I,
+extern "C" int64_t b200moe_weight_bytes(int64_t rows, int64_t K, int w_format) {
+  return w_format == B200MOE_W_E2M1 ? rows * K / 2 : rows * K;
+}
+
+extern "C" int b200moe_prepare_gate_up(const void* w, const uint8_t* scale, int layout, int w_format, int E, int H, int I,
                                        uint8_t* w_dev, uint8_t* sf_dev, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(w_format == B200MOE_W_E4M3 || w_format == B200MOE_W_E5M2 || w_format == B200MOE_W_E2M1,
+                  B200MOE_ERR_INVALID, "prepare_gate_up: unknown weight format %d", w_format);
+  B200MOE_REQUIRE(w_format != B200MOE_W_E2M1 || H % 128 == 0, B200MOE_ERR_INVALID,
+                  "prepare_gate_up: e2m1 weights need H %% 128 == 0, got %d", H);
   B200MOE_REQUIRE(w && scale && w_dev && sf_dev, B200MOE_ERR_INVALID, "prepare_gate_up: null pointer argument");
   B200MOE_REQUIRE(layout == B200MOE_LAYOUT_ROWS || layout == B200MOE_LAYOUT_NKI_X4, B200MOE_ERR_INVALID,
                   "prepare_gate_up: unknown layout %d", layout);
@@ -235,14 +273,21 @@ extern "C" int b200moe_prepare_gate_up(const void* w, const uint8_t* scale, int 
                     "prepare_gate_up: reference storage needs H %% 512 == 0 and I %% 512 == 0 (or I < 512)");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200MOE_CUDA_OK(cudaMemsetAsync(sf_dev, 0, static_cast<size_t>(E) * b200moe_sf_bytes(2LL * I, H), st));
-  prepare_gate_up_kernel<<<grid_for(static_cast<int64_t>(E) * 2 * I * (H / 32), 256), 256, 0, st>>>(
-      static_cast<const uint8_t*>(w), scale, layout, E, H, I, w_dev, sf_dev);
+  const int grid = grid_for(static_cast<int64_t>(E) * 2 * I * (H / 32), 256);
+  if (w_format == B200MOE_W_E2M1)
+    prepare_gate_up_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(w), scale, layout, E, H, I, w_dev, sf_dev);
+  else
+    prepare_gate_up_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(w), scale, layout, E, H, I, w_dev, sf_dev);
   B200MOE_LAUNCH_OK("prepare_gate_up_kernel");
   return B200MOE_OK;
 }
 
-extern "C" int b200moe_prepare_down(const void* w, const uint8_t* scale, int layout, int E, int H, int I,
+extern "C" int b200moe_prepare_down(const void* w, const uint8_t* scale, int layout, int w_format, int E, int H, int I,
                                     uint8_t* w_dev, uint8_t* sf_dev, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(w_format == B200MOE_W_E4M3 || w_format == B200MOE_W_E5M2 || w_format == B200MOE_W_E2M1,
+                  B200MOE_ERR_INVALID, "prepare_down: unknown weight format %d", w_format);
+  B200MOE_REQUIRE(w_format != B200MOE_W_E2M1 || I % 128 == 0, B200MOE_ERR_INVALID,
+                  "prepare_down: e2m1 weights need I %% 128 == 0, got %d", I);
   B200MOE_REQUIRE(w && scale && w_dev && sf_dev, B200MOE_ERR_INVALID, "prepare_down: null pointer argument");
   B200MOE_REQUIRE(layout == B200MOE_LAYOUT_ROWS || layout == B200MOE_LAYOUT_NKI_X4, B200MOE_ERR_INVALID,
                   "prepare_down: unknown layout %d", layout);
@@ -252,8 +297,11 @@ extern "C" int b200moe_prepare_down(const void* w, const uint8_t* scale, int lay
                     "prepare_down: reference storage needs I %% 512 == 0 (or I < 512)");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200MOE_CUDA_OK(cudaMemsetAsync(sf_dev, 0, static_cast<size_t>(E) * b200moe_sf_bytes(H, I), st));
-  prepare_down_kernel<<<grid_for(static_cast<int64_t>(E) * H * (I / 32), 256), 256, 0, st>>>(
-      static_cast<const uint8_t*>(w), scale, layout, E, H, I, w_dev, sf_dev);
+  const int grid = grid_for(static_cast<int64_t>(E) * H * (I / 32), 256);
+  if (w_format == B200MOE_W_E2M1)
+    prepare_down_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(w), scale, layout, E, H, I, w_dev, sf_dev);
+  else
+    prepare_down_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(w), scale, layout, E, H, I, w_dev, sf_dev);
   B200MOE_LAUNCH_OK("prepare_down_kernel");
   return B200MOE_OK;
 }

@@ -317,12 +317,12 @@ class PeerExpertParallelMoE:
                   status, st)
         mark("t1")
         _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(self.xq), _lib.ptr(self.sf), _lib.ptr(w.w1),
-                  _lib.ptr(w.w1_sf), _lib.ptr(w.bias_gu), _lib.ptr(self.b2e), _lib.ptr(self.cond),
+                  _lib.ptr(w.w1_sf), w.w_format, _lib.ptr(w.bias_gu), _lib.ptr(self.b2e), _lib.ptr(self.cond),
                   _lib.ptr(self.tile_flags), self.n_blocks_cap, B, E_L, H, I, ops.act_fn.value, nan, nan, nan, nan,
                   _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(self.status[1:]), 0, st)
         mark("t2")
         _lib.call("b200moe_grouped_gemm2_scale", _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(w.w2),
-                  _lib.ptr(w.w2_sf), _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond),
+                  _lib.ptr(w.w2_sf), w.w_format, _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond),
                   _lib.ptr(self.tile_flags), _lib.ptr(self.row_valid), self.cap_rows, self.n_blocks_cap, B, E_L, H, I,
                   _lib.ptr(self.row_aff), _lib.F32, 1, _lib.ptr(self.y_pos), _lib.ptr(self.status[2:]), 0, st)
         mark("t3")

@@ -82,11 +82,11 @@ class MoELayer:
             int(w.h_packed_order), _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(ws.tile_flags), st))
         nan = float("nan")
         timed("gemm1_swiglu", lambda: _lib.call(
-            "b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(w.w1), _lib.ptr(w.w1_sf),
+            "b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(w.w1), _lib.ptr(w.w1_sf), w.w_format,
             _lib.ptr(w.bias_gu), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(ws.tile_flags), N, B, E, H, I,
             self.act_fn.value, nan, nan, nan, nan, _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(ws.status[1:]), 0, st))
         timed("gemm2_scale", lambda: _lib.call(
-            "b200moe_grouped_gemm2_scale", _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(w.w2), _lib.ptr(w.w2_sf),
+            "b200moe_grouped_gemm2_scale", _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(w.w2), _lib.ptr(w.w2_sf), w.w_format,
             _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(ws.tile_flags), _lib.ptr(self.tpi),
             T, N, B, E, H, I, _lib.ptr(self.aff), _lib.F32, 0, _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), 0, st))
         timed("combine", lambda: _lib.call(
@@ -113,16 +113,35 @@ class MoELayer:
         return [int(self.gstatus.item())] + self.ws.status.cpu().tolist()[1:3]
 
 
-def random_expert_weights(E: int, H: int, I: int, device, seed: int = 0, std: float = 0.02) -> ExpertWeights:
-    """Synthetic MXFP8 expert weights, generated and quantised on the device.
+def random_expert_weights(E: int, H: int, I: int, device, seed: int = 0, std: float = 0.02,
+                          w_format: int = _lib.W_E4M3) -> ExpertWeights:
+    """Synthetic MX expert weights, generated on the device directly in the feed layout.
 
-    bf16 values ~ N(0, std) are pushed through the library's own MXFP8
-    quantiser (block-32 UE8M0 scales along the contraction axis), directly in
-    the feed layout; rows are i.i.d., so no relayout is needed.
+    e4m3: bf16 values ~ N(0, std) are pushed through the library's own MXFP8
+    quantiser (block-32 UE8M0 scales along the contraction axis); rows are
+    i.i.d., so no relayout is needed.  e5m2 / e2m1: uniformly random finite
+    element codes with block scales of 2^-9 .. 2^-6, which gives weights of the
+    same order of magnitude.
     """
     lib = _lib.load_library()
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
+    if w_format != _lib.W_E4M3:
+        per = 2 if w_format == _lib.W_E2M1 else 1
+
+        def codes(rows, K):
+            if w_format == _lib.W_E2M1:
+                return torch.randint(0, 256, (E, rows, K // per), dtype=torch.uint8, device=device, generator=gen)
+            sign = torch.randint(0, 2, (E, rows, K), dtype=torch.uint8, device=device, generator=gen) << 7
+            expo = torch.randint(9, 17, (E, rows, K), dtype=torch.uint8, device=device, generator=gen) << 2
+            return sign | expo | torch.randint(0, 4, (E, rows, K), dtype=torch.uint8, device=device, generator=gen)
+
+        def scales(rows, K):
+            return torch.randint(118, 122, (E * lib.b200moe_sf_bytes(rows, K),), dtype=torch.uint8, device=device,
+                                 generator=gen)
+
+        return ExpertWeights(E, H, I, codes(2 * I, H), scales(2 * I, H), codes(H, I), scales(H, I), None, None, False,
+                             w_format)
     w1 = torch.empty((E, 2 * I, H), dtype=torch.uint8, device=device)
     w2 = torch.empty((E, H, I), dtype=torch.uint8, device=device)
     sf1_e, sf2_e = lib.b200moe_sf_bytes(2 * I, H), lib.b200moe_sf_bytes(H, I)

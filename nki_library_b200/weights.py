@@ -10,6 +10,11 @@ Two sources are accepted:
   that order and the activation quantiser gathers hidden columns to match.
 * plain rows: fp8 codes ``[E, 2, I, H]`` / ``[E, H, I]`` with one UE8M0 scale per
   32 consecutive contraction elements.
+
+Weights may be e4m3 (default), e5m2 or e2m1 (MXFP4: two elements per byte, so
+every contraction axis above is half as many bytes); activations are always
+quantised to e4m3, as the reference's ``quantize_mx`` does
+(core/utils/mx_torch_common.py:31-133 for the three element types).
 """
 
 from __future__ import annotations
@@ -34,6 +39,7 @@ class ExpertWeights:
     bias_gu: Optional[torch.Tensor]  # fp32 [E, 2I] in w1 row order
     bias_d: Optional[torch.Tensor]   # fp32 [E, H]
     h_packed_order: bool   # hidden columns must be gathered in the reference's packed order
+    w_format: int = 0      # element format of w1 / w2: _lib.W_E4M3, W_E5M2 or W_E2M1 (nibbles)
 
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w1, self.w1_sf, self.w2, self.w2_sf))
@@ -44,19 +50,37 @@ def _as_u8(t: torch.Tensor) -> torch.Tensor:
     return t if t.dtype == torch.uint8 else t.view(torch.uint8)
 
 
-def _prepare(w1, s1, w2, s2, bias_gu, bias_d, layout, E, H, I) -> ExpertWeights:
+def _format_of(w_format, tensor, bytes_8bit) -> int:
+    """Resolve a weight format from an explicit name/code, else from the tensor's dtype and size."""
+    names = {"e4m3": _lib.W_E4M3, "e5m2": _lib.W_E5M2, "e2m1": _lib.W_E2M1, "mxfp8": _lib.W_E4M3, "mxfp4": _lib.W_E2M1}
+    if w_format is not None:
+        code = names.get(w_format, w_format) if isinstance(w_format, str) else int(w_format)
+        _lib.kernel_assert(code in (_lib.W_E4M3, _lib.W_E5M2, _lib.W_E2M1), f"unknown weight format {w_format!r}")
+        return code
+    nbytes = tensor.numel() * tensor.element_size()
+    if nbytes * 2 == bytes_8bit:
+        return _lib.W_E2M1
+    return _lib.W_E5M2 if tensor.dtype == torch.float8_e5m2 else _lib.W_E4M3
+
+
+def _prepare(w1, s1, w2, s2, bias_gu, bias_d, layout, E, H, I, w_format=_lib.W_E4M3) -> ExpertWeights:
     _lib.require_cuda(w1, s1, w2, s2, bias_gu, bias_d)
     dev = w1.device
     lib = _lib.load_library()
     st = _lib.stream_ptr()
-    w1_dev = torch.empty((E, 2 * I, H), dtype=torch.uint8, device=dev)
+    per = 2 if w_format == _lib.W_E2M1 else 1  # elements per byte
+    _lib.kernel_assert(per == 1 or (H % 128 == 0 and I % 128 == 0), "e2m1 weights need H and I to be multiples of 128")
+    _lib.kernel_assert(w1.numel() * w1.element_size() * per == E * 2 * I * H and
+                       w2.numel() * w2.element_size() * per == E * I * H,
+                       "weight tensors do not hold E*2*I*H / E*I*H elements of the given format")
+    w1_dev = torch.empty((E, 2 * I, H // per), dtype=torch.uint8, device=dev)
     w1_sf = torch.empty(E * lib.b200moe_sf_bytes(2 * I, H), dtype=torch.uint8, device=dev)
-    w2_dev = torch.empty((E, H, I), dtype=torch.uint8, device=dev)
+    w2_dev = torch.empty((E, H, I // per), dtype=torch.uint8, device=dev)
     w2_sf = torch.empty(E * lib.b200moe_sf_bytes(H, I), dtype=torch.uint8, device=dev)
     w1u, s1u, w2u, s2u = _as_u8(w1), _as_u8(s1), _as_u8(w2), _as_u8(s2)
-    _lib.call("b200moe_prepare_gate_up", _lib.ptr(w1u), _lib.ptr(s1u), layout, E, H, I, _lib.ptr(w1_dev),
+    _lib.call("b200moe_prepare_gate_up", _lib.ptr(w1u), _lib.ptr(s1u), layout, w_format, E, H, I, _lib.ptr(w1_dev),
               _lib.ptr(w1_sf), st)
-    _lib.call("b200moe_prepare_down", _lib.ptr(w2u), _lib.ptr(s2u), layout, E, H, I, _lib.ptr(w2_dev),
+    _lib.call("b200moe_prepare_down", _lib.ptr(w2u), _lib.ptr(s2u), layout, w_format, E, H, I, _lib.ptr(w2_dev),
               _lib.ptr(w2_sf), st)
     b_gu = None
     if bias_gu is not None:
@@ -66,21 +90,29 @@ def _prepare(w1, s1, w2, s2, bias_gu, bias_d, layout, E, H, I) -> ExpertWeights:
         b_gu = torch.empty((E, 2 * I), dtype=torch.float32, device=dev)
         _lib.call("b200moe_prepare_gate_up_bias", _lib.ptr(src), _lib.dtype_code(src), layout, E, I, _lib.ptr(b_gu), st)
     b_d = None if bias_d is None else bias_d.reshape(E, H).float().contiguous()
-    return ExpertWeights(E, H, I, w1_dev, w1_sf, w2_dev, w2_sf, b_gu, b_d, layout == _lib.LAYOUT_NKI_X4)
+    return ExpertWeights(E, H, I, w1_dev, w1_sf, w2_dev, w2_sf, b_gu, b_d, layout == _lib.LAYOUT_NKI_X4, w_format)
 
 
-def prepare_from_rows(w1_codes, w1_scales, w2_codes, w2_scales, bias_gu=None, bias_d=None) -> ExpertWeights:
-    """``w1_codes [E, 2, I, H]``, ``w1_scales [E, 2, I, H/32]``, ``w2_codes [E, H, I]``, ``w2_scales [E, H, I/32]``."""
-    E, two, I, H = w1_codes.shape
-    _lib.kernel_assert(two == 2 and tuple(w2_codes.shape) == (E, H, I), "gate_up must be [E,2,I,H] and down [E,H,I]")
+def prepare_from_rows(w1_codes, w1_scales, w2_codes, w2_scales, bias_gu=None, bias_d=None,
+                      w_format=None) -> ExpertWeights:
+    """``w1_codes [E, 2, I, H]``, ``w1_scales [E, 2, I, H/32]``, ``w2_codes [E, H, I]``, ``w2_scales [E, H, I/32]``;
+    with ``w_format="e2m1"`` the code tensors are ``[E, 2, I, H/2]`` and ``[E, H, I/2]`` bytes."""
+    E, two, I, _ = w1_scales.shape
+    H = w2_scales.shape[1]
+    fmt = _format_of(w_format, w1_codes, E * 2 * I * H)
+    per = 2 if fmt == _lib.W_E2M1 else 1
+    _lib.kernel_assert(two == 2 and tuple(w1_codes.shape) == (E, 2, I, H // per) and
+                       tuple(w2_codes.shape) == (E, H, I // per), "gate_up must be [E,2,I,H] and down [E,H,I]")
     _lib.kernel_assert(tuple(w1_scales.shape) == (E, 2, I, H // 32) and tuple(w2_scales.shape) == (E, H, I // 32),
                        "scales must hold one byte per 32 contraction elements")
-    return _prepare(w1_codes, w1_scales, w2_codes, w2_scales, bias_gu, bias_d, _lib.LAYOUT_ROWS, E, H, I)
+    return _prepare(w1_codes, w1_scales, w2_codes, w2_scales, bias_gu, bias_d, _lib.LAYOUT_ROWS, E, H, I, fmt)
 
 
 def prepare_from_nki(gate_up_proj_weight, gate_up_proj_scale, down_proj_weight, down_proj_scale,
-                     gate_and_up_proj_bias=None, down_proj_bias=None) -> ExpertWeights:
-    """Reference storage -> feed format.  Shapes are taken from the scale tensors."""
+                     gate_and_up_proj_bias=None, down_proj_bias=None, w_format=None) -> ExpertWeights:
+    """Reference storage -> feed format.  Shapes are taken from the scale tensors; the element format from
+    ``w_format`` or, when None, from the weight tensor (half the fp8 byte count = e2m1, ``torch.float8_e5m2`` =
+    e5m2, anything else e4m3)."""
     _lib.kernel_assert(gate_up_proj_scale is not None and down_proj_scale is not None,
                        "MX weights need gate_up_proj_scale and down_proj_scale")
     E, sixteen, two, nt, I = gate_up_proj_scale.shape
@@ -90,27 +122,29 @@ def prepare_from_nki(gate_up_proj_weight, gate_up_proj_scale, down_proj_weight, 
     n_tiles = I // 512 if I > 512 else 1
     _lib.kernel_assert(tuple(down_proj_scale.shape) == (E, pI // 8, n_tiles, H),
                        f"down_proj_scale must be {(E, pI // 8, n_tiles, H)}, got {tuple(down_proj_scale.shape)}")
-    _lib.kernel_assert(gate_up_proj_weight.numel() * gate_up_proj_weight.element_size() == E * 2 * I * H,
-                       "gate_up_proj_weight must hold E*2*I*H fp8 bytes (x4-packed)")
-    _lib.kernel_assert(down_proj_weight.numel() * down_proj_weight.element_size() == E * I * H,
-                       "down_proj_weight must hold E*I*H fp8 bytes (x4-packed)")
+    fmt = _format_of(w_format, gate_up_proj_weight, E * 2 * I * H)
+    per = 2 if fmt == _lib.W_E2M1 else 1
+    _lib.kernel_assert(gate_up_proj_weight.numel() * gate_up_proj_weight.element_size() * per == E * 2 * I * H,
+                       "gate_up_proj_weight must hold E*2*I*H x4-packed elements")
+    _lib.kernel_assert(down_proj_weight.numel() * down_proj_weight.element_size() * per == E * I * H,
+                       "down_proj_weight must hold E*I*H x4-packed elements")
     return _prepare(gate_up_proj_weight, gate_up_proj_scale, down_proj_weight, down_proj_scale,
-                    gate_and_up_proj_bias, down_proj_bias, _lib.LAYOUT_NKI_X4, E, H, I)
+                    gate_and_up_proj_bias, down_proj_bias, _lib.LAYOUT_NKI_X4, E, H, I, fmt)
 
 
 _cache: dict = {}
 
 
 def prepare_from_nki_cached(gate_up_proj_weight, gate_up_proj_scale, down_proj_weight, down_proj_scale,
-                            gate_and_up_proj_bias=None, down_proj_bias=None) -> ExpertWeights:
+                            gate_and_up_proj_bias=None, down_proj_bias=None, w_format=None) -> ExpertWeights:
     """Memoised on the identity and version of the source tensors (weights are static during inference)."""
     srcs = (gate_up_proj_weight, gate_up_proj_scale, down_proj_weight, down_proj_scale, gate_and_up_proj_bias,
             down_proj_bias)
-    key = tuple((t.data_ptr(), tuple(t.shape), t._version) if t is not None else None for t in srcs)
+    key = tuple((t.data_ptr(), tuple(t.shape), t._version) if t is not None else None for t in srcs) + (w_format,)
     hit = _cache.get(key)
     if hit is None:
         if len(_cache) > 8:
             _cache.clear()
-        hit = prepare_from_nki(*srcs)
+        hit = prepare_from_nki(*srcs, w_format=w_format)
         _cache[key] = hit
     return hit

@@ -56,11 +56,14 @@ def _mm(a: np.ndarray, b_t: np.ndarray) -> np.ndarray:
 
 
 class ExpertWeights:
-    """Dequantised fp32 weights of one expert: ``w1 [2, I, H]``, ``w2 [H, I]``."""
+    """Dequantised fp32 weights of one expert: ``w1 [2, I, H]``, ``w2 [H, I]``.
 
-    def __init__(self, w1_codes, w1_scales, w2_codes, w2_scales, e):
-        self.w1 = mx.dequantize_mx_rows(w1_codes[e], w1_scales[e])
-        self.w2 = mx.dequantize_mx_rows(w2_codes[e], w2_scales[e])
+    ``fmt`` is the element type of the codes ("e4m3", "e5m2" or "e2m1", one code per array element);
+    activations are quantised to e4m3 whatever the weights are (moe_tkg_torch.py:364-370)."""
+
+    def __init__(self, w1_codes, w1_scales, w2_codes, w2_scales, e, fmt="e4m3"):
+        self.w1 = mx.dequantize_mx_rows(w1_codes[e], w1_scales[e], fmt)
+        self.w2 = mx.dequantize_mx_rows(w2_codes[e], w2_scales[e], fmt)
 
 
 def expert_mlp_rows(x, ew: ExpertWeights, bias_gu=None, bias_d=None, act=SILU,
@@ -97,7 +100,7 @@ def expert_mlp_rows(x, ew: ExpertWeights, bias_gu=None, bias_d=None, act=SILU,
 def moe_cte_rows(hidden, affinities, w1_codes, w1_scales, w2_codes, w2_scales,
                  token_position_to_id, block_to_expert, block_size, conditions=None,
                  bias_gu=None, bias_d=None, act=SILU, gate_clamp=(None, None), up_clamp=(None, None),
-                 h_order=None, post_scale=True, round_inter_bf16=True, max_blocks=None):
+                 h_order=None, post_scale=True, round_inter_bf16=True, max_blocks=None, w_fmt="e4m3"):
     """Prefill layer: ``out[T, H]`` fp32 (caller casts to bf16).
 
     ``hidden [T or T+1, H]`` fp32 values; ``affinities [rows, E]`` fp32 values;
@@ -126,7 +129,7 @@ def moe_cte_rows(hidden, affinities, w1_codes, w1_scales, w2_codes, w2_scales,
             continue
         e = int(block_to_expert[b])
         if e != cache_e:
-            ew = ExpertWeights(w1_codes, w1_scales, w2_codes, w2_scales, e)
+            ew = ExpertWeights(w1_codes, w1_scales, w2_codes, w2_scales, e, w_fmt)
             cache_e = e
         tok = ids[valid]
         x = hidden[tok]
@@ -143,7 +146,7 @@ def moe_cte_rows(hidden, affinities, w1_codes, w1_scales, w2_codes, w2_scales,
 def moe_tkg_rows(hidden, affinities, expert_index, w1_codes, w1_scales, w2_codes, w2_scales,
                  bias_gu=None, bias_d=None, act=SILU, gate_clamp=(None, None), up_clamp=(None, None),
                  h_order=None, post_scale=True, round_inter_bf16=True, is_all_expert=False,
-                 expert_offset=0):
+                 expert_offset=0, w_fmt="e4m3"):
     """Decode layer, fp32 ``[T, H]``: every (token, k) pair runs its expert on that token alone.
 
     Selective mode follows moe_tkg_torch.py:432-440 (pairs are independent, so
@@ -165,7 +168,7 @@ def moe_tkg_rows(hidden, affinities, expert_index, w1_codes, w1_scales, w2_codes
             tok = np.flatnonzero((idx == ge).any(axis=1))
         if tok.size == 0:
             continue
-        ew = ExpertWeights(w1_codes, w1_scales, w2_codes, w2_scales, e)
+        ew = ExpertWeights(w1_codes, w1_scales, w2_codes, w2_scales, e, w_fmt)
         y = expert_mlp_rows(x_all[tok], ew, None if bias_gu is None else bias_gu[e],
                             None if bias_d is None else bias_d[e], act, gate_clamp, up_clamp, round_inter_bf16)
         if post_scale:

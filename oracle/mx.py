@@ -79,6 +79,63 @@ def e4m3_decode(codes: np.ndarray) -> np.ndarray:
     return _E4M3_LUT[np.asarray(codes, dtype=np.uint8)]
 
 
+def _build_e5m2_lut() -> np.ndarray:
+    """float8_e5m2 byte -> float32: S(1) E(5) M(2), bias 15 (mx_torch_common.py:85-105; like the
+    reference's unpack, exponent 31 is decoded as an ordinary binade rather than inf/NaN)."""
+    b = np.arange(256, dtype=np.int32)
+    s = (b >> 7) & 1
+    e = (b >> 2) & 0x1F
+    m = b & 0x3
+    sub = (m / 4.0) * 2.0**-14
+    nor = (1.0 + m / 4.0) * np.power(2.0, e.astype(np.float64) - 15.0)
+    v = np.where(e == 0, sub, nor)
+    return np.where(s == 1, -v, v).astype(np.float32)
+
+
+_E5M2_LUT = _build_e5m2_lut()
+# float4_e2m1fn nibble -> float32: S(1) E(2) M(1), bias 1, finite only (mx_torch_common.py:31-67)
+_E2M1_LUT = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0],
+                     dtype=np.float32)
+
+FORMATS = ("e4m3", "e5m2", "e2m1")
+
+
+def e5m2_decode(codes: np.ndarray) -> np.ndarray:
+    return _E5M2_LUT[np.asarray(codes, dtype=np.uint8)]
+
+
+def e2m1_decode(nibbles: np.ndarray) -> np.ndarray:
+    """One 4-bit code per array element (values 0..15) -> float32."""
+    return _E2M1_LUT[np.asarray(nibbles, dtype=np.uint8) & 0xF]
+
+
+def decode_elements(codes: np.ndarray, fmt: str = "e4m3") -> np.ndarray:
+    """Element codes (one per array element, whatever the storage width) -> float32."""
+    if fmt == "e4m3":
+        return e4m3_decode(codes)
+    if fmt == "e5m2":
+        return e5m2_decode(codes)
+    if fmt == "e2m1":
+        return e2m1_decode(codes)
+    raise ValueError(fmt)
+
+
+def pack_e2m1(nibbles: np.ndarray) -> np.ndarray:
+    """``[..., K]`` nibbles -> ``[..., K/2]`` bytes, element 2j in the low half of byte j.  This is also the
+    memory image of the reference's float4_e2m1fn_x4 words (16 bits, element j in bits 4j..4j+3;
+    mx_torch_common.py:70-82)."""
+    n = np.asarray(nibbles, dtype=np.uint8) & 0xF
+    return (n[..., 0::2] | (n[..., 1::2] << 4)).astype(np.uint8)
+
+
+def unpack_e2m1(packed: np.ndarray) -> np.ndarray:
+    b = np.asarray(packed, dtype=np.uint8)
+    out = np.empty(b.shape[:-1] + (b.shape[-1] * 2,), dtype=np.uint8)
+    out[..., 0::2] = b & 0xF
+    out[..., 1::2] = b >> 4
+    return out
+
+
 # --------------------------------------------------------------------------
 # block quantisation
 # --------------------------------------------------------------------------
@@ -128,12 +185,13 @@ def quantize_to_mx_ref_blocks(data: np.ndarray):
     return e4m3_encode(q.astype(np.float32)), scales
 
 
-def dequantize_mx_rows(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
-    """``x_hat = decode(code) * 2**(scale - 127)`` per 32-block (mx_torch_common.py:146-152)."""
+def dequantize_mx_rows(codes: np.ndarray, scales: np.ndarray, fmt: str = "e4m3") -> np.ndarray:
+    """``x_hat = decode(code) * 2**(scale - 127)`` per 32-block (mx_torch_common.py:146-152).
+    ``codes`` holds one element code per array element (e2m1: unpacked nibbles)."""
     codes = np.asarray(codes, dtype=np.uint8)
     lead = codes.shape[:-1]
     K = codes.shape[-1]
-    v = e4m3_decode(codes).reshape(*lead, K // BLOCK, BLOCK)
+    v = decode_elements(codes, fmt).reshape(*lead, K // BLOCK, BLOCK)
     f = np.power(2.0, scales.astype(np.float32) - 127.0).astype(np.float32)
     return (v * f[..., None]).reshape(*lead, K)
 
@@ -228,7 +286,17 @@ def ref_gate_up_bias_to_rows(bias: np.ndarray) -> np.ndarray:
     return np.ascontiguousarray(b.transpose(0, 2, 3, 1, 4).reshape(E, 2, nt * P * 4))
 
 
-def rows_to_ref_gate_up(codes: np.ndarray, scales: np.ndarray):
+def _x4_words(c4: np.ndarray, fmt: str) -> np.ndarray:
+    """``[..., 4]`` element codes -> the reference's x4 word per group: 32 bits of four bytes, or for e2m1
+    16 bits of four nibbles (element j in bits 4j..4j+3)."""
+    c4 = np.ascontiguousarray(c4, dtype=np.uint8)
+    if fmt == "e2m1":
+        c = c4.astype(np.uint16) & 0xF
+        return (c[..., 0] | (c[..., 1] << 4) | (c[..., 2] << 8) | (c[..., 3] << 12)).astype(np.uint16)
+    return c4.view(np.uint32).reshape(c4.shape[:-1])
+
+
+def rows_to_ref_gate_up(codes: np.ndarray, scales: np.ndarray, fmt: str = "e4m3"):
     """Inverse of ``ref_gate_up_to_rows`` (used to fabricate reference-format test inputs)."""
     E, two, I, H = codes.shape
     nt = H // 512
@@ -237,16 +305,16 @@ def rows_to_ref_gate_up(codes: np.ndarray, scales: np.ndarray):
     inv[perm] = np.arange(I)
     c = codes[:, :, inv, :].reshape(E, 2, I, nt, 128, 4).transpose(0, 4, 1, 3, 2, 5)
     s = scales[:, :, inv, :].reshape(E, 2, I, nt, 16).transpose(0, 4, 1, 3, 2)
-    w = np.ascontiguousarray(c).view(np.uint32).reshape(E, 128, 2, nt, I)
+    w = _x4_words(c, fmt).reshape(E, 128, 2, nt, I)
     return w, np.ascontiguousarray(s)
 
 
-def rows_to_ref_down(codes: np.ndarray, scales: np.ndarray):
+def rows_to_ref_down(codes: np.ndarray, scales: np.ndarray, fmt: str = "e4m3"):
     """Inverse of ``ref_down_to_rows``."""
     E, H, I = codes.shape
     P = 128 if I > 512 else I // 4
     nt = I // (P * 4)
     c = codes.reshape(E, H, nt, P, 4).transpose(0, 3, 2, 1, 4)
     s = scales.reshape(E, H, nt, P // 8).transpose(0, 3, 2, 1)
-    w = np.ascontiguousarray(c).view(np.uint32).reshape(E, P, nt, H)
+    w = _x4_words(c, fmt).reshape(E, P, nt, H)
     return w, np.ascontiguousarray(s)

@@ -4,6 +4,13 @@ Run once, in a container that has the reference checkout, as
 
     python tests/golden/make_golden.py /path/to/reference
 
+It also runs the reference's element decoders ``unpack_float4_x4``,
+``unpack_float8_e5m2_x4`` and ``unpack_float8_e4m3fn_x4``
+(``core/utils/mx_torch_common.py:31-131``) over every 16-bit fp4 word and every
+fp8 byte; their module imports the Trainium toolchain at the top, so the three
+functions (and the lookup table they use) are compiled on their own from the
+module's source.
+
 It imports the three reference torch references that load without the Trainium
 toolchain (``router_topk_torch_ref``, ``find_nonzero_indices_torch_ref``,
 ``indexed_flatten_torch_ref``), feeds them the seed-generated inputs of the
@@ -17,6 +24,7 @@ path) against these files without needing the reference checkout.
 
 from __future__ import annotations
 
+import ast
 import hashlib
 import json
 import os
@@ -34,7 +42,35 @@ def digest(a: np.ndarray) -> str:
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
 
+def load_functions(path: str, names) -> dict:
+    """Compile the named top-level functions / assignments of a module without running the rest of it."""
+    with open(path) as f:
+        tree = ast.parse(f.read())
+    keep = []
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name in names:
+            keep.append(node)
+        elif isinstance(node, ast.Assign) and any(getattr(t, "id", None) in names for t in node.targets):
+            keep.append(node)
+    ns = {"torch": torch, "np": np}
+    exec(compile(ast.Module(keep, []), path, "exec"), ns)
+    return ns
+
+
+def element_decoders(ref_root: str) -> None:
+    ns = load_functions(os.path.join(ref_root, "src", "nkilib_src", "nkilib", "core", "utils", "mx_torch_common.py"),
+                        {"_FP4_LUT", "unpack_float4_x4", "unpack_float8_e5m2_x4", "unpack_float8_e4m3fn_x4"})
+    words16 = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    bytes_all = np.arange(256, dtype=np.uint8).view(np.uint32).reshape(1, 64)
+    np.savez_compressed(
+        os.path.join(HERE, "mx_element_decode_ref.npz"),
+        e2m1_x4=ns["unpack_float4_x4"](words16).numpy().astype(np.float32),          # [256, 1024]
+        e5m2_x4=ns["unpack_float8_e5m2_x4"](bytes_all).numpy().astype(np.float32),   # [1, 256]
+        e4m3_x4=ns["unpack_float8_e4m3fn_x4"](bytes_all).numpy().astype(np.float32))
+
+
 def main(ref_root: str) -> None:
+    element_decoders(ref_root)
     sys.path.insert(0, os.path.join(ref_root, "src"))
     from nkilib_src.nkilib.core.router_topk.router_topk_torch import router_topk_torch_ref
     from nkilib_src.nkilib.core.subkernels.find_nonzero_indices_torch import find_nonzero_indices_torch_ref

@@ -23,6 +23,25 @@ def make_rows_weights(E, H, I, seed=0, std=0.02):
     return (c1.reshape(E, 2, I, H), s1.reshape(E, 2, I, H // 32), c2.reshape(E, H, I), s2.reshape(E, H, I // 32))
 
 
+def make_rows_weights_fmt(E, H, I, fmt, seed=0):
+    """Expert weights of element type ``fmt`` as random finite element codes (one per array element; e2m1
+    codes are nibbles 0..15) with block scales 2^-9 .. 2^-6: same shapes as ``make_rows_weights``."""
+    if fmt == "e4m3":
+        return make_rows_weights(E, H, I, seed)
+    rng = np.random.default_rng(seed)
+
+    def codes(shape):
+        if fmt == "e2m1":
+            return rng.integers(0, 16, shape, dtype=np.uint8)
+        sign = rng.integers(0, 2, shape, dtype=np.uint8) << 7
+        return (sign | (rng.integers(9, 17, shape, dtype=np.uint8) << 2) | rng.integers(0, 4, shape, dtype=np.uint8))
+
+    def scales(shape):
+        return rng.integers(118, 122, shape, dtype=np.uint8)
+
+    return (codes((E, 2, I, H)), scales((E, 2, I, H // 32)), codes((E, H, I)), scales((E, H, I // 32)))
+
+
 def make_routing(T, H, E, K, seed=0, zipf_s=None):
     """hidden bf16 values [T,H], softmax-normalised top-K affinities [T,E] (fp32), expert_index [T,K]."""
     rng = np.random.default_rng(seed + 1000)

@@ -34,7 +34,7 @@ def _run_gemm1(m, weights, x_np, b2e_np, B, impl, act=0, clamps=(None,) * 4):
               _lib.ptr(ws.x_sf), _lib.ptr(ws.tile_flags), st)
     c = [pipeline._clamp(v) for v in clamps]
     _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(weights.w1),
-              _lib.ptr(weights.w1_sf), _lib.ptr(weights.bias_gu), _lib.ptr(b2e), None, _lib.ptr(ws.tile_flags),
+              _lib.ptr(weights.w1_sf), weights.w_format, _lib.ptr(weights.bias_gu), _lib.ptr(b2e), None, _lib.ptr(ws.tile_flags),
               len(b2e_np), B, weights.E, H, weights.I, act, c[0], c[1], c[2], c[3], _lib.ptr(ws.mq), _lib.ptr(ws.m_sf),
               _lib.ptr(ws.status[1:]), impl, st)
     torch.cuda.synchronize()
@@ -296,3 +296,85 @@ def test_moe_block_tkg_vs_oracle(with_residual):
     np.testing.assert_allclose(outs[1].cpu().numpy(), logits.numpy(), rtol=0, atol=2e-2 * np.abs(logits.numpy()).max())
     ref = moe.moe_tkg_rows(normed, aff.numpy(), idx.numpy(), *w_np)
     assert max_rel(outs[0].float().cpu().numpy(), bf16_values(ref)) <= 3e-2  # bf16 RMSNorm rounding can move a row
+
+
+# ---- weights in the reference's other MX element types: float8_e5m2_x4 and float4_e2m1fn_x4 (MXFP4) ----------
+def _prep_fmt(m, w_np, fmt, bias_gu=None, bias_d=None):
+    c1, s1, c2, s2 = w_np
+    if fmt == "e2m1":
+        c1, c2 = mx.pack_e2m1(c1), mx.pack_e2m1(c2)
+    t = [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in (c1, s1, c2, s2)]
+    return m.prepare_from_rows(*t, bias_gu=None if bias_gu is None else torch.from_numpy(bias_gu).cuda(),
+                               bias_d=None if bias_d is None else torch.from_numpy(bias_d).cuda(), w_format=fmt)
+
+
+def _fmt_case(T, H, I, E, K, seed, fmt, bias=True):
+    from moe_testlib import make_rows_weights_fmt
+    hidden, _, _, idx, aff = make_routing(T, H, E, K, seed)
+    w_np = make_rows_weights_fmt(E, H, I, fmt, seed)
+    rng = np.random.default_rng(seed + 7)
+    bgu = rng.uniform(-1.0, 0.5, (E, 2, I)).astype(np.float32) if bias else None
+    bd = rng.uniform(-1.0, 1.0, (E, H)).astype(np.float32) if bias else None
+    return hidden, idx, aff, w_np, bgu, bd
+
+
+@pytest.mark.parametrize("impl", [1, 0])
+@pytest.mark.parametrize("fmt,B,T", [("e5m2", 128, 256), ("e2m1", 128, 256), ("e2m1", 256, 700)])
+def test_moe_cte_other_weight_formats(impl, fmt, B, T):
+    """e4m3 activations against e5m2 / e2m1 weights, single-CTA (B=128) and CTA-pair (B=256) tiles."""
+    import nki_library_b200 as m
+    H, I, E, K = 512, 1024, 4, 2
+    hidden, idx, aff, w_np, bgu, bd = _fmt_case(T, H, I, E, K, 71, fmt)
+    weights = _prep_fmt(m, w_np, fmt, bgu, bd)
+    assert weights.w1.shape[-1] == (H // 2 if fmt == "e2m1" else H)
+    N = m.get_n_blocks(T, K, E, B)
+    g = m.moe_group_tokens(torch.from_numpy(idx).cuda(), E, B, N, check=True)
+    out = m.moe_cte(torch.from_numpy(hidden).to(torch.bfloat16).cuda(), torch.from_numpy(aff).cuda().reshape(-1, 1),
+                    weights, None, g["token_position_to_id"], g["block_to_expert"], B,
+                    m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx), conditions=g["conditions"],
+                    skip_dma=m.SkipMode(True, False), _impl=impl, _check_status=True)
+    ref = moe.moe_cte_rows(hidden, aff, *w_np, g["token_position_to_id"].cpu().numpy(),
+                           g["block_to_expert"].cpu().numpy(), B, g["conditions"].cpu().numpy(), bgu, bd, w_fmt=fmt)
+    assert max_rel(out.float().cpu().numpy(), bf16_values(ref)) <= TOL
+
+
+@pytest.mark.parametrize("fmt", ["e5m2", "e2m1"])
+def test_moe_cte_reference_storage_other_formats(fmt):
+    """x4 words of the reference storage: 32 bits of e5m2 bytes (typed torch.float8_e5m2) or 16 bits of e2m1 nibbles."""
+    import nki_library_b200 as m
+    T, H, I, E, K, B = 200, 1024, 512, 4, 2, 128
+    hidden, idx, aff, w_np, _, bd = _fmt_case(T, H, I, E, K, 73, fmt)
+    gw, gs = mx.rows_to_ref_gate_up(w_np[0], w_np[1], fmt)
+    dw, ds = mx.rows_to_ref_down(w_np[2], w_np[3], fmt)
+    if fmt == "e2m1":
+        gw_t, dw_t = torch.from_numpy(gw.view(np.int16)).cuda(), torch.from_numpy(dw.view(np.int16)).cuda()
+    else:
+        gw_t = torch.from_numpy(gw.view(np.uint8)).cuda().view(torch.float8_e5m2)
+        dw_t = torch.from_numpy(dw.view(np.uint8)).cuda().view(torch.float8_e5m2)
+    N = m.get_n_blocks(T, K, E, B, 2)
+    g = m.moe_group_tokens(torch.from_numpy(idx).cuda(), E, B, N, check=True)
+    out = m.moe_cte(torch.from_numpy(hidden).to(torch.bfloat16).cuda(), torch.from_numpy(aff).cuda().reshape(-1, 1),
+                    gw_t, dw_t, g["token_position_to_id"], g["block_to_expert"], B,
+                    m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx), conditions=g["conditions"],
+                    down_proj_bias=torch.from_numpy(bd).cuda(),
+                    quantization_config=m.QuantizationConfig(torch.from_numpy(gs).cuda(), torch.from_numpy(ds).cuda()),
+                    skip_dma=m.SkipMode(True, False), _check_status=True)
+    ref = moe.moe_cte_rows(hidden, aff, *w_np, g["token_position_to_id"].cpu().numpy(),
+                           g["block_to_expert"].cpu().numpy(), B, g["conditions"].cpu().numpy(), None, bd,
+                           h_order=mx.hidden_packed_order(H), w_fmt=fmt)
+    assert max_rel(out.float().cpu().numpy(), bf16_values(ref)) <= TOL
+
+
+@pytest.mark.parametrize("fmt", ["e5m2", "e2m1"])
+def test_moe_tkg_other_weight_formats(fmt):
+    """Decode with MXFP4 / e5m2 expert weights (the reference's selective-expert MXFP4 path,
+    core/moe/moe_tkg/selective_expert_mx_impl.py:51-518, quantises activations to e4m3 all the same)."""
+    import nki_library_b200 as m
+    T, H, I, E, K = 64, 1024, 768, 8, 2
+    hidden, idx, aff, w_np, bgu, bd = _fmt_case(T, H, I, E, K, 75, fmt)
+    weights = _prep_fmt(m, w_np, fmt, bgu, bd)
+    out = m.moe_tkg(torch.from_numpy(hidden).to(torch.bfloat16).cuda(), weights, None, torch.from_numpy(aff).cuda(),
+                    torch.from_numpy(idx).cuda(), False,
+                    expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.POST_SCALE, _check_status=True)
+    ref = moe.moe_tkg_rows(hidden, aff, idx, *w_np, bias_gu=bgu, bias_d=bd, w_fmt=fmt)
+    assert max_rel(out.float().cpu().numpy(), bf16_values(ref)) <= TOL

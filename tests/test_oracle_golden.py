@@ -97,6 +97,46 @@ def test_e4m3_codec_against_ml_dtypes():
     assert np.array_equal(vals[ok], codes[ok].view(ml_dtypes.float8_e4m3fn).astype(np.float32))
 
 
+def test_element_decoders_match_reference_unpackers():
+    """e2m1 / e5m2 / e4m3 decoding against the reference's unpack_float4_x4, unpack_float8_e5m2_x4 and
+    unpack_float8_e4m3fn_x4 run over every 16-bit fp4 word and every byte (fixture mx_element_decode_ref.npz)."""
+    g = np.load(os.path.join(GOLD, "mx_element_decode_ref.npz"))
+    words = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    nib = np.stack([(words >> (4 * j)) & 0xF for j in range(4)], axis=-1).reshape(256, 1024).astype(np.uint8)
+    got = mx.e2m1_decode(nib)
+    assert np.array_equal(got, g["e2m1_x4"]) and np.array_equal(np.signbit(got), np.signbit(g["e2m1_x4"]))
+    # the packed image used on the device is the reference's x4 word
+    assert np.array_equal(mx.pack_e2m1(nib).view(np.uint16), words)
+    assert np.array_equal(mx.unpack_e2m1(mx.pack_e2m1(nib)), nib)
+    every = np.arange(256, dtype=np.uint8)
+    assert np.array_equal(mx.e5m2_decode(every), g["e5m2_x4"][0])
+    ours = mx.e4m3_decode(every)
+    finite = ~np.isnan(ours)
+    # 0x7F / 0xFF are NaN in e4m3fn (and on the tensor cores); the reference's unpacker reads them as +-480
+    assert list(np.flatnonzero(~finite)) == [0x7F, 0xFF]
+    assert np.array_equal(ours[finite], g["e4m3_x4"][0][finite])
+
+
+@pytest.mark.parametrize("fmt", ["e5m2", "e2m1"])
+def test_reference_storage_round_trip_other_formats(fmt):
+    """rows -> reference x4 storage -> rows for 8-bit and 4-bit element words."""
+    from moe_testlib import make_rows_weights_fmt
+    E, H, I = 2, 1024, 512
+    c1, s1, c2, s2 = make_rows_weights_fmt(E, H, I, fmt, seed=3)
+    gw, gs = mx.rows_to_ref_gate_up(c1, s1, fmt)
+    dw, ds = mx.rows_to_ref_down(c2, s2, fmt)
+    assert gw.dtype == (np.uint16 if fmt == "e2m1" else np.uint32) and gw.shape == (E, 128, 2, H // 512, I)
+    assert dw.shape == (E, 128, 1, H) and gs.shape == (E, 16, 2, H // 512, I)
+    if fmt == "e2m1":
+        g4 = np.stack([(gw >> (4 * j)) & 0xF for j in range(4)], axis=-1).astype(np.uint8)
+        d4 = np.stack([(dw >> (4 * j)) & 0xF for j in range(4)], axis=-1).astype(np.uint8)
+    else:
+        g4, d4 = gw.view(np.uint8).reshape(*gw.shape, 4), dw.view(np.uint8).reshape(*dw.shape, 4)
+    rc1, rs1 = mx.ref_gate_up_to_rows(g4, gs)
+    rc2, rs2 = mx.ref_down_to_rows(d4, ds)
+    assert np.array_equal(rc1, c1) and np.array_equal(rs1, s1) and np.array_equal(rc2, c2) and np.array_equal(rs2, s2)
+
+
 def test_quantize_rule_known_answers():
     # largest element 1.0 (biased exponent 127) -> scale byte 119, codes = x * 2^8 clipped to 448
     x = np.zeros((1, 32), dtype=np.float32)
