@@ -145,9 +145,9 @@ int b200moe_build_position_table(const int32_t* token_position_to_id, const int3
  * hidden[token_position_to_id[p]] (zeros for pad ids; identity if the pointer is
  * NULL), with the H axis taken in the reference's packed order
  * k' = t*512 + p*4 + q <- h = q*(H/4) + t*128 + p when h_packed_order != 0.
- * tile_flags (int32 [ceil(n_pos/128)], may be NULL) is set to 1 for every
- * 128-position tile that holds at least one real token; the contractions skip
- * the others. */
+ * tile_flags (int32 [ceil(n_pos/128)], may be NULL) receives, for every
+ * 128-position tile, 1 + the index of its last row that holds a real token (0 = none);
+ * the contractions skip empty tiles and copy only the leading rows of short ones. */
 int b200moe_gather_quantize_mxfp8(const void* hidden_bf16, int hidden_rows, int H, const int32_t* token_position_to_id,
                                   int64_t n_pos, int h_packed_order, uint8_t* codes, uint8_t* sf_atoms,
                                   int32_t* tile_flags, b200moe_stream_t stream);
@@ -208,6 +208,11 @@ int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, con
                                 int n_blocks, int B, int E, int H, int I, const void* affinities, int aff_dtype,
                                 int aff_per_row, void* y_pos_bf16, int32_t* status, int impl,
                                 b200moe_stream_t stream);
+
+/* Weight slabs (128 contraction elements of a weight tile) requested into L2 ahead of the shared-memory
+ * pipeline; 0 or -1 (default) = none.  Experiment knob without a reference counterpart: on the decode
+ * shapes measured it did not pay. */
+int b200moe_set_gemm_prefetch(int slabs);
 
 /* Weight rows per tile of the tensor-core kernel: 256 (default) or 128.  Tuning knob
  * with no counterpart in the reference. */

@@ -151,7 +151,12 @@ __global__ void __launch_bounds__(512) ep_plan_kernel(const int32_t* __restrict_
     row_valid[r] = valid ? static_cast<int32_t>(r) : -1;
   }
   __syncthreads();
-  for (int t = threadIdx.x; t < rows / 128; t += blockDim.x) tile_flags[t] = row_valid[static_cast<int64_t>(t) * 128] >= 0;
+  // per 128-row tile: how many leading rows hold a token (rows of an expert are packed from its first block)
+  for (int t = threadIdx.x; t < rows / 128; t += blockDim.x) {
+    int last = 127;
+    while (last >= 0 && row_valid[static_cast<int64_t>(t) * 128 + last] < 0) --last;
+    tile_flags[t] = last + 1;
+  }
 }
 
 __device__ __forceinline__ void unpack8_bf16_ep(const uint4& raw, float* out) {

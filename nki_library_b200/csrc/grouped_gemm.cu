@@ -67,6 +67,7 @@ struct GemmParams {
   unsigned long long* clock_probe;  // optional: CTA 0 writes {SM cycles, nanoseconds} spent in the kernel
   int w_format;     // element format of the weight operand (B200MOE_W_*); activations are e4m3
   uint32_t b_tx;    // bytes one weight-tile copy reports to its mbarrier
+  int prefetch;     // weight slabs requested into L2 ahead of the shared-memory pipeline (0 = none)
   int experiment;  // timing experiments only (builds with -DB200MOE_EXPERIMENT): bit 0 no loads, 1 no MMA,
                    // 2 no scale copies, 3 no epilogue math; results are meaningless when non-zero
 };
@@ -125,6 +126,12 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
           smem_u32(dst)),
       "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
       : "memory");
+}
+// Ask L2 for a weight slab without a shared-memory destination: extends the bytes in flight from HBM beyond what
+// the pipeline stages hold (weight-streaming shapes, where every weight byte is read once).
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(map), "r"(x), "r"(y), "r"(z)
+               : "memory");
 }
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -346,6 +353,16 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s,
   return true;
 }
 
+// Activation rows worth copying for a 128-position tile: tile_flags holds the number of leading rows that can
+// carry a token (tokens fill a block from its start), so short tiles -- decode, the last block of an expert --
+// copy a 32- or 64-row box.  The MMA still spans 128 rows; what it computes from the stale rows below the box
+// lands in rows nobody reads.
+__device__ __forceinline__ int tile_copy_rows(const GemmParams& p, int m_tile) {
+  if (p.tile_flags == nullptr) return kBlockM;
+  const int f = p.tile_flags[m_tile];
+  return f <= 32 ? 32 : (f <= 64 ? 64 : kBlockM);
+}
+
 template <int BLOCK_N, int STAGES, int CTAS = 1>
 struct SmemLayout {
   static constexpr int kA = kBlockM * kBlockK;
@@ -364,7 +381,8 @@ struct SmemLayout {
 
 template <int BLOCK_N, int STAGES, int EPI, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
-grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
+                          const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
                           const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                           const GemmParams p) {
   // CTAS == 2: the two CTAs of a cluster form one tcgen05 cta_group::2 unit.  Each loads its own 128
@@ -375,9 +393,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   constexpr int kSfCol = kAcc * BLOCK_N;  // TMEM columns: accumulators, then SFA (4), then SFB
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kIdesc = make_idesc(kBlockM * CTAS, BLOCK_N);
-  // operand bytes per stage (scale atoms report to sf_full); 4-bit weights land in the same padded
-  // 128-byte rows, so the count is a launch parameter rather than a constant of the tile shape
-  const uint32_t stage_bytes = CTAS * (L::kA + p.b_tx);
+  // operand bytes per stage (scale atoms report to sf_full) depend on the tile: short activation boxes, and
+  // 4-bit weights that land in the same padded 128-byte rows but report their packed size
   const uint32_t idesc_base = kIdesc | (static_cast<uint32_t>(p.w_format) << 10);
 
   extern __shared__ uint8_t smem_raw[];
@@ -449,12 +466,34 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      constexpr int kRowsB = BLOCK_N / CTAS;  // weight rows this CTA copies per slab
       for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
         int m_tile, n_tile, e, k_shift;
         if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, k_shift)) continue;
+        const int rows_lead = tile_copy_rows(p, m_tile);
+        const int rows_peer = CTAS == 2 ? tile_copy_rows(p, m_tile + 1) : 0;
         m_tile += cta_rank;
+        const int my_rows = cta_rank == 0 ? rows_lead : rows_peer;
+        const CUtensorMap* map_a = my_rows == 32 ? &tmap_a32 : (my_rows == 64 ? &tmap_a64 : &tmap_a);
+        const uint32_t stage_bytes = static_cast<uint32_t>(rows_lead + rows_peer) * kBlockK + CTAS * p.b_tx;
         const int atom0 = (n_tile * BLOCK_N) >> 7;
+        // L2 prefetch runs `p.prefetch` slabs ahead, into the next tile of this CTA when the current one ends
+        int nx_n = 0, nx_e = -1;
+        if (p.prefetch > 0) {
+          int nm, nk;
+          for (int t2 = tile + n_units; t2 < total_tiles; t2 += n_units)
+            if (decode_tile(p, sched, t2, CTAS, nm, nx_n, nx_e, nk)) break; else nx_e = -1;
+          if (tile == unit)
+            for (int kp = 0; kp < p.prefetch && kp < p.k_blocks; ++kp)
+              tma_prefetch_3d(&tmap_b, kp * kBlockK, n_tile * BLOCK_N + cta_rank * kRowsB, e);
+        }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (p.prefetch > 0) {
+            const int kp = kb + p.prefetch;
+            if (kp < p.k_blocks) tma_prefetch_3d(&tmap_b, kp * kBlockK, n_tile * BLOCK_N + cta_rank * kRowsB, e);
+            else if (nx_e >= 0 && kp - p.k_blocks < p.k_blocks)
+              tma_prefetch_3d(&tmap_b, (kp - p.k_blocks) * kBlockK, nx_n * BLOCK_N + cta_rank * kRowsB, nx_e);
+          }
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
 #ifdef B200MOE_EXPERIMENT
           if (p.experiment & 1) {
@@ -477,21 +516,21 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #ifdef B200MOE_EXPERIMENT
             const bool skip_a = (p.experiment & 16) && (kb & 1), skip_b = (p.experiment & 32) && (kb & 1);
             if (cta_rank == 0)
-              mbar_expect_tx(&full[stage], stage_bytes - (skip_a ? 2 * L::kA : 0) - (skip_b ? 2 * p.b_tx : 0));
+              mbar_expect_tx(&full[stage], stage_bytes - (skip_a ? (rows_lead + rows_peer) * kBlockK : 0) - (skip_b ? 2 * p.b_tx : 0));
             if (!skip_a)
-              tma2_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
+              tma2_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
             if (!skip_b)
               tma2_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK,
                            n_tile * BLOCK_N + cta_rank * (BLOCK_N / 2), e, &full[stage]);
 #else
             if (cta_rank == 0) mbar_expect_tx(&full[stage], stage_bytes);
-            tma2_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
+            tma2_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
             tma2_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK,
                          n_tile * BLOCK_N + cta_rank * (BLOCK_N / 2), e, &full[stage]);
 #endif
           } else {
             mbar_expect_tx(&full[stage], stage_bytes);
-            tma_load_2d(smem + L::kOffA + stage * L::kA, &tmap_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
+            tma_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
             tma_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK, n_tile * BLOCK_N, e, &full[stage]);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -889,7 +928,7 @@ int make_atoms_map(CUtensorMap* map, const void* base, int64_t n_atoms) {
 }
 
 template <int BLOCK_N, int STAGES, int EPI, int CTAS>
-int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa, const CUtensorMap& msb,
+int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorMap& msa, const CUtensorMap& msb,
               const GemmParams& p, cudaStream_t st) {
   using L = SmemLayout<BLOCK_N, STAGES, CTAS>;
   auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI, CTAS>;
@@ -913,9 +952,9 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& m
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    B200MOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, msa, msb, p));
+    B200MOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma[0], ma[1], ma[2], mb, msa, msb, p));
   } else {
-    kern<<<grid, kThreads, L::kBytes, st>>>(ma, mb, msa, msb, p);
+    kern<<<grid, kThreads, L::kBytes, st>>>(ma[0], ma[1], ma[2], mb, msa, msb, p);
   }
   B200MOE_LAUNCH_OK("grouped_mxfp8_gemm_kernel");
   return B200MOE_OK;
@@ -924,6 +963,7 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& m
 int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128 or 256)
 unsigned long long* g_clock_probe = nullptr;  // device buffer of 4 words: {cycles, ns} per projection
 int g_cta_pair = 1;   // 1: run 256-position x 256-row tiles on CTA pairs (cta_group::2) when blocks allow
+int g_prefetch = -1;  // weight slabs prefetched into L2 ahead of the pipeline; -1 = default (none)
 
 int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, int impl, cudaStream_t st) {
   B200MOE_REQUIRE(p.B > 0 && p.B % 128 == 0, B200MOE_ERR_INVALID, "block size must be a multiple of 128, got %d", p.B);
@@ -958,9 +998,14 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   const int bn = g_block_n;
   p.n_tiles = (p.n_total + bn - 1) / bn;
   const bool pair = g_cta_pair && bn == 256 && (p.B % 256 == 0) && (sm_count() % 2 == 0);
-  CUtensorMap ma, mb, msa, msb;
-  int rc = make_rows_map(&ma, a, K, static_cast<int64_t>(p.m_tiles_total) * 128, 0, kBlockM);
+  CUtensorMap ma[3], mb, msa, msb;  // activation boxes of 128, 64 and 32 rows
+  int rc = B200MOE_OK;
+  for (int i = 0; i < 3 && rc == B200MOE_OK; ++i)
+    rc = make_rows_map(&ma[i], a, K, static_cast<int64_t>(p.m_tiles_total) * 128, 0, kBlockM >> i);
   if (rc != B200MOE_OK) return rc;
+  // off unless asked for: on the decode shapes measured (8 experts x 14336 x 4096, 64 tokens) a distance of 6-24
+  // slabs made both contractions 8-60 % slower
+  p.prefetch = g_prefetch >= 0 ? g_prefetch : 0;
   rc = make_rows_map(&mb, b, K, p.n_total, p.E, pair ? bn / 2 : bn, nibbles);
   // the copy reports the bytes it read from global memory: a 4-bit slab is 64 bytes per row there
   p.b_tx = static_cast<uint32_t>((pair ? bn / 2 : bn) * (nibbles ? kBlockK / 2 : kBlockK));
@@ -983,6 +1028,12 @@ using namespace b200moe;
 
 extern "C" int b200moe_set_clock_probe(void* device_words) {
   g_clock_probe = static_cast<unsigned long long*>(device_words);
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_set_gemm_prefetch(int slabs) {
+  B200MOE_REQUIRE(slabs >= -1 && slabs <= 64, B200MOE_ERR_INVALID, "prefetch distance must be in [-1, 64], got %d", slabs);
+  g_prefetch = slabs;
   return B200MOE_OK;
 }
 

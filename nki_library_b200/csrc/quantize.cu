@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(256) gather_quantize_kernel(const __nv_bfloat1
         }
       }
       quantize_block32(v, c, s);
-      if (tile_flags != nullptr && kb == 0) tile_flags[p >> 7] = 1;
+      if (tile_flags != nullptr && kb == 0) atomicMax(&tile_flags[p >> 7], static_cast<int>(p & 127) + 1);
     }
     uint4* dst = reinterpret_cast<uint4*>(codes + p * H + kb * 32);
     dst[0] = make_uint4(c[0], c[1], c[2], c[3]);

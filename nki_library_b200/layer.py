@@ -50,9 +50,14 @@ class MoELayer:
         self.out = torch.empty((T, self.H), dtype=torch.bfloat16, device=dev)
         self.kernels_per_forward = 9  # 2 router, 3 grouping, quantise, 2 contractions, combine
 
-    def forward(self, hidden: torch.Tensor, timers: Optional[dict] = None) -> torch.Tensor:
-        """``hidden`` bf16 ``[T, H]`` on the device; returns the layer's bf16 ``[T, H]`` output buffer."""
+    def forward(self, hidden: torch.Tensor, timers: Optional[dict] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``hidden`` bf16 ``[T, H]`` on the device; returns the bf16 ``[T, H]`` output (``out`` if given, else the
+        layer's own buffer)."""
         T = hidden.shape[0]
+        out = self.out if out is None else out
+        _lib.kernel_assert(tuple(out.shape) == (self.T, self.H) and out.dtype == torch.bfloat16 and out.is_contiguous(),
+                           "out must be a contiguous bf16 [max_tokens, H] tensor")
         _lib.kernel_assert(T == self.T and hidden.shape[1] == self.H and hidden.dtype == torch.bfloat16,
                            "hidden must be bf16 [max_tokens, H]")
         st = _lib.stream_ptr()
@@ -90,8 +95,8 @@ class MoELayer:
             _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(ws.tile_flags), _lib.ptr(self.tpi),
             T, N, B, E, H, I, _lib.ptr(self.aff), _lib.F32, 0, _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), 0, st))
         timed("combine", lambda: _lib.call(
-            "b200moe_combine", _lib.ptr(ws.y_pos), _lib.ptr(self.inv), T, K, H, _lib.ptr(self.out), st))
-        return self.out
+            "b200moe_combine", _lib.ptr(ws.y_pos), _lib.ptr(self.inv), T, K, H, _lib.ptr(out), st))
+        return out
 
     def capture(self, hidden: torch.Tensor) -> None:
         """Record one forward pass on ``hidden`` (a fixed device buffer) into a CUDA graph.
@@ -107,6 +112,19 @@ class MoELayer:
     def replay(self) -> torch.Tensor:
         self._graph.replay()
         return self.out
+
+    def capture_slots(self, hiddens, outs) -> None:
+        """One graph per (input buffer, output buffer) pair, for callers that alternate staging buffers and
+        want the layer to read and write them in place.  ``replay_slot(i)`` runs pair i."""
+        self._slot_graphs = []
+        for h, o in zip(hiddens, outs):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.forward(h, out=o)
+            self._slot_graphs.append(g)
+
+    def replay_slot(self, i: int) -> None:
+        self._slot_graphs[i].replay()
 
     def device_status(self) -> list:
         """[grouping, gate/up contraction, down contraction] status words (0 = fine); synchronises."""
@@ -165,7 +183,9 @@ class HostPipeline:
 
     ``submit(host_in, host_out)`` enqueues: pinned host -> device staging (copy stream), the layer (compute
     stream, CUDA graph), device -> pinned host (second copy stream).  Two staging buffers each way let step
-    i + 1's upload and step i - 1's download run while step i computes.  ``drain()`` waits for everything.
+    i + 1's upload and step i - 1's download run while step i computes.  A :class:`MoELayer` is captured once
+    per staging pair and reads / writes the staging buffers directly, so the compute stream never queues a
+    device-to-device copy behind a PCIe transfer on a copy engine.  ``drain()`` waits for everything.
     """
 
     def __init__(self, layer):
@@ -177,6 +197,11 @@ class HostPipeline:
         layer.capture(self.hidden)
         self.stage_in = [torch.empty_like(self.hidden) for _ in range(2)]
         self.stage_out = [torch.empty_like(layer.out) for _ in range(2)]
+        # a layer that can be captured once per staging pair works on the staging buffers in place; otherwise
+        # its fixed input / output buffers are filled and drained with device-to-device copies
+        self.in_place = hasattr(layer, "capture_slots")
+        if self.in_place:
+            layer.capture_slots(self.stage_in, self.stage_out)
         self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         self.ev_in = [torch.cuda.Event() for _ in range(2)]        # upload i finished
         self.ev_in_free = [torch.cuda.Event() for _ in range(2)]   # compute consumed staging i
@@ -194,12 +219,18 @@ class HostPipeline:
             self.stage_in[i].copy_(host_in, non_blocking=True)
             self.ev_in[i].record(self.s_in)
         cur.wait_event(self.ev_in[i])
-        self.hidden.copy_(self.stage_in[i], non_blocking=True)
-        self.ev_in_free[i].record(cur)
-        self.layer.replay()
-        if not first:
-            cur.wait_event(self.ev_out_free[i])
-        self.stage_out[i].copy_(self.layer.out, non_blocking=True)
+        if self.in_place:
+            if not first:
+                cur.wait_event(self.ev_out_free[i])
+            self.layer.replay_slot(i)
+            self.ev_in_free[i].record(cur)
+        else:
+            self.hidden.copy_(self.stage_in[i], non_blocking=True)
+            self.ev_in_free[i].record(cur)
+            self.layer.replay()
+            if not first:
+                cur.wait_event(self.ev_out_free[i])
+            self.stage_out[i].copy_(self.layer.out, non_blocking=True)
         self.ev_out[i].record(cur)
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_event(self.ev_out[i])

@@ -378,3 +378,28 @@ def test_moe_tkg_other_weight_formats(fmt):
                     expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.POST_SCALE, _check_status=True)
     ref = moe.moe_tkg_rows(hidden, aff, idx, *w_np, bias_gu=bgu, bias_d=bd, w_fmt=fmt)
     assert max_rel(out.float().cpu().numpy(), bf16_values(ref)) <= TOL
+
+
+def test_host_pipeline_matches_direct_forward():
+    """Five different host batches through the overlapped host pipeline (graphs working in place on the two
+    staging pairs) give the bytes a direct forward pass gives."""
+    import nki_library_b200 as m
+    from nki_library_b200.layer import HostPipeline, MoELayer, random_expert_weights
+    T, H, I, E, K, B = 256, 512, 512, 4, 2, 128
+    dev = torch.device("cuda")
+    weights = random_expert_weights(E, H, I, dev, seed=3)
+    gen = torch.Generator().manual_seed(5)
+    router_w = (torch.randn(H, E, generator=gen) * 0.02).to(torch.bfloat16).to(dev)
+    layer = MoELayer(router_w, weights, K, B, T)
+    pipe = HostPipeline(layer)
+    assert pipe.in_place
+    ins = [torch.randn(T, H, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(5)]
+    outs = [torch.empty(T, H, dtype=torch.bfloat16).pin_memory() for _ in range(5)]
+    for a, b in zip(ins, outs):
+        pipe.submit(a, b)
+    pipe.drain()
+    assert not any(layer.device_status())
+    for a, b in zip(ins, outs):
+        ref = layer.forward(a.to(dev)).clone()
+        torch.cuda.synchronize()
+        assert torch.equal(b, ref.cpu())

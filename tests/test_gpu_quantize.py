@@ -48,7 +48,8 @@ def test_gather_quantize_bit_exact(packed, H):
     o_codes, o_scales = mx.quantize_mx_rows(src)
     assert np.array_equal(scales, o_scales)
     assert np.array_equal(codes, o_codes)
-    assert list(flags) == [1, 1, 0, 1, 0]
+    # per 128-position tile: 1 + index of the last row that holds a token (0 = all pads)
+    assert list(flags) == [128, 128, 0, 116, 0]
 
 
 def test_gather_quantize_identity_rows():
