@@ -217,8 +217,10 @@ int b200moe_set_gemm_prefetch(int slabs);
 /* Weight rows per tile of the tensor-core kernel: 256 (default) or 128.  Tuning knob
  * with no counterpart in the reference. */
 int b200moe_set_gemm_tile_n(int block_n);
-/* Run the contractions on CTA pairs (tcgen05 cta_group::2, 256 positions x 256 weight rows per pair)
- * whenever the block size is a multiple of 256 (default: on).  Tuning knob with no counterpart in the reference. */
+/* Run the contractions on CTA pairs (tcgen05 cta_group::2, 256 positions x 256 weight rows per pair).
+ * 0 = never; 1 (default) = when the block size is a multiple of 256, or with other block sizes when experts
+ * hold four or more 128-position tiles on average (an expert's tiles are then paired across its blocks, an odd
+ * tile ending in a half-empty pair); 2 = whenever possible.  Tuning knob with no counterpart in the reference. */
 int b200moe_set_gemm_cta_pair(int enable);
 /* Diagnostic: with a non-NULL device buffer of four 64-bit words, CTA 0 of the gate/up contraction writes
  * {SM cycles, nanoseconds} to words 0-1 and the down contraction to words 2-3, which gives the SM clock

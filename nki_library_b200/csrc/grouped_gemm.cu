@@ -306,20 +306,24 @@ __device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s, int m
     int run = 0;
     for (int e = 0; e < p.E; ++e) {
       s.tile_start[e] = run;
-      run += (s.mt_count[e] / mg) * p.n_tiles;
+      run += ((s.mt_count[e] + mg - 1) / mg) * p.n_tiles;  // an odd tile count leaves the last pair half empty
     }
     s.tile_start[p.E] = run;
-    s.total = s.contiguous ? run : (p.m_tiles_total / mg) * p.n_tiles;
+    // scattered blocks: pairs stay inside a block when it holds an even number of tiles, else every tile is
+    // a unit of its own (the pair's second CTA idles)
+    const int units = (mg == 2 && (sub & 1)) ? p.m_tiles_total : p.m_tiles_total / mg;
+    s.total = s.contiguous ? run : units * p.n_tiles;
   }
   __syncthreads();
 }
 
-// m_tile is the first position tile of the unit; with mg == 2 the pair's CTAs take m_tile and m_tile + 1.
-// k_shift: the slab a tile starts its K loop at (always 0: starting the units that share a weight
-// tile at spread-out slabs was measured slower than letting their identical requests merge in L2).
+// m_tile is the first position tile of the unit; with mg == 2 the pair's CTAs take m_tile and m_tile + 1, and
+// `second` says whether m_tile + 1 is a tile of the same expert that holds tokens (an expert with an odd number
+// of tiles ends in a half-empty pair: its second CTA still supplies half of the weight tile but copies no
+// activations and writes nothing).
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s, int tile, int mg, int& m_tile,
-                                            int& n_tile, int& expert, int& k_shift) {
-  k_shift = 0;
+                                            int& n_tile, int& expert, int& second) {
+  second = mg == 2 ? 1 : 0;
   if (s.contiguous) {
     int lo = 0, hi = p.E;
     while (hi - lo > 1) {
@@ -328,10 +332,14 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s,
     }
     expert = lo;
     const int local = tile - s.tile_start[lo];
-    const int cnt = s.mt_count[lo] / mg;
-    m_tile = s.mt_first[lo] + (local % cnt) * mg;
+    const int cnt = (s.mt_count[lo] + mg - 1) / mg;
+    const int idx = local % cnt;
+    m_tile = s.mt_first[lo] + idx * mg;
     n_tile = local / cnt;
+    if (mg == 2 && idx * 2 + 1 >= s.mt_count[lo]) second = 0;
   } else {
+    const bool solo = mg == 2 && ((p.B >> 7) & 1);
+    if (solo) { mg = 1; second = 0; }
     const int units = p.m_tiles_total / mg;
     const int per_group = kGroupM * p.n_tiles;
     const int g = tile / per_group;
@@ -346,9 +354,8 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s,
     if (expert < 0 || expert >= p.E) return false;
   }
   if (p.tile_flags != nullptr) {
-    int any = 0;
-    for (int i = 0; i < mg; ++i) any |= p.tile_flags[m_tile + i];
-    if (any == 0) return false;
+    if (second && p.tile_flags[m_tile + 1] == 0) second = 0;
+    if (p.tile_flags[m_tile] == 0 && !second) return false;
   }
   return true;
 }
@@ -360,7 +367,7 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s,
 __device__ __forceinline__ int tile_copy_rows(const GemmParams& p, int m_tile) {
   if (p.tile_flags == nullptr) return kBlockM;
   const int f = p.tile_flags[m_tile];
-  return f <= 32 ? 32 : (f <= 64 ? 64 : kBlockM);
+  return f <= 0 ? 0 : (f <= 32 ? 32 : (f <= 64 ? 64 : kBlockM));
 }
 
 template <int BLOCK_N, int STAGES, int CTAS = 1>
@@ -468,10 +475,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       bool ok = true;
       constexpr int kRowsB = BLOCK_N / CTAS;  // weight rows this CTA copies per slab
       for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
-        int m_tile, n_tile, e, k_shift;
-        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, k_shift)) continue;
+        int m_tile, n_tile, e, second;
+        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second)) continue;
         const int rows_lead = tile_copy_rows(p, m_tile);
-        const int rows_peer = CTAS == 2 ? tile_copy_rows(p, m_tile + 1) : 0;
+        const int rows_peer = second ? tile_copy_rows(p, m_tile + 1) : 0;
         m_tile += cta_rank;
         const int my_rows = cta_rank == 0 ? rows_lead : rows_peer;
         const CUtensorMap* map_a = my_rows == 32 ? &tmap_a32 : (my_rows == 64 ? &tmap_a64 : &tmap_a);
@@ -517,20 +524,22 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             const bool skip_a = (p.experiment & 16) && (kb & 1), skip_b = (p.experiment & 32) && (kb & 1);
             if (cta_rank == 0)
               mbar_expect_tx(&full[stage], stage_bytes - (skip_a ? (rows_lead + rows_peer) * kBlockK : 0) - (skip_b ? 2 * p.b_tx : 0));
-            if (!skip_a)
+            if (!skip_a && my_rows > 0)
               tma2_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
             if (!skip_b)
               tma2_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK,
                            n_tile * BLOCK_N + cta_rank * (BLOCK_N / 2), e, &full[stage]);
 #else
             if (cta_rank == 0) mbar_expect_tx(&full[stage], stage_bytes);
-            tma2_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
+            if (my_rows > 0)
+              tma2_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
             tma2_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK,
                          n_tile * BLOCK_N + cta_rank * (BLOCK_N / 2), e, &full[stage]);
 #endif
           } else {
             mbar_expect_tx(&full[stage], stage_bytes);
-            tma_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
+            if (my_rows > 0)
+              tma_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
             tma_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK, n_tile * BLOCK_N, e, &full[stage]);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -548,8 +557,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
-        int m_tile, n_tile, e, k_shift;
-        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, k_shift)) continue;
+        int m_tile, n_tile, e, second;
+        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second)) continue;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
@@ -595,8 +604,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     uint32_t phase = 0;
     bool ok = true;
     for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
-      int m_tile, n_tile, e, k_shift;
-      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, k_shift)) continue;
+      int m_tile, n_tile, e, second;
+      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second)) continue;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait(&sf_full[stage], phase, abort_flag, p.status, 6)) { ok = false; break; }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kSfCol + stage * 16;
@@ -637,8 +646,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     const float g_lo = p.gate_lo == p.gate_lo ? p.gate_lo : -INFINITY, g_hi = p.gate_hi == p.gate_hi ? p.gate_hi : INFINITY;
     const float u_lo = p.up_lo == p.up_lo ? p.up_lo : -INFINITY, u_hi = p.up_hi == p.up_hi ? p.up_hi : INFINITY;
     for (int tile = unit; tile < total_tiles; tile += n_units) {
-      int m_tile, n_tile, e, k_shift;
-      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, k_shift)) continue;
+      int m_tile, n_tile, e, second;
+      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second)) continue;
       m_tile += cta_rank;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after();
@@ -659,6 +668,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #ifdef B200MOE_EXPERIMENT
       if (p.experiment & 8) continue;
 #endif
+      if (CTAS == 2 && cta_rank != 0 && !second) continue;  // half-empty pair: these rows belong to someone else
 
       if constexpr (EPI == 0) {
         const int64_t k_atoms = (p.I + 127) >> 7;
@@ -937,7 +947,7 @@ int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorM
     B200MOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     attr_set = true;
   }
-  const int total = (p.m_tiles_total / CTAS) * p.n_tiles;
+  const int total = ((p.m_tiles_total + CTAS - 1) / CTAS) * p.n_tiles;  // only sizes the grid
   int grid = (total < sm_count() / CTAS ? total : sm_count() / CTAS) * CTAS;
   if constexpr (CTAS == 2) {
     cudaLaunchConfig_t cfg = {};
@@ -997,7 +1007,11 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   B200MOE_REQUIRE(K % 16 == 0, B200MOE_ERR_INVALID, "TMA needs row pitches that are multiples of 16 bytes");
   const int bn = g_block_n;
   p.n_tiles = (p.n_total + bn - 1) / bn;
-  const bool pair = g_cta_pair && bn == 256 && (p.B % 256 == 0) && (sm_count() % 2 == 0);
+  // CTA pairs need two position tiles per weight tile: always there when a block holds an even number of 128-row
+  // tiles; with odd blocks (B = 128) an expert's tiles are paired across its blocks, which pays once experts have
+  // several tiles on average (prefill) and not for one short tile per expert (decode)
+  const bool pair = g_cta_pair && bn == 256 && (sm_count() % 2 == 0) &&
+                    (p.B % 256 == 0 || (g_cta_pair == 2 || p.m_tiles_total >= 4 * p.E));
   CUtensorMap ma[3], mb, msa, msb;  // activation boxes of 128, 64 and 32 rows
   int rc = B200MOE_OK;
   for (int i = 0; i < 3 && rc == B200MOE_OK; ++i)
@@ -1038,7 +1052,7 @@ extern "C" int b200moe_set_gemm_prefetch(int slabs) {
 }
 
 extern "C" int b200moe_set_gemm_cta_pair(int enable) {
-  g_cta_pair = enable ? 1 : 0;
+  g_cta_pair = enable < 0 ? 0 : (enable > 2 ? 2 : enable);
   return B200MOE_OK;
 }
 

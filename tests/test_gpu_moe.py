@@ -113,9 +113,14 @@ def test_moe_cte_c1_rows_weights(impl, variant):
     assert max_rel(out.float().cpu().numpy(), ref) <= TOL
 
 
-@pytest.mark.parametrize("B,T", [(256, 700), (512, 1500)])
-def test_moe_cte_cta_pair_mode(B, T):
-    """The cta_group::2 kernel (two CTAs share a weight tile) against the oracle and the single-CTA kernel."""
+@pytest.mark.parametrize("B,T,scatter", [(256, 700, False), (512, 1500, False), (128, 700, False), (128, 900, True),
+                                         (384, 1100, False), (256, 700, True)])
+def test_moe_cte_cta_pair_mode(B, T, scatter):
+    """The cta_group::2 kernel (two CTAs share a weight tile) against the oracle and the single-CTA kernel.
+
+    Blocks of 128 or 384 positions make an expert's 128-row tiles pair up across its blocks, with a half-empty
+    last pair for an odd count; ``scatter`` shuffles the block order, so experts are no longer contiguous and
+    the kernel walks blocks in the given order (tiles of odd-sized blocks then run one per pair)."""
     import nki_library_b200 as m
     from nki_library_b200 import _lib
     H, I, E, K = 512, 512, 4, 2
@@ -123,19 +128,25 @@ def test_moe_cte_cta_pair_mode(B, T):
     weights = _prep(m, w_np, bgu, bd)
     N = m.get_n_blocks(T, K, E, B)
     g = m.moe_group_tokens(torch.from_numpy(idx).cuda(), E, B, N, check=True)
+    tpi, b2e, cond = g["token_position_to_id"], g["block_to_expert"], g["conditions"]
+    if scatter:
+        n_act = int(cond[:N].sum().item())
+        perm = torch.cat([torch.randperm(n_act, generator=torch.Generator().manual_seed(B + T)), torch.arange(n_act, N)])
+        tpi = tpi.view(N, B)[perm.cuda()].reshape(-1).contiguous()
+        b2e = b2e[perm.cuda()].contiguous()
     args = (torch.from_numpy(hidden).to(torch.bfloat16).cuda(), torch.from_numpy(aff).cuda().reshape(-1, 1), weights,
-            None, g["token_position_to_id"], g["block_to_expert"], B,
-            m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx))
-    kw = dict(conditions=g["conditions"], skip_dma=m.SkipMode(True, False), _check_status=True)
+            None, tpi, b2e, B, m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx))
+    kw = dict(conditions=cond, skip_dma=m.SkipMode(True, False), _check_status=True)
     _lib.call("b200moe_set_gemm_cta_pair", 0)
     try:
         single = m.moe_cte(*args, **kw)
+        _lib.call("b200moe_set_gemm_cta_pair", 2)
+        paired = m.moe_cte(*args, **kw)
+        paired2 = m.moe_cte(*args, **kw)
     finally:
         _lib.call("b200moe_set_gemm_cta_pair", 1)
-    paired = m.moe_cte(*args, **kw)
-    paired2 = m.moe_cte(*args, **kw)
-    ref = _oracle_cte(hidden, aff, w_np, g["token_position_to_id"].cpu().numpy(), g["block_to_expert"].cpu().numpy(),
-                      g["conditions"].cpu().numpy(), B, bgu, bd, moe.SILU, None)
+    ref = _oracle_cte(hidden, aff, w_np, tpi.cpu().numpy(), b2e.cpu().numpy(), cond.cpu().numpy(), B, bgu, bd,
+                      moe.SILU, None)
     assert max_rel(paired.float().cpu().numpy(), ref) <= TOL
     assert torch.equal(paired, paired2)
     assert max_rel(paired.float().cpu().numpy(), single.float().cpu().numpy()) <= 1e-2
