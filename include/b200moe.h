@@ -152,6 +152,15 @@ int b200moe_gather_quantize_mxfp8(const void* hidden_bf16, int hidden_rows, int 
                                   int64_t n_pos, int h_packed_order, uint8_t* codes, uint8_t* sf_atoms,
                                   int32_t* tile_flags, b200moe_stream_t stream);
 
+/* The same quantisation driven by the inverse map (inverse_map[t*K + k] = position of token t's k-th expert, or
+ * negative; what b200moe_group_tokens writes): every token row is read and quantised once and stored to its K
+ * positions, so hidden crosses HBM once instead of K times.  Positions that no (token, k) pair maps to are NOT
+ * written -- the contractions never let such rows reach a result -- and tile_flags is filled as above.
+ * No reference counterpart (the reference gathers per block, core/moe/moe_cte/moe_cte_mx_utils.py:456-945). */
+int b200moe_scatter_quantize_mxfp8(const void* hidden_bf16, int T, int H, const int32_t* inverse_map, int K,
+                                   int64_t n_pos, int h_packed_order, uint8_t* codes, uint8_t* sf_atoms,
+                                   int32_t* tile_flags, b200moe_stream_t stream);
+
 /* ---- weight preparation (once per model load) ----------------------------------
  * Source B200MOE_LAYOUT_ROWS: codes [E,2,I,H] + scales [E,2,I,H/32] (gate_up) and
  * codes [E,H,I] + scales [E,H,I/32] (down).

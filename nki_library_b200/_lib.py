@@ -50,6 +50,8 @@ SIGNATURES = {
                                              c_void_p]),
     "b200moe_gather_quantize_mxfp8": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p,
                                               c_void_p, c_void_p]),
+    "b200moe_scatter_quantize_mxfp8": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_int, c_void_p,
+                                               c_void_p, c_void_p, c_void_p]),
     "b200moe_prepare_gate_up": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                         c_void_p]),
     "b200moe_prepare_down": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

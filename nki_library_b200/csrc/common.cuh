@@ -8,6 +8,9 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <mutex>
+#include <set>
+#include <utility>
 
 #include "../../include/b200moe.h"
 
@@ -43,14 +46,32 @@ void set_error(const char* fmt, ...);
   } while (0)
 
 inline int sm_count() {
-  static int n = 0;
+  static int cached[64] = {};  // per device ordinal; racing threads write the same value
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  int n = cached[dev];
   if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     if (n <= 0) n = 148;
+    cached[dev] = n;
   }
   return n;
+}
+
+// Opt a kernel in to `bytes` of dynamic shared memory, once per (device, kernel); safe to call from several
+// host threads and with several devices in one process.
+inline cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<int, const void*>> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({dev, kernel})) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.insert({dev, kernel});
+  return e;
 }
 
 __host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }

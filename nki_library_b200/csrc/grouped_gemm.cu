@@ -942,11 +942,7 @@ int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorM
               const GemmParams& p, cudaStream_t st) {
   using L = SmemLayout<BLOCK_N, STAGES, CTAS>;
   auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI, CTAS>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200MOE_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
-    attr_set = true;
-  }
+  B200MOE_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kBytes));
   const int total = ((p.m_tiles_total + CTAS - 1) / CTAS) * p.n_tiles;  // only sizes the grid
   int grid = (total < sm_count() / CTAS ? total : sm_count() / CTAS) * CTAS;
   if constexpr (CTAS == 2) {

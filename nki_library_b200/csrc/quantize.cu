@@ -75,6 +75,99 @@ __global__ void __launch_bounds__(256) gather_quantize_kernel(const __nv_bfloat1
   }
 }
 
+// Token-major twin of gather_quantize_kernel for callers that hold the inverse map (position of every
+// (token, k) pair): one warp reads a token's row once, quantises it once and stores codes and scale cells to its
+// K positions, so the hidden tensor crosses HBM once instead of K times.  Per pass of 256 columns lane l holds
+// 8 bf16 (16 bytes); the four lanes l & ~3 .. l | 3 hold one 32-element block, so the block maximum is two
+// shuffles away, every lane stores its 8 code bytes (256 contiguous bytes per warp and position) and lanes 0 and
+// 16 store one 4-byte scale cell each.  Positions no pair maps to are not written.
+__global__ void __launch_bounds__(256) scatter_quantize_kernel(const __nv_bfloat16* __restrict__ hidden, int T, int H,
+                                                               const int32_t* __restrict__ inverse_map, int K,
+                                                               int64_t n_pos, int packed, uint8_t* __restrict__ codes,
+                                                               uint8_t* __restrict__ sf,
+                                                               int32_t* __restrict__ tile_flags) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int64_t k_atoms = (H + 127) >> 7;
+  int my_pos = -1;
+  if (lane < K) {
+    my_pos = inverse_map[static_cast<int64_t>(t) * K + lane];
+    if (my_pos < 0 || my_pos >= n_pos) my_pos = -1;
+    else if (tile_flags != nullptr && blockIdx.y == 0) atomicMax(&tile_flags[my_pos >> 7], (my_pos & 127) + 1);
+  }
+  int pos[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) pos[k] = __shfl_sync(0xffffffffu, my_pos, k);
+  const __nv_bfloat16* row = hidden + static_cast<int64_t>(t) * H;
+  const int passes = (H + 255) >> 8;
+  const int q = lane & 3, blk = lane >> 2;
+  constexpr int kU = 4;  // passes per warp: blockIdx.y walks the row in chunks of 1024 columns
+  {
+    const int it0 = blockIdx.y * kU;
+    uint4 raw[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int it = it0 + u;
+      const int col = it * 256 + lane * 8;
+      raw[u] = make_uint4(0, 0, 0, 0);
+      if (it < passes && col < H) {
+        if (!packed) {
+          raw[u] = __ldg(reinterpret_cast<const uint4*>(row + col));
+        } else {
+          const int kb = it * 8 + blk;
+          raw[u] = __ldg(reinterpret_cast<const uint4*>(row + q * (H >> 2) + (kb >> 4) * 128 + (kb & 15) * 8));
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int it = it0 + u;
+      if (it >= passes) break;  // uniform across the warp
+      const int col = it * 256 + lane * 8;
+      float v[8];
+      unpack8_bf16(raw[u], v);
+      uint32_t mx = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = max(mx, __float_as_uint(v[j]) & 0x7fffffffu);
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      float f1, f2;
+      mx_block_factors(mx, f1, f2);
+      uint32_t w0 = pack4_e4m3(v[0] * f1 * f2, v[1] * f1 * f2, v[2] * f1 * f2, v[3] * f1 * f2);
+      uint32_t w1 = pack4_e4m3(v[4] * f1 * f2, v[5] * f1 * f2, v[6] * f1 * f2, v[7] * f1 * f2);
+      if (packed) {
+        // lane q holds elements p*4 + q (p = 0..7) of the block; it stores bytes 8q .. 8q+7, i.e. byte pair
+        // (2q, 2q+1) of every lane of its group of four
+        uint32_t o0 = 0, o1 = 0;
+#pragma unroll
+        for (int s2 = 0; s2 < 4; ++s2) {
+          const uint32_t a0 = __shfl_sync(0xffffffffu, w0, (lane & ~3) + s2);
+          const uint32_t a1 = __shfl_sync(0xffffffffu, w1, (lane & ~3) + s2);
+          const uint32_t x = ((q >= 2 ? a1 : a0) >> (16 * (q & 1))) & 0xffffu;
+          o0 |= (x & 0xffu) << (8 * s2);
+          o1 |= (x >> 8) << (8 * s2);
+        }
+        w0 = o0;
+        w1 = o1;
+      }
+      // the four scale bytes of a 128-column cell sit in lanes 0, 4, 8, 12 (+16) of the warp
+      uint32_t cell = col < H ? static_cast<uint32_t>(mx_block_scale_byte(mx)) << (8 * (blk & 3)) : 0u;
+      cell |= __shfl_xor_sync(0xffffffffu, cell, 4);
+      cell |= __shfl_xor_sync(0xffffffffu, cell, 8);
+      if (col < H) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (k >= K || pos[k] < 0) continue;
+          const int64_t p = pos[k];
+          *reinterpret_cast<uint2*>(codes + p * H + col) = make_uint2(w0, w1);
+          if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sf + sf_atom_offset(p, col >> 5, k_atoms)) = cell;
+        }
+      }
+    }
+  }
+}
+
 // ---- weight relayout ---------------------------------------------------------
 // Destination row of gate/up source row (s = 0 gate / 1 up, i): 32 gate rows then
 // the matching 32 up rows.
@@ -251,6 +344,29 @@ extern "C" int b200moe_gather_quantize_mxfp8(const void* hidden_bf16, int hidden
       static_cast<const __nv_bfloat16*>(hidden_bf16), hidden_rows, H, token_position_to_id, n_pos, h_packed_order,
       codes, sf_atoms, tile_flags);
   B200MOE_LAUNCH_OK("gather_quantize_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_scatter_quantize_mxfp8(const void* hidden_bf16, int T, int H, const int32_t* inverse_map, int K,
+                                              int64_t n_pos, int h_packed_order, uint8_t* codes, uint8_t* sf_atoms,
+                                              int32_t* tile_flags, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(hidden_bf16 && inverse_map && codes && sf_atoms, B200MOE_ERR_INVALID,
+                  "scatter_quantize: null pointer argument");
+  B200MOE_REQUIRE(T > 0 && H > 0 && H % 32 == 0 && n_pos > 0, B200MOE_ERR_INVALID,
+                  "scatter_quantize: T, n_pos must be positive and H a positive multiple of 32 (H = %d)", H);
+  B200MOE_REQUIRE(K >= 1 && K <= 8, B200MOE_ERR_INVALID, "scatter_quantize: K must be in [1, 8], got %d", K);
+  B200MOE_REQUIRE(!h_packed_order || H % 512 == 0, B200MOE_ERR_INVALID,
+                  "scatter_quantize: the packed hidden order needs H %% 512 == 0, got %d", H);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((H % 128) != 0)  // the unused quarter cells of the last 128-column atom must read as zero
+    B200MOE_CUDA_OK(cudaMemsetAsync(sf_atoms, 0, b200moe_sf_bytes(n_pos, H), st));
+  if (tile_flags != nullptr)
+    B200MOE_CUDA_OK(cudaMemsetAsync(tile_flags, 0, static_cast<size_t>(ceil_div64(n_pos, 128)) * 4, st));
+  const dim3 grid(static_cast<unsigned>((T + 7) / 8), static_cast<unsigned>((H + 1023) / 1024));
+  scatter_quantize_kernel<<<grid, 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(hidden_bf16), T, H, inverse_map, K, n_pos, h_packed_order, codes, sf_atoms,
+      tile_flags);
+  B200MOE_LAUNCH_OK("scatter_quantize_kernel");
   return B200MOE_OK;
 }
 

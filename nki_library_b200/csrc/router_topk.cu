@@ -382,11 +382,7 @@ extern "C" int b200moe_router_topk(const void* x, int x_is_TH, const void* w, co
   B200MOE_REQUIRE(workspace != nullptr && workspace_bytes >= need, B200MOE_ERR_WORKSPACE,
                   "router_topk: workspace of %zu bytes is smaller than the required %zu", workspace_bytes, need);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200MOE_CUDA_OK(cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024));
-    attr_set = true;
-  }
+  B200MOE_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(router_logits_kernel), 164 * 1024));
   LogitArgs la{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), x_is_TH, T, H, E,
                p.mw, p.nw, p.h_per_split, p.stages, static_cast<float*>(workspace)};
   dim3 grid((T + p.tm - 1) / p.tm, p.splits);

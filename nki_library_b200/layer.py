@@ -82,8 +82,9 @@ class MoELayer:
             "b200moe_group_tokens", _lib.ptr(self.idx), _lib.ROUTING_INDEX, _lib.I32, T, E, K, B, N, 1, 1,
             _lib.ptr(self.tpi), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(self.counts), _lib.ptr(self.inv),
             _lib.ptr(self.gstatus), _lib.ptr(self.gws), self.gws.numel(), st))
+        # token-major: each row is read and quantised once and stored to its K positions
         timed("gather_quantize", lambda: _lib.call(
-            "b200moe_gather_quantize_mxfp8", _lib.ptr(hidden), T, H, _lib.ptr(self.tpi), N * B,
+            "b200moe_scatter_quantize_mxfp8", _lib.ptr(hidden), T, H, _lib.ptr(self.inv), K, N * B,
             int(w.h_packed_order), _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(ws.tile_flags), st))
         nan = float("nan")
         timed("gemm1_swiglu", lambda: _lib.call(

@@ -96,3 +96,45 @@ def test_prepare_weights_layouts(layout, I):
     for e in range(E):
         assert np.array_equal(sf_atoms_to_rows(sf2[e], H, I), s2[e])
     assert np.array_equal(w.bias_d.cpu().numpy(), bd)
+
+
+@pytest.mark.parametrize("packed", [False, True])
+@pytest.mark.parametrize("H,K", [(512, 2), (4096, 8), (1024, 1), (96, 3)])
+def test_scatter_quantize_equals_gather_quantize(packed, H, K):
+    """The token-major kernel (driven by the inverse map) writes, at every occupied position, the bytes the
+    position-major kernel writes, and the same per-tile row counts; unoccupied positions keep their old bytes."""
+    from nki_library_b200 import _lib
+    import nki_library_b200 as m
+    if packed and H % 512:
+        pytest.skip("the packed hidden order needs H % 512 == 0")
+    rng = np.random.default_rng(3)
+    T, E, B = 333, 8, 128
+    hidden = bf16_values(rng.standard_normal((T, H)).astype(np.float32) * np.exp(rng.uniform(-4, 4, (T, 1))))
+    idx = np.stack([rng.permutation(E)[:K] for _ in range(T)]).astype(np.int32)
+    N = m.get_n_blocks(T, K, E, B)
+    g = m.moe_group_tokens(torch.from_numpy(idx).cuda(), E, B, N, top_k=K, check=True)
+    tpi, inv = g["token_position_to_id"], g["inverse_map"]
+    n_pos = N * B
+    hid = torch.from_numpy(hidden).to(torch.bfloat16).cuda()
+    lib = _lib.load_library()
+
+    def buffers():
+        return (torch.full((n_pos, H), 0xAB, dtype=torch.uint8, device="cuda"),
+                torch.full((lib.b200moe_sf_bytes(n_pos, H),), 0xCD, dtype=torch.uint8, device="cuda"),
+                torch.full((n_pos // 128,), 7, dtype=torch.int32, device="cuda"))
+    c1, s1, f1 = buffers()
+    c2, s2, f2 = buffers()
+    _lib.call("b200moe_gather_quantize_mxfp8", _lib.ptr(hid), T, H, _lib.ptr(tpi), n_pos, int(packed), _lib.ptr(c1),
+              _lib.ptr(s1), _lib.ptr(f1), _lib.stream_ptr())
+    _lib.call("b200moe_scatter_quantize_mxfp8", _lib.ptr(hid), T, H, _lib.ptr(inv), K, n_pos, int(packed),
+              _lib.ptr(c2), _lib.ptr(s2), _lib.ptr(f2), _lib.stream_ptr())
+    torch.cuda.synchronize()
+    occ = (tpi >= 0).cpu().numpy()
+    assert torch.equal(f1, f2)
+    c1, c2 = c1.cpu().numpy(), c2.cpu().numpy()
+    assert np.array_equal(c1[occ], c2[occ])
+    r1 = sf_atoms_to_rows(s1.cpu().numpy(), n_pos, H if H % 128 == 0 else (H + 127) // 128 * 128)
+    r2 = sf_atoms_to_rows(s2.cpu().numpy(), n_pos, H if H % 128 == 0 else (H + 127) // 128 * 128)
+    assert np.array_equal(r1[occ][:, : H // 32], r2[occ][:, : H // 32])
+    if H % 128 == 0:
+        assert (c2[~occ] == 0xAB).all()   # untouched
