@@ -281,6 +281,9 @@ def run_ours(args, cfg, name):
     if args.prefetch >= -1:
         from nki_library_b200 import _lib
         _lib.call("b200moe_set_gemm_prefetch", args.prefetch)
+    if args.router_path >= 0:
+        from nki_library_b200 import _lib
+        _lib.call("b200moe_set_router_path", args.router_path)
     if args.cta_pair >= 0:
         from nki_library_b200 import _lib
         _lib.call("b200moe_set_gemm_cta_pair", args.cta_pair)
@@ -517,6 +520,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cta-pair", type=int, default=-1, help="1/0: force the cta_group::2 GEMM on/off (-1 = default)")
     ap.add_argument("--prefetch", type=int, default=-2, help="weight slabs prefetched into L2 (-1 = by shape)")
+    ap.add_argument("--router-path", type=int, default=-1, help="1 split-K router, 2 tcgen05 router (-1 = by shape)")
     ap.add_argument("--tile-n", type=int, default=0, help="weight rows per GEMM tile (128/192/256; 0 = library default)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]

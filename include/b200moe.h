@@ -71,9 +71,15 @@ size_t b200moe_sf_bytes(int64_t rows, int64_t K);
  * (router_topk.py:515-547).  x is bf16 [T,H] (x_is_TH=1) or [H,T]; w bf16 [H,E];
  * w_bias bf16 [E] or NULL.  Outputs (each may be NULL to skip): router_logits
  * [T,E], expert_index uint32 [T,k], expert_affinities [T,E] (dense, zeros outside
- * the top-k when scattered).  E <= 512, k <= 8.  workspace holds the split-K partial
- * logits (b200moe_router_workspace_bytes). */
+ * the top-k when scattered).  E <= 512, k <= 8.  workspace (256-byte aligned,
+ * b200moe_router_workspace_bytes) starts with an int32 status word -- non-zero after the
+ * call's kernels have run means a device-side wait ran out -- followed by scratch: split-K
+ * partial logits, or the transposed router weight of the single-kernel tcgen05 path that
+ * large token counts take (x [T,H], E <= 256, H % 64 == 0). */
 size_t b200moe_router_workspace_bytes(int T, int H, int E);
+/* 0 (default): choose by shape; 1: always the split-K path; 2: the tcgen05 path whenever the shape
+ * is eligible.  Tuning knob without a reference counterpart. */
+int b200moe_set_router_path(int path);
 int b200moe_router_topk(const void* x, int x_is_TH, const void* w, const void* w_bias, int T, int H, int E, int k,
                         int act_fn, int router_pre_norm, int norm_topk_prob, void* router_logits, int logits_dtype,
                         uint32_t* expert_index, void* expert_affinities, int aff_dtype, void* workspace,

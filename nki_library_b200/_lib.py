@@ -63,6 +63,7 @@ SIGNATURES = {
     "b200moe_grouped_gemm2_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                             c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "b200moe_set_router_path": (c_int, [c_int]),
     "b200moe_set_gemm_tile_n": (c_int, [c_int]),
     "b200moe_set_gemm_cta_pair": (c_int, [c_int]),
     "b200moe_set_gemm_prefetch": (c_int, [c_int]),

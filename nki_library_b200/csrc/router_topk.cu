@@ -11,7 +11,17 @@
 #include "common.cuh"
 
 namespace b200moe {
+// Large-T path (router_tc.cu): the logits GEMM on the tcgen05 tensor cores, one pass over x.
+size_t router_tc_workspace_bytes(int T, int H, int E);
+bool router_tc_eligible(int x_is_TH, int T, int H, int E);
+int router_tc_run(const void* x, const void* w, int T, int H, int E, void* workspace, int32_t* status,
+                  float** logits_out, cudaStream_t st);
+
 namespace {
+
+constexpr size_t kWsHeader = 256;  // workspace bytes in front of the scratch: int32 status word, then padding
+int g_router_path = 0;             // 0 = by shape, 1 = split-K mma.sync path, 2 = tcgen05 path when eligible
+constexpr int kTcMinTokens = 8192;
 
 constexpr int kKC = 64;           // hidden slab per pipeline stage
 constexpr int kXPad = 8;          // halfs of padding per smem row (bank spread)
@@ -359,7 +369,15 @@ using namespace b200moe;
 
 extern "C" size_t b200moe_router_workspace_bytes(int T, int H, int E) {
   const RouterPlan p = plan_router(T, H, E, 1);
-  return static_cast<size_t>(p.splits) * T * E * sizeof(float);
+  const size_t split_k = static_cast<size_t>(p.splits) * T * E * sizeof(float);
+  const size_t tc = router_tc_workspace_bytes(T, H, E);
+  return kWsHeader + (split_k > tc ? split_k : tc);
+}
+
+extern "C" int b200moe_set_router_path(int path) {
+  B200MOE_REQUIRE(path >= 0 && path <= 2, B200MOE_ERR_INVALID, "router path must be 0, 1 or 2, got %d", path);
+  g_router_path = path;
+  return B200MOE_OK;
 }
 
 extern "C" int b200moe_router_topk(const void* x, int x_is_TH, const void* w, const void* w_bias, int T, int H, int E,
@@ -378,17 +396,35 @@ extern "C" int b200moe_router_topk(const void* x, int x_is_TH, const void* w, co
                       (aff_dtype == B200MOE_F32 || aff_dtype == B200MOE_BF16),
                   B200MOE_ERR_INVALID, "router_topk: outputs must be fp32 or bf16");
   const RouterPlan p = plan_router(T, H, E, x_is_TH);
-  const size_t need = static_cast<size_t>(p.splits) * T * E * sizeof(float);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool use_tc = router_tc_eligible(x_is_TH, T, H, E) &&
+                      (g_router_path == 2 || (g_router_path == 0 && T >= kTcMinTokens));
+  const size_t need = kWsHeader + (use_tc ? router_tc_workspace_bytes(T, H, E)
+                                          : static_cast<size_t>(p.splits) * T * E * sizeof(float));
   B200MOE_REQUIRE(workspace != nullptr && workspace_bytes >= need, B200MOE_ERR_WORKSPACE,
                   "router_topk: workspace of %zu bytes is smaller than the required %zu", workspace_bytes, need);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B200MOE_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(router_logits_kernel), 164 * 1024));
-  LogitArgs la{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), x_is_TH, T, H, E,
-               p.mw, p.nw, p.h_per_split, p.stages, static_cast<float*>(workspace)};
-  dim3 grid((T + p.tm - 1) / p.tm, p.splits);
-  router_logits_kernel<<<grid, 256, p.smem, st>>>(la);
-  B200MOE_LAUNCH_OK("router_logits_kernel");
-  RankArgs ra{static_cast<const float*>(workspace), p.splits, static_cast<const __nv_bfloat16*>(w_bias), T, E, k,
+  B200MOE_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, B200MOE_ERR_INVALID,
+                  "router_topk: the workspace must be 256-byte aligned");
+  int32_t* status = static_cast<int32_t*>(workspace);
+  workspace = static_cast<uint8_t*>(workspace) + kWsHeader;
+  const float* partial = static_cast<const float*>(workspace);
+  int splits = p.splits;
+  if (use_tc) {
+    float* logits = nullptr;
+    const int rc = router_tc_run(x, w, T, H, E, workspace, status, &logits, st);
+    if (rc != B200MOE_OK) return rc;
+    partial = logits;
+    splits = 1;
+  } else {
+    B200MOE_CUDA_OK(cudaMemsetAsync(status, 0, 4, st));
+    B200MOE_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(router_logits_kernel), 164 * 1024));
+    LogitArgs la{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), x_is_TH, T, H, E,
+                 p.mw, p.nw, p.h_per_split, p.stages, static_cast<float*>(workspace)};
+    dim3 grid((T + p.tm - 1) / p.tm, p.splits);
+    router_logits_kernel<<<grid, 256, p.smem, st>>>(la);
+    B200MOE_LAUNCH_OK("router_logits_kernel");
+  }
+  RankArgs ra{partial, splits, static_cast<const __nv_bfloat16*>(w_bias), T, E, k,
               act_fn, router_pre_norm, norm_topk_prob, router_logits, logits_dtype, expert_index, expert_affinities,
               aff_dtype};
   const dim3 rgrid((T + 7) / 8);

@@ -128,8 +128,9 @@ class MoELayer:
         self._slot_graphs[i].replay()
 
     def device_status(self) -> list:
-        """[grouping, gate/up contraction, down contraction] status words (0 = fine); synchronises."""
-        return [int(self.gstatus.item())] + self.ws.status.cpu().tolist()[1:3]
+        """[grouping, gate/up contraction, down contraction, router] status words (0 = fine); synchronises."""
+        return ([int(self.gstatus.item())] + self.ws.status.cpu().tolist()[1:3] +
+                [int(self.rws[:4].view(torch.int32).item())])
 
 
 def random_expert_weights(E: int, H: int, I: int, device, seed: int = 0, std: float = 0.02,

@@ -31,9 +31,21 @@ def digests():
         return json.load(f)
 
 
+@pytest.fixture(params=["split_k", "tcgen05"])
+def router_path(request):
+    """Runs a router test on the split-K path and with the single-kernel tcgen05 path forced wherever the shape
+    is eligible for it (x [T, H], E <= 256, H % 64 == 0; other shapes fall back by themselves)."""
+    from nki_library_b200 import _lib
+    _lib.call("b200moe_set_router_path", 1 if request.param == "split_k" else 2)
+    yield request.param
+    _lib.call("b200moe_set_router_path", 0)
+
+
 @pytest.mark.parametrize("name", list(gi.ROUTER_CASES))
 @pytest.mark.parametrize("x_layout", [1, 0])
-def test_router_topk_vs_reference_fixture(lib, name, x_layout):
+def test_router_topk_vs_reference_fixture(lib, name, x_layout, router_path):
+    if router_path == "tcgen05" and x_layout == 0:
+        pytest.skip("the tcgen05 path takes x as [T, H] only")
     gold = np.load(os.path.join(GOLD, "router_topk_ref.npz"))
     T, H, E, k, act, has_bias, pre_norm, l1 = gi.ROUTER_CASES[name]
     x, w, b = gi.router_inputs(T, H, E, has_bias)
