@@ -465,7 +465,7 @@ def run_ours(args, cfg, name):
         cpu = (dict(value=None, sample="skipped (--skip-cpu)") if args.skip_cpu
                else cpu_sample(cfg, 2, 1, os.cpu_count() or 1))
         decode = decode_mxfp4 = None
-        if world == 1 and name == "mixtral_prefill":
+        if world == 1 and name == "mixtral_prefill" and not args.no_decode_leg:
             decode = decode_leg(weights, peaks, dev, args.weight_format)
             if args.weight_format == "e4m3":
                 # the same decode step with MXFP4 (e2m1) expert weights: half the bytes to stream
@@ -520,6 +520,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cta-pair", type=int, default=-1, help="1/0: force the cta_group::2 GEMM on/off (-1 = default)")
     ap.add_argument("--prefetch", type=int, default=-2, help="weight slabs prefetched into L2 (-1 = by shape)")
+    ap.add_argument("--no-decode-leg", action="store_true", help="omit the secondary decode measurements (profiling runs)")
     ap.add_argument("--router-path", type=int, default=-1, help="1 split-K router, 2 tcgen05 router (-1 = by shape)")
     ap.add_argument("--tile-n", type=int, default=0, help="weight rows per GEMM tile (128/192/256; 0 = library default)")
     args = ap.parse_args()

@@ -68,6 +68,9 @@ struct GemmParams {
   int w_format;     // element format of the weight operand (B200MOE_W_*); activations are e4m3
   uint32_t b_tx;    // bytes one weight-tile copy reports to its mbarrier
   int prefetch;     // weight slabs requested into L2 ahead of the shared-memory pipeline (0 = none)
+  int tile_filter;  // which position tiles a launch walks when experts are contiguous: 0 all, 1 (CTA-pair
+                    // kernel) only pairs of two live tiles, 2 (single-CTA kernel) only the tile an expert with
+                    // an odd number of live tiles has left over
   int experiment;  // timing experiments only (builds with -DB200MOE_EXPERIMENT): bit 0 no loads, 1 no MMA,
                    // 2 no scale copies, 3 no epilogue math; results are meaningless when non-zero
 };
@@ -77,7 +80,11 @@ struct Sched {
   int tile_start[kMaxExperts + 1];  // tiles before expert e (expert-aligned order)
   int mt_first[kMaxExperts];        // first 128-position tile of expert e
   int mt_count[kMaxExperts];        // its number of position tiles among the active blocks
-  int runs[kMaxExperts];            // how many separate block runs expert e has (1 when sorted)
+  int runs[kMaxExperts];            // how many separate block runs expert e has (1 when sorted); after the
+                                    // build, in left-over mode: the expert of left-over tile i
+  int n_live[kMaxExperts];          // 1 + index (among the expert's tiles) of its last tile that holds a token
+  int left_m[kMaxExperts];          // left-over mode: position tile of left-over i
+  int n_left;                       // left-over mode: number of left-over tiles
   int n_active;                     // blocks before the first zero condition
   int contiguous;                   // every expert's blocks are adjacent
   int total;                        // number of tiles to walk
@@ -105,17 +112,34 @@ __device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s, int m
     atomicAdd(&s.mt_count[e], sub);
   }
   __syncthreads();
+  for (int e = tid; e < p.E; e += nthr) {
+    int live = s.mt_count[e];
+    if (p.tile_flags != nullptr)
+      while (live > 0 && p.tile_flags[s.mt_first[e] + live - 1] == 0) --live;
+    s.n_live[e] = live;
+  }
+  __syncthreads();
   if (tid == 0) {
-    int run = 0;
+    int run = 0, n_left = 0;
+    const bool leftovers = s.contiguous && p.tile_filter == 2;
     for (int e = 0; e < p.E; ++e) {
       s.tile_start[e] = run;
-      run += ((s.mt_count[e] + mg - 1) / mg) * p.n_tiles;  // an odd tile count leaves the last pair half empty
+      if (s.contiguous && p.tile_filter == 1) {
+        run += (s.n_live[e] / 2) * p.n_tiles;                // full pairs only; the odd tile goes to the other launch
+      } else if (leftovers) {
+        if (s.n_live[e] & 1) { s.left_m[n_left] = s.mt_first[e] + s.n_live[e] - 1; s.runs[n_left] = e; ++n_left; }
+      } else {
+        run += ((s.mt_count[e] + mg - 1) / mg) * p.n_tiles;  // an odd tile count leaves the last pair half empty
+      }
     }
+    s.n_left = n_left;
+    if (leftovers) run = n_left * p.n_tiles;
+    if (!s.contiguous && p.tile_filter == 2) run = 0;        // scattered blocks: the pair launch does everything
     s.tile_start[p.E] = run;
     // scattered blocks: pairs stay inside a block when it holds an even number of tiles, else every tile is
     // a unit of its own (the pair's second CTA idles)
     const int units = (mg == 2 && (sub & 1)) ? p.m_tiles_total : p.m_tiles_total / mg;
-    s.total = s.contiguous ? run : units * p.n_tiles;
+    s.total = (s.contiguous || p.tile_filter == 2) ? run : units * p.n_tiles;
   }
   __syncthreads();
 }
@@ -127,6 +151,13 @@ __device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s, int m
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s, int tile, int mg, int& m_tile,
                                             int& n_tile, int& expert, int& second) {
   second = mg == 2 ? 1 : 0;
+  if (s.contiguous && p.tile_filter == 2) {
+    const int i = tile % s.n_left;
+    m_tile = s.left_m[i];
+    expert = s.runs[i];
+    n_tile = tile / s.n_left;
+    return true;
+  }
   if (s.contiguous) {
     int lo = 0, hi = p.E;
     while (hi - lo > 1) {
@@ -135,7 +166,7 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s,
     }
     expert = lo;
     const int local = tile - s.tile_start[lo];
-    const int cnt = (s.mt_count[lo] + mg - 1) / mg;
+    const int cnt = p.tile_filter == 1 ? s.n_live[lo] / 2 : (s.mt_count[lo] + mg - 1) / mg;
     const int idx = local % cnt;
     m_tile = s.mt_first[lo] + idx * mg;
     n_tile = local / cnt;
@@ -730,7 +761,8 @@ int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorM
   using L = SmemLayout<BLOCK_N, STAGES, CTAS>;
   auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI, CTAS>;
   B200MOE_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kBytes));
-  const int total = ((p.m_tiles_total + CTAS - 1) / CTAS) * p.n_tiles;  // only sizes the grid
+  // only sizes the grid; a left-over launch has at most one tile per expert and weight tile
+  const int total = p.tile_filter == 2 ? p.E * p.n_tiles : ((p.m_tiles_total + CTAS - 1) / CTAS) * p.n_tiles;
   int grid = (total < sm_count() / CTAS ? total : sm_count() / CTAS) * CTAS;
   if constexpr (CTAS == 2) {
     cudaLaunchConfig_t cfg = {};
@@ -756,6 +788,7 @@ int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorM
 int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128 or 256)
 unsigned long long* g_clock_probe = nullptr;  // device buffer of 4 words: {cycles, ns} per projection
 int g_cta_pair = 1;   // 1: run 256-position x 256-row tiles on CTA pairs (cta_group::2) when blocks allow
+int g_split_leftover = 1;  // CTA-pair path: odd left-over tiles go to a second, single-CTA launch
 int g_prefetch = -1;  // weight slabs prefetched into L2 ahead of the pipeline; -1 = default (none)
 
 int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, int impl, cudaStream_t st) {
@@ -811,8 +844,22 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   if (rc != B200MOE_OK) return rc;
   rc = make_atoms_map(&msb, p.b_sf, static_cast<int64_t>(p.E) * p.b_row_atoms * p.k_blocks);
   if (rc != B200MOE_OK) return rc;
-  if (pair)
-    return epi == 0 ? launch_tc<256, 6, 0, 2>(ma, mb, msa, msb, p, st) : launch_tc<256, 6, 1, 2>(ma, mb, msa, msb, p, st);
+  if (pair) {
+    // Two launches: the CTA-pair kernel walks the pairs of live 128-row tiles, the single-CTA kernel the one
+    // tile an expert with an odd number of live tiles has left over (a half-empty pair would pay for a full
+    // 256-row MMA: with ~1000 rows per expert that was one tile in five).
+    p.tile_filter = g_split_leftover ? 1 : 0;
+    rc = epi == 0 ? launch_tc<256, 6, 0, 2>(ma, mb, msa, msb, p, st) : launch_tc<256, 6, 1, 2>(ma, mb, msa, msb, p, st);
+    if (rc != B200MOE_OK || !g_split_leftover) return rc;
+    GemmParams p2 = p;
+    p2.tile_filter = 2;
+    p2.clock_probe = nullptr;
+    p2.b_tx = static_cast<uint32_t>(bn * (nibbles ? kBlockK / 2 : kBlockK));
+    CUtensorMap mb2;
+    rc = make_rows_map(&mb2, b, K, p.n_total, p.E, bn, nibbles);
+    if (rc != B200MOE_OK) return rc;
+    return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb2, msa, msb, p2, st) : launch_tc<256, 4, 1, 1>(ma, mb2, msa, msb, p2, st);
+  }
   if (bn == 256)
     return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb, msa, msb, p, st) : launch_tc<256, 4, 1, 1>(ma, mb, msa, msb, p, st);
   return epi == 0 ? launch_tc<128, 6, 0, 1>(ma, mb, msa, msb, p, st) : launch_tc<128, 6, 1, 1>(ma, mb, msa, msb, p, st);
@@ -835,6 +882,9 @@ extern "C" int b200moe_set_gemm_prefetch(int slabs) {
 }
 
 extern "C" int b200moe_set_gemm_cta_pair(int enable) {
+  // bit 2 (value 4) switches the separate launch for left-over tiles off: pairs then run half empty
+  g_split_leftover = (enable >= 0 && (enable & 4)) ? 0 : 1;
+  if (enable >= 0) enable &= 3;
   g_cta_pair = enable < 0 ? 0 : (enable > 2 ? 2 : enable);
   return B200MOE_OK;
 }
