@@ -276,7 +276,9 @@ class PeerExpertParallelMoE:
         self.gstatus = torch.zeros(1, dtype=torch.int32, device=dev)
         self.gws = torch.empty(lib.b200moe_group_tokens_workspace_bytes(self.T, self.E), dtype=torch.uint8, device=dev)
         self.timers = None
-        self.kernels_per_forward = 2 + 3 + 1 + 1 + 1 + 1 + 2 + 1 + 1 + 1
+        # router 2, grouping 3, count exchange, dispatch, wait, plan, contractions (CTA-pair launch + left-over
+        # launch each when the block size allows pairs), return, wait, combine
+        self.kernels_per_forward = 2 + 3 + 1 + 1 + 1 + 1 + (4 if self.B % 256 == 0 else 2) + 1 + 1 + 1
         self._graph = None
 
     def forward(self, hidden: torch.Tensor) -> torch.Tensor:
