@@ -39,8 +39,8 @@ WORKLOADS = {
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
 # profiles/ (one capture per workload; null where none was taken).
 NCU_TRAFFIC_BYTES = {
-    "mixtral_prefill": 1.906486e9 + 137.900544e6,
-    "mixtral_decode": 976.613888e6 + 18.093824e6,
+    "mixtral_prefill": (1.004123e9 + 118.779392e6) + (0.486658e9 + 10.018304e6),  # CTA-pair + left-over launch
+    "mixtral_decode": 971.416576e6 + 18.775808e6,
 }
 
 
