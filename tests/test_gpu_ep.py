@@ -49,7 +49,7 @@ def _worker(rank, world, port, results, backend):
             out = layer.forward(x).clone()
             out2 = layer.forward(x).clone()
             out3 = layer.forward(x).clone()
-            assert layer.device_status() == [0, 0, 0], layer.device_status()
+            assert not any(layer.device_status()), layer.device_status()
             assert torch.equal(out2, out3)
             rows = int((layer.row_valid >= 0).sum().item())
         torch.cuda.synchronize()
@@ -74,7 +74,7 @@ def test_peer_memory_exchange_single_rank():
         layer = PeerExpertParallelMoE(torch.from_numpy(router_w).cuda(), full, E, K, B, T_LOCAL)
         out = layer.forward(x).clone()
         out2 = layer.forward(x).clone()
-        assert layer.device_status() == [0, 0, 0], layer.device_status()
+        assert not any(layer.device_status()), layer.device_status()
         assert torch.equal(out, out2)
         assert int((layer.row_valid >= 0).sum().item()) == T_LOCAL * K
         ref_gpu = MoELayer(torch.from_numpy(router_w).cuda(), full, K, B, T_LOCAL).forward(x)
