@@ -381,6 +381,9 @@ def run_ours(args, cfg, name):
     t_end.record()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
+    status = device_status()
+    if any(status):
+        raise RuntimeError(f"device status after the timed steps: {status}")
     # -------- the same steps again, eagerly, with CUDA events around every kernel (roofline input)
     from nki_library_b200 import _lib as _l
     probe = torch.zeros(4, dtype=torch.int64, device=dev)
@@ -403,6 +406,9 @@ def run_ours(args, cfg, name):
                       for i, nm in enumerate(names)}
     forward(hidden_d)  # drops the event hooks again
     barrier()
+    status = device_status()
+    if any(status):
+        raise RuntimeError(f"device status after the instrumented steps: {status}")
     # -------- end-to-end leg: host buffers through the public layer call
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -436,7 +442,7 @@ def run_ours(args, cfg, name):
         ms_total, ms_e2e = t.tolist()
     status = device_status()
     if any(status):
-        raise RuntimeError(f"device status after timing: {status}")
+        raise RuntimeError(f"device status after the end-to-end steps: {status}")
 
     if rank == 0:
         work = algorithmic_work(cfg, args.weight_format)

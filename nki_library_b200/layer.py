@@ -198,7 +198,9 @@ class HostPipeline:
     def __init__(self, layer):
         dev = layer.out.device
         self.layer = layer
-        self.hidden = torch.empty((layer.T, layer.H), dtype=torch.bfloat16, device=dev)
+        # the set-up pass below runs on real-looking data: with uninitialised (or constant) input every token may
+        # pick the same experts, which an expert-parallel layer reports as a receive-buffer overflow
+        self.hidden = torch.randn((layer.T, layer.H), dtype=torch.float32, device=dev).to(torch.bfloat16)
         layer.forward(self.hidden)  # make sure every kernel attribute is set before capture
         torch.cuda.synchronize()
         layer.capture(self.hidden)
