@@ -26,7 +26,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs that fit one GPU (configs[1] is the headline prefill case)
+# benchmark configurations that fit one GPU (mixtral_prefill is the headline case)
 WORKLOADS = {
     "mixtral_prefill": dict(kind="prefill", T=4096, H=4096, I=14336, E=8, K=2, B=512, zipf=None),
     "mixtral_decode": dict(kind="decode", T=64, H=4096, I=14336, E=8, K=2, B=128, zipf=None),
@@ -228,7 +228,7 @@ def run_reference(args, cfg, name):
 
 # ------------------------------------------------------------------ GPU leg
 def decode_leg(weights, peaks, device, w_format="e4m3"):
-    """Mixtral decode workload (BASELINE config 3) on the given expert weights: tokens/s and HBM fraction."""
+    """Mixtral decode workload (T = 64 tokens, Mixtral-8x7B shapes) on the given expert weights: tokens/s and HBM fraction."""
     import torch
 
     from nki_library_b200.layer import MoELayer

@@ -43,7 +43,7 @@ def test_find_nonzero_fuzz(T, C, density, seed):
 
 @pytest.mark.parametrize("T,H,I,E,K,B,zipf", [(8192, 7168, 2048, 256, 8, 128, 1.2), (32768, 4096, 1536, 128, 8, 256, None)])
 def test_full_size_layer_properties(T, H, I, E, K, B, zipf):
-    """BASELINE configs 4 and 5 at full size: grouping bit-exact, the layer deterministic and linear in the affinity,
+    """The fine-grained and the 32768-token prefill configurations at full size: grouping bit-exact, the layer deterministic and linear in the affinity,
     and a sample of tokens within tolerance of the oracle (weights read back from the device)."""
     import nki_library_b200 as m
     from moe_testlib import bf16_values, gate_up_dev_rows, max_rel, sf_atoms_to_rows

@@ -89,7 +89,7 @@ def _oracle_cte(hidden, aff, w_np, tpi, b2e, cond, B, bgu, bd, act, clamp, h_ord
 @pytest.mark.parametrize("impl", [1, 0])
 @pytest.mark.parametrize("variant", ["plain", "bias_clamp_swish"])
 def test_moe_cte_c1_rows_weights(impl, variant):
-    """BASELINE config 1: T=256, H=512, I=1024, E=4, top-2, B=128."""
+    """Smallest benchmark configuration: T=256, H=512, I=1024, E=4, top-2, B=128."""
     import nki_library_b200 as m
     T, H, I, E, K, B = 256, 512, 1024, 4, 2, 128
     bias = variant != "plain"
@@ -209,7 +209,7 @@ def test_moe_cte_conditions_stop_and_skew():
 
 @pytest.mark.parametrize("mode,I", [("selective", 768), ("all_expert", 768), ("selective", 5120)])
 def test_moe_tkg_vs_oracle(mode, I):
-    """Decode: T=64 tokens, top-2 of 8 experts (BASELINE config 3 with H, I scaled down; I = 5120 gives the
+    """Decode: T=64 tokens, top-2 of 8 experts (the decode configuration with H, I scaled down; I = 5120 gives the
     gate/up contraction more weight tiles than there are SMs, so CTAs walk several tiles each)."""
     import nki_library_b200 as m
     T, H, E, K = 64, 1024, 8, 2
@@ -236,7 +236,7 @@ def test_moe_tkg_vs_oracle(mode, I):
 
 
 def test_moe_cte_properties_at_mixtral_block_shape():
-    """Size-independent checks at BASELINE config 2's block geometry (B=512, H=4096, K=2, E=8; I cut to 2048)."""
+    """Size-independent checks at the Mixtral prefill configuration's block geometry (B=512, H=4096, K=2, E=8; I cut to 2048)."""
     import nki_library_b200 as m
     from nki_library_b200 import _lib, pipeline
     T, H, I, E, K, B = 2048, 4096, 2048, 8, 2, 512
