@@ -85,13 +85,16 @@ struct Sched {
   int n_live[kMaxExperts];          // 1 + index (among the expert's tiles) of its last tile that holds a token
   int left_m[kMaxExperts];          // left-over mode: position tile of left-over i
   int n_left;                       // left-over mode: number of left-over tiles
+  int n_full;                       // tiles [0, n_full) are whole; each later index is half (128 weight rows) of
+                                    // one of the tiles that would not fill a last round of CTAs
   int n_active;                     // blocks before the first zero condition
   int contiguous;                   // every expert's blocks are adjacent
   int total;                        // number of tiles to walk
 };
 
 // `mg` = position tiles per scheduling unit (1, or 2 when a CTA pair shares a weight tile).
-__device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s, int mg) {
+// `halves`: single-CTA launches with 256-row weight tiles may cut the tiles of a partly filled last round in two.
+__device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s, int mg, bool halves, int n_units) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int sub = p.B >> 7;
   if (tid == 0) { s.n_active = p.n_blocks; s.contiguous = 1; }
@@ -140,6 +143,13 @@ __device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s, int m
     // a unit of its own (the pair's second CTA idles)
     const int units = (mg == 2 && (sub & 1)) ? p.m_tiles_total : p.m_tiles_total / mg;
     s.total = (s.contiguous || p.tile_filter == 2) ? run : units * p.n_tiles;
+    s.n_full = s.total;
+    if (halves && (s.contiguous || p.tile_filter == 2) && s.total >= 2 * n_units) {
+      // whole rounds of n_units tiles keep their width; if the rest fits one round even when cut in two, cut it:
+      // the last round then takes half as long
+      const int whole = (s.total / n_units) * n_units, rest = s.total - whole;
+      if (rest > 0 && 2 * rest <= n_units) { s.n_full = whole; s.total = whole + 2 * rest; }
+    }
   }
   __syncthreads();
 }
@@ -148,9 +158,15 @@ __device__ __forceinline__ void build_sched(const GemmParams& p, Sched& s, int m
 // `second` says whether m_tile + 1 is a tile of the same expert that holds tokens (an expert with an odd number
 // of tiles ends in a half-empty pair: its second CTA still supplies half of the weight tile but copies no
 // activations and writes nothing).
+// `part`: -1 for a whole weight tile, 0 / 1 for its first / second 128 rows (see Sched::n_full).
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, const Sched& s, int tile, int mg, int& m_tile,
-                                            int& n_tile, int& expert, int& second) {
+                                            int& n_tile, int& expert, int& second, int& part) {
   second = mg == 2 ? 1 : 0;
+  part = -1;
+  if (tile >= s.n_full) {
+    part = (tile - s.n_full) & 1;
+    tile = s.n_full + ((tile - s.n_full) >> 1);
+  }
   if (s.contiguous && p.tile_filter == 2) {
     const int i = tile % s.n_left;
     m_tile = s.left_m[i];
@@ -224,8 +240,8 @@ template <int BLOCK_N, int STAGES, int EPI, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
                           const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
-                          const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                          const GemmParams p) {
+                          const __grid_constant__ CUtensorMap tmap_b128, const __grid_constant__ CUtensorMap tmap_sfa,
+                          const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p) {
   // CTAS == 2: the two CTAs of a cluster form one tcgen05 cta_group::2 unit.  Each loads its own 128
   // activation rows and half of the weight tile; the even CTA issues M = 256 MMAs that read both CTAs'
   // shared memory and write both CTAs' TMEM, so a weight byte crosses L2 -> SM once per 256 rows.
@@ -260,7 +276,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   }
   const int cta_rank = CTAS == 2 ? static_cast<int>(cluster_cta_rank()) : 0;
   const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;
-  build_sched(p, sched, CTAS);
+  build_sched(p, sched, CTAS, CTAS == 1 && BLOCK_N == 256, n_units);
   const int total_tiles = sched.total;
 
   if (threadIdx.x == 0) {
@@ -309,21 +325,24 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       bool ok = true;
       constexpr int kRowsB = BLOCK_N / CTAS;  // weight rows this CTA copies per slab
       for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
-        int m_tile, n_tile, e, second;
-        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second)) continue;
+        int m_tile, n_tile, e, second, part;
+        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) continue;
         const int rows_lead = tile_copy_rows(p, m_tile);
         const int rows_peer = second ? tile_copy_rows(p, m_tile + 1) : 0;
         m_tile += cta_rank;
         const int my_rows = cta_rank == 0 ? rows_lead : rows_peer;
         const CUtensorMap* map_a = my_rows == 32 ? &tmap_a32 : (my_rows == 64 ? &tmap_a64 : &tmap_a);
-        const uint32_t stage_bytes = static_cast<uint32_t>(rows_lead + rows_peer) * kBlockK + CTAS * p.b_tx;
-        const int atom0 = (n_tile * BLOCK_N) >> 7;
+        // a half tile (single-CTA launches only) copies 128 weight rows through the 128-row map
+        const int n_row0 = n_tile * BLOCK_N + (part > 0 ? BLOCK_N / 2 : 0);
+        const uint32_t b_bytes = part >= 0 ? p.b_tx / 2 : p.b_tx;
+        const uint32_t stage_bytes = static_cast<uint32_t>(rows_lead + rows_peer) * kBlockK + CTAS * b_bytes;
+        const int atom0 = n_row0 >> 7;
         // L2 prefetch runs `p.prefetch` slabs ahead, into the next tile of this CTA when the current one ends
         int nx_n = 0, nx_e = -1;
         if (p.prefetch > 0) {
           int nm, nk;
           for (int t2 = tile + n_units; t2 < total_tiles; t2 += n_units)
-            if (decode_tile(p, sched, t2, CTAS, nm, nx_n, nx_e, nk)) break; else nx_e = -1;
+            if (decode_tile(p, sched, t2, CTAS, nm, nx_n, nx_e, nk, nk)) break; else nx_e = -1;
           if (tile == unit)
             for (int kp = 0; kp < p.prefetch && kp < p.k_blocks; ++kp)
               tma_prefetch_3d(&tmap_b, kp * kBlockK, n_tile * BLOCK_N + cta_rank * kRowsB, e);
@@ -374,7 +393,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             mbar_expect_tx(&full[stage], stage_bytes);
             if (my_rows > 0)
               tma_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
-            tma_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK, n_tile * BLOCK_N, e, &full[stage]);
+            tma_load_3d(smem + L::kOffB + stage * L::kB, part >= 0 ? &tmap_b128 : &tmap_b, kb * kBlockK, n_row0, e,
+                        &full[stage]);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -391,12 +411,16 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
-        int m_tile, n_tile, e, second;
-        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second)) continue;
+        int m_tile, n_tile, e, second, part;
+        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) continue;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-        const uint32_t sfb_off = ((n_tile * BLOCK_N) & 127) >> 5;  // a tile may start mid-atom
+        const int n_row0 = n_tile * BLOCK_N + (part > 0 ? BLOCK_N / 2 : 0);
+        const uint32_t sfb_off = (n_row0 & 127) >> 5;  // a tile may start mid-atom
+        // half tiles run N = 128 MMAs into the first 128 accumulator columns
+        const uint32_t idesc_tile = part >= 0 ? ((idesc_base & ~(0x3Fu << 17)) | (static_cast<uint32_t>(128 >> 3) << 17))
+                                              : idesc_base;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
           if (!mbar_wait(&sf_ready[stage], phase, abort_flag, p.status, 5)) { ok = false; break; }
@@ -410,7 +434,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #endif
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint32_t idesc = idesc_base | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
+            const uint32_t idesc = idesc_tile | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
             if constexpr (CTAS == 2)
               tc2_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
             else
@@ -438,8 +462,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     uint32_t phase = 0;
     bool ok = true;
     for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
-      int m_tile, n_tile, e, second;
-      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second)) continue;
+      int m_tile, n_tile, e, second, part;
+      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) continue;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait(&sf_full[stage], phase, abort_flag, p.status, 6)) { ok = false; break; }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kSfCol + stage * 16;
@@ -480,8 +504,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     const float g_lo = p.gate_lo == p.gate_lo ? p.gate_lo : -INFINITY, g_hi = p.gate_hi == p.gate_hi ? p.gate_hi : INFINITY;
     const float u_lo = p.up_lo == p.up_lo ? p.up_lo : -INFINITY, u_hi = p.up_hi == p.up_hi ? p.up_hi : INFINITY;
     for (int tile = unit; tile < total_tiles; tile += n_units) {
-      int m_tile, n_tile, e, second;
-      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second)) continue;
+      int m_tile, n_tile, e, second, part;
+      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) continue;
       m_tile += cta_rank;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after();
@@ -503,13 +527,15 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       if (p.experiment & 8) continue;
 #endif
       if (CTAS == 2 && cta_rank != 0 && !second) continue;  // half-empty pair: these rows belong to someone else
+      if (part >= 0 && half != 0) continue;                 // half tile: only 128 accumulator columns hold results
+      const int n_row0 = n_tile * BLOCK_N + (part > 0 ? BLOCK_N / 2 : 0);
 
       if constexpr (EPI == 0) {
         const int64_t k_atoms = (p.I + 127) >> 7;
         const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.n_total : nullptr;
 #pragma unroll
         for (int c = 0; c < kLd / 2; ++c) {
-          const int n0 = n_tile * BLOCK_N + half * kCW + c * 64;
+          const int n0 = n_row0 + half * kCW + c * 64;
           const int i0 = n0 >> 1;
           if (i0 >= p.I) continue;
           float g[32], u[32];
@@ -571,7 +597,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.H_out : nullptr;
 #pragma unroll
         for (int l = 0; l < kLd; ++l) {
-          const int col0 = n_tile * BLOCK_N + half * kCW + l * 32;
+          const int col0 = n_row0 + half * kCW + l * 32;
           if (col0 >= p.H_out || !valid) continue;
           uint32_t o[16];
 #pragma unroll
@@ -756,8 +782,8 @@ int make_atoms_map(CUtensorMap* map, const void* base, int64_t n_atoms) {
 }
 
 template <int BLOCK_N, int STAGES, int EPI, int CTAS>
-int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorMap& msa, const CUtensorMap& msb,
-              const GemmParams& p, cudaStream_t st) {
+int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorMap& mb128, const CUtensorMap& msa,
+              const CUtensorMap& msb, const GemmParams& p, cudaStream_t st) {
   using L = SmemLayout<BLOCK_N, STAGES, CTAS>;
   auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI, CTAS>;
   B200MOE_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kBytes));
@@ -777,9 +803,9 @@ int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorM
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    B200MOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma[0], ma[1], ma[2], mb, msa, msb, p));
+    B200MOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma[0], ma[1], ma[2], mb, mb128, msa, msb, p));
   } else {
-    kern<<<grid, kThreads, L::kBytes, st>>>(ma[0], ma[1], ma[2], mb, msa, msb, p);
+    kern<<<grid, kThreads, L::kBytes, st>>>(ma[0], ma[1], ma[2], mb, mb128, msa, msb, p);
   }
   B200MOE_LAUNCH_OK("grouped_mxfp8_gemm_kernel");
   return B200MOE_OK;
@@ -828,7 +854,7 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   // several tiles on average (prefill) and not for one short tile per expert (decode)
   const bool pair = g_cta_pair && bn == 256 && (sm_count() % 2 == 0) &&
                     (p.B % 256 == 0 || (g_cta_pair == 2 || p.m_tiles_total >= 4 * p.E));
-  CUtensorMap ma[3], mb, msa, msb;  // activation boxes of 128, 64 and 32 rows
+  CUtensorMap ma[3], mb, mb128, msa, msb;  // activation boxes of 128, 64 and 32 rows; weight boxes: tile, 128 rows
   int rc = B200MOE_OK;
   for (int i = 0; i < 3 && rc == B200MOE_OK; ++i)
     rc = make_rows_map(&ma[i], a, K, static_cast<int64_t>(p.m_tiles_total) * 128, 0, kBlockM >> i);
@@ -840,6 +866,8 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   // the copy reports the bytes it read from global memory: a 4-bit slab is 64 bytes per row there
   p.b_tx = static_cast<uint32_t>((pair ? bn / 2 : bn) * (nibbles ? kBlockK / 2 : kBlockK));
   if (rc != B200MOE_OK) return rc;
+  rc = make_rows_map(&mb128, b, K, p.n_total, p.E, 128, nibbles);  // half tiles of the single-CTA launches
+  if (rc != B200MOE_OK) return rc;
   rc = make_atoms_map(&msa, p.a_sf, static_cast<int64_t>(p.m_tiles_total) * p.k_blocks);
   if (rc != B200MOE_OK) return rc;
   rc = make_atoms_map(&msb, p.b_sf, static_cast<int64_t>(p.E) * p.b_row_atoms * p.k_blocks);
@@ -849,7 +877,7 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
     // tile an expert with an odd number of live tiles has left over (a half-empty pair would pay for a full
     // 256-row MMA: with ~1000 rows per expert that was one tile in five).
     p.tile_filter = g_split_leftover ? 1 : 0;
-    rc = epi == 0 ? launch_tc<256, 6, 0, 2>(ma, mb, msa, msb, p, st) : launch_tc<256, 6, 1, 2>(ma, mb, msa, msb, p, st);
+    rc = epi == 0 ? launch_tc<256, 6, 0, 2>(ma, mb, mb128, msa, msb, p, st) : launch_tc<256, 6, 1, 2>(ma, mb, mb128, msa, msb, p, st);
     if (rc != B200MOE_OK || !g_split_leftover) return rc;
     GemmParams p2 = p;
     p2.tile_filter = 2;
@@ -858,11 +886,11 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
     CUtensorMap mb2;
     rc = make_rows_map(&mb2, b, K, p.n_total, p.E, bn, nibbles);
     if (rc != B200MOE_OK) return rc;
-    return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb2, msa, msb, p2, st) : launch_tc<256, 4, 1, 1>(ma, mb2, msa, msb, p2, st);
+    return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb2, mb128, msa, msb, p2, st) : launch_tc<256, 4, 1, 1>(ma, mb2, mb128, msa, msb, p2, st);
   }
   if (bn == 256)
-    return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb, msa, msb, p, st) : launch_tc<256, 4, 1, 1>(ma, mb, msa, msb, p, st);
-  return epi == 0 ? launch_tc<128, 6, 0, 1>(ma, mb, msa, msb, p, st) : launch_tc<128, 6, 1, 1>(ma, mb, msa, msb, p, st);
+    return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb, mb128, msa, msb, p, st) : launch_tc<256, 4, 1, 1>(ma, mb, mb128, msa, msb, p, st);
+  return epi == 0 ? launch_tc<128, 6, 0, 1>(ma, mb, mb128, msa, msb, p, st) : launch_tc<128, 6, 1, 1>(ma, mb, mb128, msa, msb, p, st);
 }
 
 }  // namespace
