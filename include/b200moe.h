@@ -290,6 +290,20 @@ int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32_t* pair_to
                                  int rank, int world, int h_packed_order, void* const* xq_peers, void* const* sf_peers,
                                  void* const* aff_peers, void* const* src_peers, int64_t cap_rows,
                                  b200moe_stream_t stream);
+/* The down contraction of an expert-parallel step with the return fused into its epilogue: instead of writing
+ * y_pos and copying it out afterwards (b200moe_ep_return_rows), every result row is stored straight into the
+ * buffer of the GPU its token came from -- row (row_src[r] & 0xffffff) of back_peers[row_src[r] >> 24], plain
+ * peer stores over NVLink -- while the tensor cores work on the next tile.  Arguments as
+ * b200moe_grouped_gemm2_scale with per-row affinities (row_affinity fp32 [cap_rows]) and row_valid in the
+ * place of token_position_to_id; follow it with b200moe_ep_signal_wait(slot 2) as after ep_return_rows.
+ * The reference leaves this exchange to an external all_to_all_v (experimental/collectives/topk_reduce.py:31-62). */
+int b200moe_ep_gemm2_scale_return(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
+                                  const uint8_t* w2_sf, int w_format, const float* bias_d,
+                                  const int32_t* block_to_expert, const int32_t* conditions,
+                                  const int32_t* tile_flags, const int32_t* row_valid, int64_t cap_rows, int n_blocks,
+                                  int B, int E_local, int H, int I, const float* row_affinity, const int32_t* row_src,
+                                  void* const* back_peers, int world, int64_t back_rows, int32_t* status, int impl,
+                                  b200moe_stream_t stream);
 int b200moe_ep_return_rows(const void* y_pos_bf16, const int32_t* row_valid, const int32_t* row_src,
                            void* const* back_peers, int world, int64_t cap_rows, int H, int64_t back_rows,
                            b200moe_stream_t stream);

@@ -82,6 +82,9 @@ SIGNATURES = {
     "b200moe_ep_dispatch_quantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_int64, c_void_p]),
+    "b200moe_ep_gemm2_scale_return": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                              c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p]),
     "b200moe_ep_return_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int64,
                                        c_void_p]),
 }

@@ -63,6 +63,11 @@ struct GemmParams {
   int aff_per_row;  // 0: table [rows, E] addressed tok*E + e; 1: vector [rows] addressed tok
   __nv_bfloat16* y_pos;
   int H_out;
+  // expert parallelism: when row_src is set, row r of the result goes to row (row_src[r] & 0xffffff) of the buffer
+  // peer_out[row_src[r] >> 24] (the GPU the token came from, over NVLink) instead of y_pos
+  const int32_t* row_src;
+  int64_t peer_rows;
+  void* peer_out[8];
   int32_t* status;
   unsigned long long* clock_probe;  // optional: CTA 0 writes {SM cycles, nanoseconds} spent in the kernel
   int w_format;     // element format of the weight operand (B200MOE_W_*); activations are e4m3
@@ -589,7 +594,15 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         }
       } else {
         const int tok = p.tpi ? p.tpi[row] : static_cast<int>(row);
-        const bool valid = tok >= 0 && tok < p.hidden_rows;
+        bool valid = tok >= 0 && tok < p.hidden_rows;
+        __nv_bfloat16* out_row = p.y_pos + row * p.H_out;
+        if (p.row_src != nullptr && valid) {
+          const int32_t src = p.row_src[row];
+          const int dst_rank = (src >> 24) & 0x7f;
+          const int64_t dst_row = src & 0xffffff;
+          valid = dst_rank < 8 && dst_row < p.peer_rows && p.peer_out[dst_rank] != nullptr;
+          if (valid) out_row = static_cast<__nv_bfloat16*>(p.peer_out[dst_rank]) + dst_row * p.H_out;
+        }
         float aff = 1.0f;
         if (valid && p.aff != nullptr)
           aff = load_as_float(p.aff, p.aff_per_row ? static_cast<int64_t>(tok) : static_cast<int64_t>(tok) * p.E + e,
@@ -607,7 +620,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             const __nv_bfloat162 b2 = __floats2bfloat162_rn(a0 * aff, a1 * aff);
             o[j] = *reinterpret_cast<const uint32_t*>(&b2);
           }
-          uint4* dst = reinterpret_cast<uint4*>(p.y_pos + row * p.H_out + col0);
+          uint4* dst = reinterpret_cast<uint4*>(out_row + col0);
 #pragma unroll
           for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         }
@@ -739,7 +752,15 @@ __global__ void simt_gemm2_kernel(const uint8_t* m, const uint8_t* w, GemmParams
     if (p.aff)
       y *= load_as_float(p.aff, p.aff_per_row ? static_cast<int64_t>(tok) : static_cast<int64_t>(tok) * p.E + e,
                          p.aff_dtype);
-    p.y_pos[row * p.H_out + h] = __float2bfloat16_rn(y);
+    __nv_bfloat16* out_row = p.y_pos + row * p.H_out;
+    if (p.row_src != nullptr) {
+      const int32_t src = p.row_src[row];
+      const int dst_rank = (src >> 24) & 0x7f;
+      const int64_t dst_row = src & 0xffffff;
+      if (dst_rank >= 8 || dst_row >= p.peer_rows || p.peer_out[dst_rank] == nullptr) continue;
+      out_row = static_cast<__nv_bfloat16*>(p.peer_out[dst_rank]) + dst_row * p.H_out;
+    }
+    out_row[h] = __float2bfloat16_rn(y);
   }
 }
 
@@ -962,16 +983,15 @@ extern "C" int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_
   return run_gemm(0, x_codes, w1_dev, p, H, impl, st);
 }
 
-extern "C" int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
-                                           const uint8_t* w2_sf, int w_format, const float* bias_d,
-                                           const int32_t* block_to_expert,
-                                           const int32_t* conditions, const int32_t* tile_flags,
-                                           const int32_t* token_position_to_id, int hidden_rows, int n_blocks, int B,
-                                           int E, int H, int I, const void* affinities, int aff_dtype,
-                                           int aff_per_row, void* y_pos_bf16, int32_t* status, int impl,
-                                           b200moe_stream_t stream) {
-  B200MOE_REQUIRE(m_codes && m_sf && w2_dev && w2_sf && block_to_expert && y_pos_bf16, B200MOE_ERR_INVALID,
-                  "grouped_gemm2: null pointer argument");
+namespace {
+int gemm2_impl(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev, const uint8_t* w2_sf, int w_format,
+               const float* bias_d, const int32_t* block_to_expert, const int32_t* conditions,
+               const int32_t* tile_flags, const int32_t* token_position_to_id, int hidden_rows, int n_blocks, int B,
+               int E, int H, int I, const void* affinities, int aff_dtype, int aff_per_row, void* y_pos_bf16,
+               const int32_t* row_src, void* const* peer_out, int world, int64_t peer_rows, int32_t* status, int impl,
+               b200moe_stream_t stream) {
+  B200MOE_REQUIRE(m_codes && m_sf && w2_dev && w2_sf && block_to_expert && (y_pos_bf16 || row_src),
+                  B200MOE_ERR_INVALID, "grouped_gemm2: null pointer argument");
   B200MOE_REQUIRE(H % 32 == 0 && H > 0, B200MOE_ERR_INVALID, "grouped_gemm2: H must be a positive multiple of 32, got %d", H);
   B200MOE_REQUIRE(aff_dtype == B200MOE_F32 || aff_dtype == B200MOE_BF16, B200MOE_ERR_INVALID,
                   "grouped_gemm2: affinities must be fp32 or bf16");
@@ -996,5 +1016,41 @@ extern "C" int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t
   p.H_out = H;
   p.I = I;
   p.status = status;
+  if (row_src != nullptr) {
+    B200MOE_REQUIRE(peer_out != nullptr && world >= 1 && world <= 8 && token_position_to_id != nullptr,
+                    B200MOE_ERR_INVALID, "grouped_gemm2: peer output needs 1..8 peer buffers and the row validity list");
+    p.row_src = row_src;
+    p.peer_rows = peer_rows;
+    for (int i = 0; i < 8; ++i) p.peer_out[i] = i < world ? peer_out[i] : nullptr;
+    for (int i = 0; i < world; ++i)
+      B200MOE_REQUIRE(p.peer_out[i] != nullptr, B200MOE_ERR_INVALID, "grouped_gemm2: peer buffer %d is null", i);
+  }
   return run_gemm(1, m_codes, w2_dev, p, I, impl, static_cast<cudaStream_t>(stream));
 }
+}  // namespace
+
+extern "C" int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
+                                           const uint8_t* w2_sf, int w_format, const float* bias_d,
+                                           const int32_t* block_to_expert, const int32_t* conditions,
+                                           const int32_t* tile_flags, const int32_t* token_position_to_id,
+                                           int hidden_rows, int n_blocks, int B, int E, int H, int I,
+                                           const void* affinities, int aff_dtype, int aff_per_row, void* y_pos_bf16,
+                                           int32_t* status, int impl, b200moe_stream_t stream) {
+  return gemm2_impl(m_codes, m_sf, w2_dev, w2_sf, w_format, bias_d, block_to_expert, conditions, tile_flags,
+                    token_position_to_id, hidden_rows, n_blocks, B, E, H, I, affinities, aff_dtype, aff_per_row,
+                    y_pos_bf16, nullptr, nullptr, 0, 0, status, impl, stream);
+}
+
+extern "C" int b200moe_ep_gemm2_scale_return(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
+                                             const uint8_t* w2_sf, int w_format, const float* bias_d,
+                                             const int32_t* block_to_expert, const int32_t* conditions,
+                                             const int32_t* tile_flags, const int32_t* row_valid, int64_t cap_rows,
+                                             int n_blocks, int B, int E_local, int H, int I, const float* row_affinity,
+                                             const int32_t* row_src, void* const* back_peers, int world,
+                                             int64_t back_rows, int32_t* status, int impl, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(row_valid && row_src && back_peers, B200MOE_ERR_INVALID, "ep_gemm2_scale_return: null pointer argument");
+  return gemm2_impl(m_codes, m_sf, w2_dev, w2_sf, w_format, bias_d, block_to_expert, conditions, tile_flags, row_valid,
+                    static_cast<int>(cap_rows), n_blocks, B, E_local, H, I, row_affinity, B200MOE_F32, 1, nullptr,
+                    row_src, back_peers, world, back_rows, status, impl, stream);
+}
+

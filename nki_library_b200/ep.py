@@ -220,8 +220,9 @@ class PeerExpertParallelMoE:
     def __init__(self, router_w, weights: ExpertWeights, num_experts: int, top_k: int, block_size: int,
                  tokens_per_rank: int, group=None, router_bias=None, capacity_factor: float = 2.5,
                  router_act=RouterActFnType.SOFTMAX, router_pre_norm=True, norm_topk_prob=True,
-                 act_fn=ActFnType.SiLU):
+                 act_fn=ActFnType.SiLU, fuse_return: bool = True):
         self.group = group
+        self.fuse_return = fuse_return  # down contraction stores its rows into the peers (no separate return launch)
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         _lib.kernel_assert(num_experts % self.world == 0,
@@ -278,7 +279,8 @@ class PeerExpertParallelMoE:
         self.timers = None
         # router 2, grouping 3, count exchange, dispatch, wait, plan, contractions (CTA-pair launch + left-over
         # launch each when the block size allows pairs), return, wait, combine
-        self.kernels_per_forward = 2 + 3 + 1 + 1 + 1 + 1 + (4 if self.B % 256 == 0 else 2) + 1 + 1 + 1
+        self.kernels_per_forward = (2 + 3 + 1 + 1 + 1 + 1 + (4 if self.B % 256 == 0 else 2) + (0 if fuse_return else 1)
+                                    + 1 + 1)
         self._graph = None
 
     def forward(self, hidden: torch.Tensor) -> torch.Tensor:
@@ -323,13 +325,22 @@ class PeerExpertParallelMoE:
                   _lib.ptr(self.tile_flags), self.n_blocks_cap, B, E_L, H, I, ops.act_fn.value, nan, nan, nan, nan,
                   _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(self.status[1:]), 0, st)
         mark("t2")
-        _lib.call("b200moe_grouped_gemm2_scale", _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(w.w2),
-                  _lib.ptr(w.w2_sf), w.w_format, _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond),
-                  _lib.ptr(self.tile_flags), _lib.ptr(self.row_valid), self.cap_rows, self.n_blocks_cap, B, E_L, H, I,
-                  _lib.ptr(self.row_aff), _lib.F32, 1, _lib.ptr(self.y_pos), _lib.ptr(self.status[2:]), 0, st)
-        mark("t3")
-        _lib.call("b200moe_ep_return_rows", _lib.ptr(self.y_pos), _lib.ptr(self.row_valid), _lib.ptr(self.row_src),
-                  self.p_back, G, self.cap_rows, H, T * K, st)
+        if self.fuse_return:
+            # the down contraction's epilogue stores every row into the GPU its token came from
+            _lib.call("b200moe_ep_gemm2_scale_return", _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(w.w2),
+                      _lib.ptr(w.w2_sf), w.w_format, _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond),
+                      _lib.ptr(self.tile_flags), _lib.ptr(self.row_valid), self.cap_rows, self.n_blocks_cap, B, E_L,
+                      H, I, _lib.ptr(self.row_aff), _lib.ptr(self.row_src), self.p_back, G, T * K,
+                      _lib.ptr(self.status[2:]), 0, st)
+            mark("t3")
+        else:
+            _lib.call("b200moe_grouped_gemm2_scale", _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(w.w2),
+                      _lib.ptr(w.w2_sf), w.w_format, _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond),
+                      _lib.ptr(self.tile_flags), _lib.ptr(self.row_valid), self.cap_rows, self.n_blocks_cap, B, E_L,
+                      H, I, _lib.ptr(self.row_aff), _lib.F32, 1, _lib.ptr(self.y_pos), _lib.ptr(self.status[2:]), 0, st)
+            mark("t3")
+            _lib.call("b200moe_ep_return_rows", _lib.ptr(self.y_pos), _lib.ptr(self.row_valid),
+                      _lib.ptr(self.row_src), self.p_back, G, self.cap_rows, H, T * K, st)
         _lib.call("b200moe_ep_signal_wait", self.p_flags, self.rank, G, 2, epoch, status, st)
         _lib.call("b200moe_combine", _lib.ptr(self.back), _lib.ptr(self.inv), T, K, H, _lib.ptr(self.out), st)
         return self.out

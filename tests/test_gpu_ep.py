@@ -45,7 +45,8 @@ def _worker(rank, world, port, results, backend):
             out2 = layer.forward(x).clone()
             rows = layer.last_rows_received
         else:
-            layer = PeerExpertParallelMoE(torch.from_numpy(router_w).cuda(), local, E, K, B, T_LOCAL)
+            layer = PeerExpertParallelMoE(torch.from_numpy(router_w).cuda(), local, E, K, B, T_LOCAL,
+                                          fuse_return=backend == "peer")
             out = layer.forward(x).clone()
             out2 = layer.forward(x).clone()
             out3 = layer.forward(x).clone()
@@ -58,8 +59,11 @@ def _worker(rank, world, port, results, backend):
         dist.destroy_process_group()
 
 
-def test_peer_memory_exchange_single_rank():
-    """World size 1: every 'peer' is this GPU, so the dispatch / plan / return kernels run without a second device."""
+@pytest.mark.parametrize("fuse_return", [True, False])
+def test_peer_memory_exchange_single_rank(fuse_return):
+    """World size 1: every 'peer' is this GPU, so the dispatch / plan / return kernels run without a second device.
+    ``fuse_return``: the down contraction stores its rows into the (peer) result buffer itself, or a separate
+    kernel copies them out of y_pos."""
     import nki_library_b200 as m
     from moe_testlib import bf16_values, max_rel
     from nki_library_b200.ep import PeerExpertParallelMoE
@@ -71,7 +75,8 @@ def test_peer_memory_exchange_single_rank():
         hidden, router_w, w_np = _inputs(0)
         full = m.prepare_from_rows(*(torch.from_numpy(a).cuda() for a in w_np))
         x = torch.from_numpy(hidden).to(torch.bfloat16).cuda()
-        layer = PeerExpertParallelMoE(torch.from_numpy(router_w).cuda(), full, E, K, B, T_LOCAL)
+        layer = PeerExpertParallelMoE(torch.from_numpy(router_w).cuda(), full, E, K, B, T_LOCAL,
+                                      fuse_return=fuse_return)
         out = layer.forward(x).clone()
         out2 = layer.forward(x).clone()
         assert not any(layer.device_status()), layer.device_status()
@@ -88,7 +93,7 @@ def test_peer_memory_exchange_single_rank():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("backend", ["nccl", "peer"])
+@pytest.mark.parametrize("backend", ["nccl", "peer", "peer_unfused"])
 def test_expert_parallel_two_gpus_matches_oracle_and_single_gpu(backend):
     import nki_library_b200 as m
     from moe_testlib import bf16_values, max_rel
@@ -97,7 +102,8 @@ def test_expert_parallel_two_gpus_matches_oracle_and_single_gpu(backend):
     world = 2
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(world, 29711 if backend == "nccl" else 29712, results, backend), nprocs=world, join=True)
+    port = {"nccl": 29711, "peer": 29712, "peer_unfused": 29713}[backend]
+    mp.spawn(_worker, args=(world, port, results, backend), nprocs=world, join=True)
     rows = 0
     for rank in range(world):
         hidden, router_w, w_np = _inputs(rank)
