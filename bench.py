@@ -317,7 +317,7 @@ def run_ours(args, cfg, name):
         if args.ep_backend == "peer":
             # dispatch / combine by this library's own kernels storing into peer GPUs' memory (NVLink)
             layer = PeerExpertParallelMoE(router_w.to(dev), weights, E, K, B, T, router_bias=bias_d,
-                                          capacity_factor=args.capacity_factor, fuse_return=not args.no_fuse_return)
+                                          capacity_factor=args.capacity_factor, fuse_return={"auto": None, "on": True, "off": False}[args.fuse_return])
 
             def forward(h, timers=None):
                 layer.timers = timers
@@ -526,9 +526,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cta-pair", type=int, default=-1, help="1/0: force the cta_group::2 GEMM on/off (-1 = default)")
     ap.add_argument("--prefetch", type=int, default=-2, help="weight slabs prefetched into L2 (-1 = by shape)")
-    ap.add_argument("--no-fuse-return", action="store_true",
-                    help="expert parallelism: copy result rows to their GPUs in a separate kernel instead of the "
-                         "down contraction's epilogue")
+    ap.add_argument("--fuse-return", default="auto", choices=["auto", "on", "off"],
+                    help="expert parallelism: let the down contraction's epilogue store result rows into their GPUs "
+                         "(on), copy them in a separate kernel (off), or choose by rank count (auto)")
     ap.add_argument("--no-decode-leg", action="store_true", help="omit the secondary decode measurements (profiling runs)")
     ap.add_argument("--router-path", type=int, default=-1, help="1 split-K router, 2 tcgen05 router (-1 = by shape)")
     ap.add_argument("--tile-n", type=int, default=0, help="weight rows per GEMM tile (128/192/256; 0 = library default)")
