@@ -73,12 +73,6 @@ __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int x, i
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(map), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(dst)),
-               "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
 
 // ---- thread-block-pair (cta_group::2) variants --------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
@@ -126,9 +120,6 @@ __device__ __forceinline__ void tc2_commit_pair(uint64_t* bar) {
                "h"(mask)
                : "memory");
 }
-__device__ __forceinline__ void tc2_cp_sf(uint32_t taddr, uint64_t desc) {
-  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
-}
 __device__ __forceinline__ void tc2_mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
   asm volatile(
@@ -146,9 +137,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
-}
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
 }
 __device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
@@ -193,13 +181,6 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
   d |= static_cast<uint64_t>(1024 >> 4) << 32;     // stride byte offset
   d |= static_cast<uint64_t>(1) << 46;             // descriptor version (Blackwell)
   d |= static_cast<uint64_t>(2) << 61;             // SWIZZLE_128B
-  return d;
-}
-// Scale atom: 32 rows of 16 bytes, no swizzle, 8-row groups 128 B apart.
-__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
-  uint64_t d = static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(128 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
   return d;
 }
 // kind::mxf8f6f4 block-scaled instruction descriptor: e4m3 activations (A format, bits 7-9 = 0), UE8M0
