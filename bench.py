@@ -171,7 +171,7 @@ def make_inputs(cfg, device, seed):
 
 
 # ------------------------------------------------------------------ CPU legs (oracle)
-def cpu_sample(cfg, steps, warmup, threads):
+def cpu_sample(cfg, steps, warmup, threads, budget_s=None):
     """Time the oracle restatement of the reference's per-block golden loop on a bounded sample.
 
     Sample: ``n_rows`` token-expert rows of one expert at the workload's H and I
@@ -201,8 +201,10 @@ def cpu_sample(cfg, steps, warmup, threads):
         if it >= warmup:
             times.append(dt)
         del ew, y
+        if budget_s is not None and times and sum(times) + times[-1] > budget_s:
+            break  # the next step would overrun the wall-clock budget of this leg
     t = sum(times) / len(times)
-    return dict(value=n_rows / K / t, seconds_per_step=t, rows=n_rows,
+    return dict(value=n_rows / K / t, seconds_per_step=t, rows=n_rows, steps=len(times),
                 sample=f"{n_rows} token-expert rows through one expert (dequantise weights + quantise/gate-up/SwiGLU/"
                        f"re-quantise/down) at H={H}, I={I}; tokens/s = rows/K/time")
 
@@ -212,11 +214,13 @@ def run_reference(args, cfg, name):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
-    r = cpu_sample(cfg, steps, 1 if args.warmup > 0 else 0, threads)
+    # every step is the same bounded sample; run the K steps asked for unless that would take over ~2.5 minutes
+    warm = max(0, min(args.warmup, 2))
+    r = cpu_sample(cfg, max(1, args.steps), warm, threads, budget_s=150.0)
+    steps = r["steps"]
     line = {
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": r["value"], "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": 1 if args.warmup > 0 else 0,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm,
         "ms_per_step": r["seconds_per_step"] * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "mxfp8_e4m3", "data": "synthetic", "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}},
         "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": threads, "kind": "port",
