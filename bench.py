@@ -475,7 +475,7 @@ def run_ours(args, cfg, name):
                         "peak_source": f"{peaks['source']} copy bandwidth",
                         "layer_gbs": work["decode_bytes"] / (ms_step * 1e-3) / 1e9}
         cpu = (dict(value=None, sample="skipped (--skip-cpu)") if args.skip_cpu
-               else cpu_sample(cfg, 2, 1, os.cpu_count() or 1))
+               else cpu_sample(cfg, 4, 1, os.cpu_count() or 1))
         decode = decode_mxfp4 = None
         if world == 1 and name == "mixtral_prefill" and not args.no_decode_leg:
             decode = decode_leg(weights, peaks, dev, args.weight_format)
