@@ -3,8 +3,9 @@
 This is the call sequence the reference leaves to its caller for prefill
 (router and grouping sub-kernels, then ``moe_cte``) and fuses for decode in
 ``moe_block_tkg`` (core/moe_block/moe_block_tkg.py:192-340, without the RMSNorm).
-All buffers are allocated once; a forward pass launches eight kernels on the
-current stream and never synchronises with the host.
+All buffers are allocated once; a forward pass launches nine to twelve kernels
+(``kernels_per_forward``) on the current stream and never synchronises with the
+host.
 """
 
 from __future__ import annotations
