@@ -587,9 +587,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             for (int j = 0; j < 8; ++j)
               w[j] = pack4_e4m3(g[4 * j] * f1 * f2, g[4 * j + 1] * f1 * f2, g[4 * j + 2] * f1 * f2, g[4 * j + 3] * f1 * f2);
           }
-          uint4* dst = reinterpret_cast<uint4*>(p.m_codes + row * p.I + i0);
-          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          st_global_256(p.m_codes + row * p.I + i0, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
           p.m_sf[sf_atom_offset(row, i0 >> 5, k_atoms)] = mx_block_scale_byte(mx);
         }
       } else {
@@ -620,9 +618,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             const __nv_bfloat162 b2 = __floats2bfloat162_rn(a0 * aff, a1 * aff);
             o[j] = *reinterpret_cast<const uint32_t*>(&b2);
           }
-          uint4* dst = reinterpret_cast<uint4*>(out_row + col0);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          for (int j = 0; j < 2; ++j)
+            st_global_256(out_row + col0 + 16 * j, o[8 * j], o[8 * j + 1], o[8 * j + 2], o[8 * j + 3], o[8 * j + 4],
+                          o[8 * j + 5], o[8 * j + 6], o[8 * j + 7]);
         }
       }
     }
@@ -956,6 +955,8 @@ extern "C" int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_
                   "grouped_gemm1: null pointer argument");
   B200MOE_REQUIRE(I % 32 == 0 && I > 0, B200MOE_ERR_INVALID, "grouped_gemm1: I must be a positive multiple of 32, got %d", I);
   B200MOE_REQUIRE(act_fn >= 0 && act_fn <= 3, B200MOE_ERR_INVALID, "grouped_gemm1: unknown activation %d", act_fn);
+  B200MOE_REQUIRE((reinterpret_cast<uintptr_t>(m_codes) & 31) == 0, B200MOE_ERR_INVALID,
+                  "grouped_gemm1: m_codes must be 32-byte aligned (the epilogue stores 32 bytes at a time)");
   GemmParams p{};
   p.a_sf = x_sf;
   p.b_sf = w1_sf;
@@ -1023,7 +1024,11 @@ int gemm2_impl(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_de
     p.peer_rows = peer_rows;
     for (int i = 0; i < 8; ++i) p.peer_out[i] = i < world ? peer_out[i] : nullptr;
     for (int i = 0; i < world; ++i)
-      B200MOE_REQUIRE(p.peer_out[i] != nullptr, B200MOE_ERR_INVALID, "grouped_gemm2: peer buffer %d is null", i);
+      B200MOE_REQUIRE(p.peer_out[i] != nullptr && (reinterpret_cast<uintptr_t>(p.peer_out[i]) & 31) == 0,
+                      B200MOE_ERR_INVALID, "grouped_gemm2: peer buffer %d is null or not 32-byte aligned", i);
+  } else {
+    B200MOE_REQUIRE((reinterpret_cast<uintptr_t>(y_pos_bf16) & 31) == 0, B200MOE_ERR_INVALID,
+                    "grouped_gemm2: y_pos must be 32-byte aligned (the epilogue stores 32 bytes at a time)");
   }
   return run_gemm(1, m_codes, w2_dev, p, I, impl, static_cast<cudaStream_t>(stream));
 }

@@ -174,6 +174,14 @@ __device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]
       : "memory");
 }
 
+// 32-byte store (one full sector per thread); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_256(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e,
+                                              uint32_t f, uint32_t g, uint32_t h) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e),
+               "r"(f), "r"(g), "r"(h)
+               : "memory");
+}
+
 // K-major operand tile, rows of 128 bytes, 128B swizzle: 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
   uint64_t d = static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
