@@ -225,10 +225,11 @@ class PeerExpertParallelMoE:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         # The down contraction can store its rows into the peers itself (no separate return launch).  Its epilogue
-        # owns one row per thread, so those stores are 16-byte pieces; measured per step on B200 / NVSwitch: 1.465 vs
-        # 1.491 ms at 2 ranks, but 1.58 vs 1.53 ms at 4 and 1.68 vs 1.59 ms at 8, where most rows leave the GPU and
-        # the coalesced copy kernel uses the links better.  Default: fused up to 2 ranks.
-        self.fuse_return = (self.world <= 2) if fuse_return is None else bool(fuse_return)
+        # owns one row per thread and stores 32 bytes at a time; measured per step on B200 / NVSwitch against the
+        # separate, fully coalesced copy kernel: 1.423 vs 1.470 ms at 2 ranks, 1.482 vs 1.546 ms at 4.  At 8 ranks
+        # it was only measured with 16-byte stores, which lost everywhere beyond 2 ranks (1.68 vs 1.59 ms), so the
+        # default stays separate there.
+        self.fuse_return = (self.world <= 4) if fuse_return is None else bool(fuse_return)
         fuse_return = self.fuse_return
         _lib.kernel_assert(num_experts % self.world == 0,
                            f"num_experts ({num_experts}) must be divisible by the number of ranks ({self.world})")
