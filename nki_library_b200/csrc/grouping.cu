@@ -5,7 +5,7 @@
 // smaller id), computed from per-chunk bitmaps with popcounts -- no atomics
 // decide an ordering.
 //
-// Three launches: (1) per 256-token chunk, build a [columns x 256-bit] bitmap in
+// Three launches (one, with block barriers in between, when all tokens fit a single chunk): (1) per 256-token chunk, build a [columns x 256-bit] bitmap in
 // shared memory and emit per-chunk column counts; (2) one CTA turns the counts
 // into per-chunk prefixes, per-expert block ranges, block_to_expert and
 // conditions; (3) per chunk, rebuild the bitmap and scatter token ids.
@@ -46,7 +46,7 @@ __device__ __forceinline__ void build_bitmap(const GroupArgs& a, int chunk, uint
     for (int c0 = 0; c0 < a.n_cols; c0 += 32) {
       const int c = c0 + lane;
       uint32_t word = 0;
-      if (c < a.n_cols) {
+      if (c < a.n_cols && warp < kWords) {  // one warp per bitmap word; extra warps of a larger CTA idle here
         for (int j = 0; j < 32; ++j) {
           const int t = t0 + warp * 32 + j;
           if (t < a.T) {
@@ -61,9 +61,8 @@ __device__ __forceinline__ void build_bitmap(const GroupArgs& a, int chunk, uint
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(kThreads) group_count_kernel(GroupArgs a, int32_t* chunk_counts, int32_t* fill_ptr,
-                                                               int64_t fill_n, int32_t fill_val) {
-  extern __shared__ uint32_t bits[];
+__device__ __forceinline__ void count_phase(const GroupArgs& a, uint32_t* bits, int32_t* chunk_counts,
+                                            int32_t* fill_ptr, int64_t fill_n, int32_t fill_val) {
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < fill_n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x)
     fill_ptr[i] = fill_val;
@@ -76,11 +75,16 @@ __global__ void __launch_bounds__(kThreads) group_count_kernel(GroupArgs a, int3
   }
 }
 
+__global__ void __launch_bounds__(kThreads) group_count_kernel(GroupArgs a, int32_t* chunk_counts, int32_t* fill_ptr,
+                                                               int64_t fill_n, int32_t fill_val) {
+  extern __shared__ uint32_t bits[];
+  count_phase(a, bits, chunk_counts, fill_ptr, fill_n, fill_val);
+}
+
 // mode 0: find_nonzero_indices (column c writes at c*T); mode 1: block grouping.
-__global__ void __launch_bounds__(1024) group_scan_kernel(int32_t* chunk_counts, int n_chunks, int n_cols, int mode,
-                                                          int T, int B, int N, int mx_conditions, int32_t* counts,
-                                                          int64_t* col_base, int32_t* block_to_expert,
-                                                          int32_t* conditions, int32_t* status) {
+__device__ __forceinline__ void scan_phase(int32_t* chunk_counts, int n_chunks, int n_cols, int mode, int T, int B,
+                                           int N, int mx_conditions, int32_t* counts, int64_t* col_base,
+                                           int32_t* block_to_expert, int32_t* conditions, int32_t* status) {
   __shared__ int s_bpe[1024];
   __shared__ int s_first[1024];
   __shared__ int s_npad;
@@ -96,7 +100,7 @@ __global__ void __launch_bounds__(1024) group_scan_kernel(int32_t* chunk_counts,
   }
   if (mode == 0) {
     if (c < n_cols) col_base[c] = static_cast<int64_t>(c) * T;
-    return;
+    return;  // (returns to the caller: the fused single-chunk kernel goes on to its scatter phase)
   }
   s_bpe[c] = (c < n_cols) ? (total + B - 1) / B : 0;
   __syncthreads();
@@ -122,11 +126,17 @@ __global__ void __launch_bounds__(1024) group_scan_kernel(int32_t* chunk_counts,
   for (int i = c; i < n_cond; i += blockDim.x) conditions[i] = (i < n_cond - n_zero) ? 1 : 0;
 }
 
-__global__ void __launch_bounds__(kThreads) group_scatter_kernel(GroupArgs a, const int32_t* chunk_prefix,
-                                                                 const int64_t* col_base, int64_t out_len,
-                                                                 int32_t* out_ids, int32_t* inverse_map) {
-  extern __shared__ uint32_t bits[];
-  build_bitmap(a, blockIdx.x, bits);
+__global__ void __launch_bounds__(1024) group_scan_kernel(int32_t* chunk_counts, int n_chunks, int n_cols, int mode,
+                                                          int T, int B, int N, int mx_conditions, int32_t* counts,
+                                                          int64_t* col_base, int32_t* block_to_expert,
+                                                          int32_t* conditions, int32_t* status) {
+  scan_phase(chunk_counts, n_chunks, n_cols, mode, T, B, N, mx_conditions, counts, col_base, block_to_expert,
+             conditions, status);
+}
+
+__device__ __forceinline__ void scatter_phase(const GroupArgs& a, const uint32_t* bits, const int32_t* chunk_prefix,
+                                              const int64_t* col_base, int64_t out_len, int32_t* out_ids,
+                                              int32_t* inverse_map) {
   const int t0 = blockIdx.x * kChunk;
   for (int i = threadIdx.x; i < a.n_cols * kWords; i += blockDim.x) {
     const int c = i / kWords, w = i - c * kWords;
@@ -162,6 +172,31 @@ __global__ void __launch_bounds__(kThreads) group_scatter_kernel(GroupArgs a, co
       inverse_map[static_cast<int64_t>(t) * a.K + (i - tl * a.K)] = pos;
     }
   }
+}
+
+__global__ void __launch_bounds__(kThreads) group_scatter_kernel(GroupArgs a, const int32_t* chunk_prefix,
+                                                                 const int64_t* col_base, int64_t out_len,
+                                                                 int32_t* out_ids, int32_t* inverse_map) {
+  extern __shared__ uint32_t bits[];
+  build_bitmap(a, blockIdx.x, bits);
+  scatter_phase(a, bits, chunk_prefix, col_base, out_len, out_ids, inverse_map);
+}
+
+// All three phases in one CTA for inputs of a single 256-token chunk (decode batches): the bitmap is built once
+// and the phases are separated by block barriers instead of kernel boundaries.
+__global__ void __launch_bounds__(1024) group_single_chunk_kernel(GroupArgs a, int mode, int B, int N, int mx_conditions,
+                                                                  int32_t* chunk_counts, int64_t* col_base,
+                                                                  int64_t out_len, int32_t fill_val, int32_t* out_ids,
+                                                                  int32_t* counts, int32_t* block_to_expert,
+                                                                  int32_t* conditions, int32_t* inverse_map,
+                                                                  int32_t* status) {
+  extern __shared__ uint32_t bits[];
+  count_phase(a, bits, chunk_counts, out_ids, out_len, fill_val);
+  __syncthreads();
+  scan_phase(chunk_counts, 1, a.n_cols, mode, a.T, B, N, mx_conditions, counts, col_base, block_to_expert, conditions,
+             status);
+  __syncthreads();
+  scatter_phase(a, bits, chunk_counts, col_base, out_len, out_ids, inverse_map);
 }
 
 __global__ void cumsum_kernel(const void* x, int dtype, int64_t cols, void* out) {
@@ -258,6 +293,13 @@ int run_grouping(const GroupArgs& a, int mode, int B, int N, int mx_conditions, 
                                                  ((static_cast<size_t>(n_chunks) * a.n_cols * 4 + 255) / 256) * 256);
   const size_t smem = static_cast<size_t>(a.n_cols) * kWords * 4;
   if (status) B200MOE_CUDA_OK(cudaMemsetAsync(status, 0, 4, st));
+  if (n_chunks == 1) {
+    group_single_chunk_kernel<<<1, 1024, smem, st>>>(a, mode, B, N, mx_conditions, chunk_counts, col_base, out_len,
+                                                     fill_val, out_ids, counts, block_to_expert, conditions,
+                                                     inverse_map, status);
+    B200MOE_LAUNCH_OK("group_single_chunk_kernel");
+    return B200MOE_OK;
+  }
   group_count_kernel<<<n_chunks, kThreads, smem, st>>>(a, chunk_counts, out_ids, out_len, fill_val);
   B200MOE_LAUNCH_OK("group_count_kernel");
   group_scan_kernel<<<1, 1024, 0, st>>>(chunk_counts, n_chunks, a.n_cols, mode, a.T, B, N, mx_conditions, counts,

@@ -50,11 +50,12 @@ class MoELayer:
         self.ws = pipeline.BlockWorkspace(self.N * B, self.H, self.I, dev)
         self.out = torch.empty((T, self.H), dtype=torch.bfloat16, device=dev)
         # launches per forward pass: router (logits + ranking, or weight transpose + tcgen05 logits + ranking for
-        # large T), 3 grouping, quantise, the contractions (CTA-pair launch + left-over launch each when the
+        # large T), grouping (3, or 1 up to 256 tokens), quantise, the contractions (CTA-pair launch + left-over launch each when the
         # library takes its pair path, else one each), combine -- mirrors the library's own shape rules
         router_launches = 3 if (T >= 8192 and E <= 256 and self.H % 64 == 0) else 2
         pair_path = B % 256 == 0 or self.N * (B // 128) >= 4 * E
-        self.kernels_per_forward = router_launches + 3 + 1 + (4 if pair_path else 2) + 1
+        group_launches = 1 if T <= 256 else 3  # one 256-token chunk: the three grouping phases share a CTA
+        self.kernels_per_forward = router_launches + group_launches + 1 + (4 if pair_path else 2) + 1
 
     def forward(self, hidden: torch.Tensor, timers: Optional[dict] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
