@@ -237,7 +237,9 @@ int b200moe_set_gemm_tile_n(int block_n);
  * hold four or more 128-position tiles on average (an expert's tiles are then paired across its blocks, an odd
  * tile ending in a half-empty pair); 2 = whenever possible.  On this path the one tile an expert with an odd
  * number of occupied 128-position tiles has left over runs in a second, single-CTA launch instead of a
- * half-empty pair; adding 4 to the value switches that off.  Tuning knob with no counterpart in the reference. */
+ * half-empty pair; adding 4 to the value switches that off.  The left-over launch is a programmatic dependent
+ * launch that never waits for the pair launch (they write different rows), so it fills the SMs the pair launch
+ * frees while it drains; adding 8 runs it strictly afterwards.  Tuning knob with no counterpart in the reference. */
 int b200moe_set_gemm_cta_pair(int enable);
 /* Diagnostic: with a non-NULL device buffer of four 64-bit words, CTA 0 of the gate/up contraction writes
  * {SM cycles, nanoseconds} to words 0-1 and the down contraction to words 2-3, which gives the SM clock

@@ -73,6 +73,7 @@ struct GemmParams {
   int w_format;     // element format of the weight operand (B200MOE_W_*); activations are e4m3
   uint32_t b_tx;    // bytes one weight-tile copy reports to its mbarrier
   int prefetch;     // weight slabs requested into L2 ahead of the shared-memory pipeline (0 = none)
+  int early_successor;  // 1: let the next launch in the stream begin as soon as SMs free up (it touches other rows)
   int tile_filter;  // which position tiles a launch walks when experts are contiguous: 0 all, 1 (CTA-pair
                     // kernel) only pairs of two live tiles, 2 (single-CTA kernel) only the tile an expert with
                     // an odd number of live tiles has left over
@@ -279,6 +280,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     probe_c0 = clock64();
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(probe_t0));
   }
+  // The left-over launch that follows a CTA-pair launch works on different rows of the same buffers: it may start
+  // on every SM this launch no longer needs (programmatic dependent launch; the successor never waits on us, and
+  // whatever comes after it in the stream still waits for both).
+  if (p.early_successor && threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int cta_rank = CTAS == 2 ? static_cast<int>(cluster_cta_rank()) : 0;
   const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;
   build_sched(p, sched, CTAS, CTAS == 1 && BLOCK_N == 256, n_units);
@@ -803,7 +808,7 @@ int make_atoms_map(CUtensorMap* map, const void* base, int64_t n_atoms) {
 
 template <int BLOCK_N, int STAGES, int EPI, int CTAS>
 int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorMap& mb128, const CUtensorMap& msa,
-              const CUtensorMap& msb, const GemmParams& p, cudaStream_t st) {
+              const CUtensorMap& msb, const GemmParams& p, cudaStream_t st, bool overlap_predecessor = false) {
   using L = SmemLayout<BLOCK_N, STAGES, CTAS>;
   auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI, CTAS>;
   B200MOE_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kBytes));
@@ -824,6 +829,20 @@ int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorM
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     B200MOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma[0], ma[1], ma[2], mb, mb128, msa, msb, p));
+  } else if (overlap_predecessor) {
+    // programmatic stream serialisation: this grid may be scheduled while the previous kernel of the stream is
+    // still draining (the kernel never waits for it: it shares no rows with it)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = L::kBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200MOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma[0], ma[1], ma[2], mb, mb128, msa, msb, p));
   } else {
     kern<<<grid, kThreads, L::kBytes, st>>>(ma[0], ma[1], ma[2], mb, mb128, msa, msb, p);
   }
@@ -834,6 +853,7 @@ int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorM
 int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128 or 256)
 unsigned long long* g_clock_probe = nullptr;  // device buffer of 4 words: {cycles, ns} per projection
 int g_cta_pair = 1;   // 1: run 256-position x 256-row tiles on CTA pairs (cta_group::2) when blocks allow
+int g_overlap_leftover = 1; // the left-over launch may start while the CTA-pair launch drains
 int g_split_leftover = 1;  // CTA-pair path: odd left-over tiles go to a second, single-CTA launch
 int g_prefetch = -1;  // weight slabs prefetched into L2 ahead of the pipeline; -1 = default (none)
 
@@ -897,16 +917,20 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
     // tile an expert with an odd number of live tiles has left over (a half-empty pair would pay for a full
     // 256-row MMA: with ~1000 rows per expert that was one tile in five).
     p.tile_filter = g_split_leftover ? 1 : 0;
+    p.early_successor = (g_split_leftover && g_overlap_leftover) ? 1 : 0;
     rc = epi == 0 ? launch_tc<256, 6, 0, 2>(ma, mb, mb128, msa, msb, p, st) : launch_tc<256, 6, 1, 2>(ma, mb, mb128, msa, msb, p, st);
     if (rc != B200MOE_OK || !g_split_leftover) return rc;
     GemmParams p2 = p;
     p2.tile_filter = 2;
+    p2.early_successor = 0;
     p2.clock_probe = nullptr;
     p2.b_tx = static_cast<uint32_t>(bn * (nibbles ? kBlockK / 2 : kBlockK));
     CUtensorMap mb2;
     rc = make_rows_map(&mb2, b, K, p.n_total, p.E, bn, nibbles);
     if (rc != B200MOE_OK) return rc;
-    return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb2, mb128, msa, msb, p2, st) : launch_tc<256, 4, 1, 1>(ma, mb2, mb128, msa, msb, p2, st);
+    const bool ov = g_overlap_leftover != 0;
+    return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb2, mb128, msa, msb, p2, st, ov)
+                    : launch_tc<256, 4, 1, 1>(ma, mb2, mb128, msa, msb, p2, st, ov);
   }
   if (bn == 256)
     return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb, mb128, msa, msb, p, st) : launch_tc<256, 4, 1, 1>(ma, mb, mb128, msa, msb, p, st);
@@ -932,6 +956,7 @@ extern "C" int b200moe_set_gemm_prefetch(int slabs) {
 extern "C" int b200moe_set_gemm_cta_pair(int enable) {
   // bit 2 (value 4) switches the separate launch for left-over tiles off: pairs then run half empty
   g_split_leftover = (enable >= 0 && (enable & 4)) ? 0 : 1;
+  g_overlap_leftover = (enable >= 0 && (enable & 8)) ? 0 : 1;  // bit 3 (value 8): left-over launch strictly after
   if (enable >= 0) enable &= 3;
   g_cta_pair = enable < 0 ? 0 : (enable > 2 ? 2 : enable);
   return B200MOE_OK;
