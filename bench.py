@@ -279,18 +279,6 @@ def run_ours(args, cfg, name):
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
     T, H, I, E, K, B = (cfg[k] for k in "THIEKB")
-    if args.tile_n:
-        from nki_library_b200 import _lib
-        _lib.call("b200moe_set_gemm_tile_n", args.tile_n)
-    if args.prefetch >= -1:
-        from nki_library_b200 import _lib
-        _lib.call("b200moe_set_gemm_prefetch", args.prefetch)
-    if args.router_path >= 0:
-        from nki_library_b200 import _lib
-        _lib.call("b200moe_set_router_path", args.router_path)
-    if args.cta_pair >= 0:
-        from nki_library_b200 import _lib
-        _lib.call("b200moe_set_gemm_cta_pair", args.cta_pair)
 
     hidden_h, router_w, bias = make_inputs(cfg, dev, rank)
     hidden_pin = hidden_h.pin_memory()
@@ -299,7 +287,8 @@ def run_ours(args, cfg, name):
     bias_d = None if bias is None else bias.to(dev)
     if world == 1:
         weights = random_expert_weights(E, H, I, dev, seed=7, w_format=W_FORMATS[args.weight_format])
-        layer = MoELayer(router_w.to(dev), weights, K, B, T, bias_d)
+        layer = MoELayer(router_w.to(dev), weights, K, B, T, bias_d, router_path=args.router_path,
+                         gemm_variant=args.gemm_variant)
         n_blocks = layer.N
 
         def forward(h, timers=None):
@@ -389,15 +378,16 @@ def run_ours(args, cfg, name):
     if any(status):
         raise RuntimeError(f"device status after the timed steps: {status}")
     # -------- the same steps again, eagerly, with CUDA events around every kernel (roofline input)
-    from nki_library_b200 import _lib as _l
     probe = torch.zeros(4, dtype=torch.int64, device=dev)
-    _l.call("b200moe_set_clock_probe", _l.ptr(probe))
+    if world == 1:
+        layer.clock_probe = probe
     timers = {}
     barrier()
     for _ in range(args.steps):
         forward(hidden_d, timers)
     barrier()
-    _l.call("b200moe_set_clock_probe", None)
+    if world == 1:
+        layer.clock_probe = None
     pr = probe.cpu().tolist()
     kernel_sm_mhz = {"gemm1_swiglu": round(1e3 * pr[0] / pr[1], 1) if pr[1] else None,
                      "gemm2_scale": round(1e3 * pr[2] / pr[3], 1) if pr[3] else None}
@@ -530,14 +520,13 @@ def main():
     ap.add_argument("--capacity-factor", type=float, default=2.5,
                     help="receive-buffer size of the peer-memory exchange, in multiples of a rank's fair share")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--cta-pair", type=int, default=-1, help="1/0: force the cta_group::2 GEMM on/off (-1 = default)")
-    ap.add_argument("--prefetch", type=int, default=-2, help="weight slabs prefetched into L2 (-1 = by shape)")
+    ap.add_argument("--gemm-variant", type=lambda v: int(v, 0), default=0,
+                    help="variant word of the grouped contractions (B200MOE_GEMM_* bits; 0 = library default)")
     ap.add_argument("--fuse-return", default="auto", choices=["auto", "on", "off"],
                     help="expert parallelism: let the down contraction's epilogue store result rows into their GPUs "
                          "(on), copy them in a separate kernel (off), or choose by rank count (auto)")
     ap.add_argument("--no-decode-leg", action="store_true", help="omit the secondary decode measurements (profiling runs)")
-    ap.add_argument("--router-path", type=int, default=-1, help="1 split-K router, 2 tcgen05 router (-1 = by shape)")
-    ap.add_argument("--tile-n", type=int, default=0, help="weight rows per GEMM tile (128/192/256; 0 = library default)")
+    ap.add_argument("--router-path", type=int, default=0, help="1 split-K router, 2 tcgen05 router (0 = by shape)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -54,6 +54,25 @@ enum { B200MOE_LAYOUT_ROWS = 0, B200MOE_LAYOUT_NKI_X4 = 1 };
  * (core/utils/mx_torch_common.py:31-133, core/moe/moe_cte/moe_cte_mx_utils.py:58-107).  e2m1 packs two
  * elements per byte (element 2j in the low nibble), so a weight row of K elements is K/2 bytes. */
 enum { B200MOE_W_E4M3 = 0, B200MOE_W_E5M2 = 1, B200MOE_W_E2M1 = 5 };
+/* Variant word (`impl`) of the grouped contractions, per call.  No counterpart in the reference.
+ *   B200MOE_IMPL_SIMT        CUDA-core validation kernels instead of the tensor-core path
+ *   B200MOE_GEMM_TILE_N128   128 weight rows per tile instead of 256
+ *   B200MOE_GEMM_NO_PAIR     never run on CTA pairs (tcgen05 cta_group::2, 256 positions x 256 weight rows)
+ *   B200MOE_GEMM_FORCE_PAIR  pair an expert's 128-position tiles across its blocks whatever the block size
+ *                            (default: when the block size is a multiple of 256, or experts hold four or more
+ *                            tiles on average; an odd tile then ends in a half-empty pair)
+ *   B200MOE_GEMM_NO_SPLIT    keep the tile an expert with an odd number of occupied tiles has left over in a
+ *                            half-empty pair (default: a second, single-CTA launch takes the left-over tiles)
+ *   B200MOE_GEMM_NO_OVERLAP  run that second launch strictly after the first (default: a programmatic
+ *                            dependent launch that fills SMs as the first drains and finishes after it) */
+enum {
+  B200MOE_IMPL_SIMT = 1,
+  B200MOE_GEMM_TILE_N128 = 0x100,
+  B200MOE_GEMM_NO_PAIR = 0x200,
+  B200MOE_GEMM_FORCE_PAIR = 0x400,
+  B200MOE_GEMM_NO_SPLIT = 0x800,
+  B200MOE_GEMM_NO_OVERLAP = 0x1000
+};
 /* routing source accepted by b200moe_group_tokens */
 enum { B200MOE_ROUTING_INDEX = 0, B200MOE_ROUTING_MASK = 1 };
 
@@ -77,12 +96,11 @@ size_t b200moe_sf_bytes(int64_t rows, int64_t K);
  * partial logits, or the transposed router weight of the single-kernel tcgen05 path that
  * large token counts take (x [T,H], E <= 256, H % 64 == 0). */
 size_t b200moe_router_workspace_bytes(int T, int H, int E);
-/* 0 (default): choose by shape; 1: always the split-K path; 2: the tcgen05 path whenever the shape
- * is eligible.  Tuning knob without a reference counterpart. */
-int b200moe_set_router_path(int path);
+/* path (per call, no reference counterpart): 0 = choose by shape; 1 = always the split-K path; 2 = the
+ * tcgen05 path whenever the shape is eligible. */
 int b200moe_router_topk(const void* x, int x_is_TH, const void* w, const void* w_bias, int T, int H, int E, int k,
                         int act_fn, int router_pre_norm, int norm_topk_prob, void* router_logits, int logits_dtype,
-                        uint32_t* expert_index, void* expert_affinities, int aff_dtype, void* workspace,
+                        uint32_t* expert_index, void* expert_affinities, int aff_dtype, int path, void* workspace,
                         size_t workspace_bytes, b200moe_stream_t stream);
 
 /* ---- grouping ----------------------------------------------------------------
@@ -193,9 +211,13 @@ int b200moe_prepare_gate_up_bias(const void* bias, int dtype, int layout, int E,
  * reference's block loop); tile_flags (NULL = all
  * tiles run; see b200moe_gather_quantize_mxfp8); token_position_to_id [n_blocks*B] and
  * hidden_rows (ids outside [0, hidden_rows) are pads, their rows are not written); status: device
- * int32[1], set non-zero if a kernel-internal wait ran out; impl: 0 = tcgen05
- * tensor-core kernel, 1 = plain CUDA-core validation kernel (slow, same results
- * up to summation order).
+ * int32[1], set non-zero if a kernel-internal wait ran out; impl: the per-call variant
+ * word, 0 = tcgen05 tensor-core kernel with tile shapes chosen by the library,
+ * B200MOE_IMPL_SIMT = plain CUDA-core validation kernel (slow, same results up to
+ * summation order), B200MOE_GEMM_* bits = restrictions on the tile shapes (below);
+ * clock_probe: NULL, or a device buffer of two 64-bit words (8-byte aligned) into which
+ * CTA 0 of the contraction writes {SM cycles, nanoseconds} it ran for, which gives the SM
+ * clock the kernel really saw (diagnostic, no reference counterpart).
  *
  * gemm1 = gate_up_projection_mx + clamp + act(gate)*up + quantize_mx of the result
  * (core/mlp/mlp_tkg/gate_up_projection_mx_shard_H.py:48-225,
@@ -208,7 +230,7 @@ int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_t* x_sf, co
                                  const int32_t* conditions, const int32_t* tile_flags,
                                  int n_blocks, int B, int E, int H, int I, int act_fn, float gate_lo, float gate_hi,
                                  float up_lo, float up_hi, uint8_t* m_codes, uint8_t* m_sf, int32_t* status, int impl,
-                                 b200moe_stream_t stream);
+                                 void* clock_probe, b200moe_stream_t stream);
 
 /* gemm2 = down_projection_mx + bias + affinity scaling of each row
  * (core/mlp/mlp_tkg/down_projection_mx_shard_H.py:212-387,
@@ -222,29 +244,7 @@ int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, con
                                 const int32_t* token_position_to_id, int hidden_rows,
                                 int n_blocks, int B, int E, int H, int I, const void* affinities, int aff_dtype,
                                 int aff_per_row, void* y_pos_bf16, int32_t* status, int impl,
-                                b200moe_stream_t stream);
-
-/* Weight slabs (128 contraction elements of a weight tile) requested into L2 ahead of the shared-memory
- * pipeline; 0 or -1 (default) = none.  Experiment knob without a reference counterpart: on the decode
- * shapes measured it did not pay. */
-int b200moe_set_gemm_prefetch(int slabs);
-
-/* Weight rows per tile of the tensor-core kernel: 256 (default) or 128.  Tuning knob
- * with no counterpart in the reference. */
-int b200moe_set_gemm_tile_n(int block_n);
-/* Run the contractions on CTA pairs (tcgen05 cta_group::2, 256 positions x 256 weight rows per pair).
- * 0 = never; 1 (default) = when the block size is a multiple of 256, or with other block sizes when experts
- * hold four or more 128-position tiles on average (an expert's tiles are then paired across its blocks, an odd
- * tile ending in a half-empty pair); 2 = whenever possible.  On this path the one tile an expert with an odd
- * number of occupied 128-position tiles has left over runs in a second, single-CTA launch instead of a
- * half-empty pair; adding 4 to the value switches that off.  The left-over launch is a programmatic dependent
- * launch that never waits for the pair launch (they write different rows), so it fills the SMs the pair launch
- * frees while it drains; adding 8 runs it strictly afterwards.  Tuning knob with no counterpart in the reference. */
-int b200moe_set_gemm_cta_pair(int enable);
-/* Diagnostic: with a non-NULL device buffer of four 64-bit words, CTA 0 of the gate/up contraction writes
- * {SM cycles, nanoseconds} to words 0-1 and the down contraction to words 2-3, which gives the SM clock
- * the kernel really ran at (cycles / ns).  NULL switches it off.  No counterpart in the reference. */
-int b200moe_set_clock_probe(void* device_words);
+                                void* clock_probe, b200moe_stream_t stream);
 
 /* combine = the accumulate-and-scatter tail of the block loop
  * (core/moe/moe_cte/bwmm_shard_on_block_mx.py:1303-1347): out[t,:] = sum over the

@@ -24,6 +24,9 @@ F32, BF16, I32 = 0, 1, 2
 LAYOUT_ROWS, LAYOUT_NKI_X4 = 0, 1
 W_E4M3, W_E5M2, W_E2M1 = 0, 1, 5  # weight element formats (B200MOE_W_*)
 ROUTING_INDEX, ROUTING_MASK = 0, 1
+# per-call variant word of the grouped contractions (B200MOE_IMPL_* / B200MOE_GEMM_*)
+IMPL_SIMT, GEMM_TILE_N128, GEMM_NO_PAIR, GEMM_FORCE_PAIR, GEMM_NO_SPLIT, GEMM_NO_OVERLAP = 1, 0x100, 0x200, 0x400, 0x800, 0x1000
+ROUTER_AUTO, ROUTER_SPLIT_K, ROUTER_TCGEN05 = 0, 1, 2
 
 # name -> (restype, argtypes); must list every symbol of include/b200moe.h
 SIGNATURES = {
@@ -32,7 +35,8 @@ SIGNATURES = {
     "b200moe_sf_bytes": (c_size_t, [c_int64, c_int64]),
     "b200moe_router_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "b200moe_router_topk": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                    c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+                                    c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_size_t,
+                                    c_void_p]),
     "b200moe_find_nonzero_workspace_bytes": (c_size_t, [c_int, c_int]),
     "b200moe_find_nonzero_indices": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                              c_void_p, c_size_t, c_void_p]),
@@ -59,15 +63,11 @@ SIGNATURES = {
     "b200moe_prepare_gate_up_bias": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "b200moe_grouped_gemm1_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-                                             c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+                                             c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                             c_void_p]),
     "b200moe_grouped_gemm2_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                            c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
-    "b200moe_set_router_path": (c_int, [c_int]),
-    "b200moe_set_gemm_tile_n": (c_int, [c_int]),
-    "b200moe_set_gemm_cta_pair": (c_int, [c_int]),
-    "b200moe_set_gemm_prefetch": (c_int, [c_int]),
-    "b200moe_set_clock_probe": (c_int, [c_void_p]),
+                                            c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "b200moe_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "b200moe_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
                                 c_void_p]),

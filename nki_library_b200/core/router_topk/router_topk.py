@@ -30,6 +30,7 @@ def router_topk(
     shard_on_tokens: bool = False,
     skip_store_expert_index: bool = False,
     skip_store_router_logits: bool = False,
+    _path: int = 0,
 ):
     """Router logits, top-K expert ids and affinities, written into the caller's tensors.
 
@@ -41,7 +42,8 @@ def router_topk(
     (router_topk.py:1129-1188).  Flags that only steer Trainium engines
     (``x_sb_layout``, ``use_column_tiling``, ``use_indirect_dma_scatter``,
     ``use_PE_broadcast_w_bias``, ``shard_on_tokens``) are accepted and checked
-    for the same illegal combinations, then ignored.
+    for the same illegal combinations, then ignored.  ``_path`` (no reference
+    counterpart) forces the logits kernel: 0 by shape, 1 split-K, 2 tcgen05.
     """
     _lib.require_cuda(x, w, w_bias, router_logits, expert_affinities, expert_index)
     _lib.kernel_assert(x.dim() == 2 and w.dim() == 2, "x and w must be 2-D")
@@ -73,7 +75,7 @@ def router_topk(
         "b200moe_router_topk", _lib.ptr(x), x_is_TH, _lib.ptr(w), _lib.ptr(w_bias), T, H, E, k, act_fn.value,
         int(router_pre_norm), int(norm_topk_prob), _lib.ptr(router_logits), _lib.dtype_code(router_logits),
         None if skip_store_expert_index else _lib.ptr(expert_index), _lib.ptr(expert_affinities),
-        _lib.dtype_code(expert_affinities), _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
+        _lib.dtype_code(expert_affinities), int(_path), _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
     outs = [router_logits, expert_index, expert_affinities]
     if return_eager_affi:
         idx = expert_index.to(torch.int64)

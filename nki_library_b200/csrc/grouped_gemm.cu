@@ -26,8 +26,6 @@
 // and tears down.
 #include <cuda.h>
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "tcgen05_ptx.cuh"
 
@@ -72,13 +70,12 @@ struct GemmParams {
   unsigned long long* clock_probe;  // optional: CTA 0 writes {SM cycles, nanoseconds} spent in the kernel
   int w_format;     // element format of the weight operand (B200MOE_W_*); activations are e4m3
   uint32_t b_tx;    // bytes one weight-tile copy reports to its mbarrier
-  int prefetch;     // weight slabs requested into L2 ahead of the shared-memory pipeline (0 = none)
   int early_successor;  // 1: let the next launch in the stream begin as soon as SMs free up (it touches other rows)
   int tile_filter;  // which position tiles a launch walks when experts are contiguous: 0 all, 1 (CTA-pair
                     // kernel) only pairs of two live tiles, 2 (single-CTA kernel) only the tile an expert with
                     // an odd number of live tiles has left over
-  int experiment;  // timing experiments only (builds with -DB200MOE_EXPERIMENT): bit 0 no loads, 1 no MMA,
-                   // 2 no scale copies, 3 no epilogue math; results are meaningless when non-zero
+  int wait_predecessor;  // 1: launched with programmatic stream serialisation behind a launch that signalled
+                         // early; wait for that launch to finish before this grid may finish
 };
 
 // Per-CTA tile schedule, built once in shared memory.
@@ -281,8 +278,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(probe_t0));
   }
   // The left-over launch that follows a CTA-pair launch works on different rows of the same buffers: it may start
-  // on every SM this launch no longer needs (programmatic dependent launch; the successor never waits on us, and
-  // whatever comes after it in the stream still waits for both).
+  // on every SM this launch no longer needs (programmatic dependent launch).  The successor does its tiles without
+  // waiting and executes griddepcontrol.wait before it exits, so it never completes before this grid has.
   if (p.early_successor && threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int cta_rank = CTAS == 2 ? static_cast<int>(cluster_cta_rank()) : 0;
   const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;
@@ -347,32 +344,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const uint32_t b_bytes = part >= 0 ? p.b_tx / 2 : p.b_tx;
         const uint32_t stage_bytes = static_cast<uint32_t>(rows_lead + rows_peer) * kBlockK + CTAS * b_bytes;
         const int atom0 = n_row0 >> 7;
-        // L2 prefetch runs `p.prefetch` slabs ahead, into the next tile of this CTA when the current one ends
-        int nx_n = 0, nx_e = -1;
-        if (p.prefetch > 0) {
-          int nm, nk;
-          for (int t2 = tile + n_units; t2 < total_tiles; t2 += n_units)
-            if (decode_tile(p, sched, t2, CTAS, nm, nx_n, nx_e, nk, nk)) break; else nx_e = -1;
-          if (tile == unit)
-            for (int kp = 0; kp < p.prefetch && kp < p.k_blocks; ++kp)
-              tma_prefetch_3d(&tmap_b, kp * kBlockK, n_tile * BLOCK_N + cta_rank * kRowsB, e);
-        }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (p.prefetch > 0) {
-            const int kp = kb + p.prefetch;
-            if (kp < p.k_blocks) tma_prefetch_3d(&tmap_b, kp * kBlockK, n_tile * BLOCK_N + cta_rank * kRowsB, e);
-            else if (nx_e >= 0 && kp - p.k_blocks < p.k_blocks)
-              tma_prefetch_3d(&tmap_b, (kp - p.k_blocks) * kBlockK, nx_n * BLOCK_N + cta_rank * kRowsB, nx_e);
-          }
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
-#ifdef B200MOE_EXPERIMENT
-          if (p.experiment & 1) {
-            if (cta_rank == 0) mbar_arrive(&full[stage]);
-            mbar_arrive(&sf_full[stage]);
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-            continue;
-          }
-#endif
           // scale atoms of this CTA's rows and of the whole weight tile -> this CTA's own barrier
           // (rows past the end of the atom table read as zero and still count their bytes)
           mbar_expect_tx(&sf_full[stage], L::kSfa + L::kSfb);
@@ -383,22 +356,11 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                         (e * p.b_row_atoms + atom0 + j) * p.k_blocks + kb, &sf_full[stage]);
           if constexpr (CTAS == 2) {
             // operand tiles of both CTAs complete on the even CTA's barrier
-#ifdef B200MOE_EXPERIMENT
-            const bool skip_a = (p.experiment & 16) && (kb & 1), skip_b = (p.experiment & 32) && (kb & 1);
-            if (cta_rank == 0)
-              mbar_expect_tx(&full[stage], stage_bytes - (skip_a ? (rows_lead + rows_peer) * kBlockK : 0) - (skip_b ? 2 * p.b_tx : 0));
-            if (!skip_a && my_rows > 0)
-              tma2_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
-            if (!skip_b)
-              tma2_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK,
-                           n_tile * BLOCK_N + cta_rank * (BLOCK_N / 2), e, &full[stage]);
-#else
             if (cta_rank == 0) mbar_expect_tx(&full[stage], stage_bytes);
             if (my_rows > 0)
               tma2_load_2d(smem + L::kOffA + stage * L::kA, map_a, kb * kBlockK, m_tile * kBlockM, &full[stage]);
             tma2_load_3d(smem + L::kOffB + stage * L::kB, &tmap_b, kb * kBlockK,
                          n_tile * BLOCK_N + cta_rank * (BLOCK_N / 2), e, &full[stage]);
-#endif
           } else {
             mbar_expect_tx(&full[stage], stage_bytes);
             if (my_rows > 0)
@@ -439,9 +401,6 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           const uint32_t sfb_tmem = sfa_tmem + 4 + sfb_off;
           const uint64_t a_desc = desc_sw128(smem_u32(smem + L::kOffA + stage * L::kA));
           const uint64_t b_desc = desc_sw128(smem_u32(smem + L::kOffB + stage * L::kB));
-#ifdef B200MOE_EXPERIMENT
-          if (!(p.experiment & 2))
-#endif
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t idesc = idesc_tile | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
@@ -477,9 +436,6 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait(&sf_full[stage], phase, abort_flag, p.status, 6)) { ok = false; break; }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kSfCol + stage * 16;
-#ifdef B200MOE_EXPERIMENT
-        if (!(p.experiment & 4))
-#endif
         {
           const uint4 va = *reinterpret_cast<const uint4*>(smem + L::kOffSfa + stage * L::kSfa + lane * 16);
           tc_st4(taddr, va);
@@ -533,9 +489,6 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         else mbar_arrive(&tmem_empty[acc]);
       }
       if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
-#ifdef B200MOE_EXPERIMENT
-      if (p.experiment & 8) continue;
-#endif
       if (CTAS == 2 && cta_rank != 0 && !second) continue;  // half-empty pair: these rows belong to someone else
       if (part >= 0 && half != 0) continue;                 // half tile: only 128 accumulator columns hold results
       const int n_row0 = n_tile * BLOCK_N + (part > 0 ? BLOCK_N / 2 : 0);
@@ -632,6 +585,9 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     }
   }
 
+  // A grid that was allowed to start while its predecessor drains must not finish before it: whatever follows in
+  // the stream waits for this grid only, and relies on both having completed.
+  if (p.wait_predecessor) asm volatile("griddepcontrol.wait;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   if (p.clock_probe != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -850,14 +806,15 @@ int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorM
   return B200MOE_OK;
 }
 
-int g_block_n = 256;  // weight rows per tile of the tensor-core kernel (128 or 256)
-unsigned long long* g_clock_probe = nullptr;  // device buffer of 4 words: {cycles, ns} per projection
-int g_cta_pair = 1;   // 1: run 256-position x 256-row tiles on CTA pairs (cta_group::2) when blocks allow
-int g_overlap_leftover = 1; // the left-over launch may start while the CTA-pair launch drains
-int g_split_leftover = 1;  // CTA-pair path: odd left-over tiles go to a second, single-CTA launch
-int g_prefetch = -1;  // weight slabs prefetched into L2 ahead of the pipeline; -1 = default (none)
-
-int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, int impl, cudaStream_t st) {
+// `impl` is the per-call variant word of the entry points: bit 0 selects the CUDA-core validation kernels, the
+// B200MOE_GEMM_* bits restrict the tile shapes the tensor-core path may pick.  Nothing here is process state.
+int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, int impl, void* clock_probe,
+             cudaStream_t st) {
+  B200MOE_REQUIRE((impl & ~(B200MOE_IMPL_SIMT | B200MOE_GEMM_TILE_N128 | B200MOE_GEMM_NO_PAIR | B200MOE_GEMM_FORCE_PAIR |
+                            B200MOE_GEMM_NO_SPLIT | B200MOE_GEMM_NO_OVERLAP)) == 0,
+                  B200MOE_ERR_INVALID, "unknown bits in the variant word 0x%x", impl);
+  B200MOE_REQUIRE(clock_probe == nullptr || (reinterpret_cast<uintptr_t>(clock_probe) & 7) == 0, B200MOE_ERR_INVALID,
+                  "the clock probe buffer must be 8-byte aligned");
   B200MOE_REQUIRE(p.B > 0 && p.B % 128 == 0, B200MOE_ERR_INVALID, "block size must be a multiple of 128, got %d", p.B);
   B200MOE_REQUIRE(K % 32 == 0 && K >= 32, B200MOE_ERR_INVALID, "contraction length must be a multiple of 32, got %d", K);
   B200MOE_REQUIRE(p.n_blocks > 0 && p.E > 0 && p.E <= kMaxExperts, B200MOE_ERR_INVALID,
@@ -869,39 +826,36 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   B200MOE_REQUIRE(!nibbles || K % 128 == 0, B200MOE_ERR_INVALID,
                   "e2m1 weights need a contraction length that is a multiple of 128, got %d", K);
   p.m_tiles_total = p.n_blocks * (p.B / 128);
-  p.clock_probe = g_clock_probe ? g_clock_probe + 2 * epi : nullptr;
-#ifdef B200MOE_EXPERIMENT
-  if (const char* ev = getenv("B200MOE_EXPERIMENT")) p.experiment = atoi(ev);
-#endif
+  p.clock_probe = static_cast<unsigned long long*>(clock_probe);
   p.k_blocks = (K + kBlockK - 1) / kBlockK;
   p.b_row_atoms = (p.n_total + 127) / 128;
   p.b_sf_expert_stride = static_cast<int64_t>(p.b_row_atoms) * p.k_blocks * 512;
   B200MOE_CUDA_OK(cudaMemsetAsync(p.status, 0, 4, st));
-  if (impl == 1) {
+  if (impl & B200MOE_IMPL_SIMT) {
     const int64_t work = epi == 0 ? static_cast<int64_t>(p.m_tiles_total) * 128 * (p.I / 32)
                                   : static_cast<int64_t>(p.m_tiles_total) * 128 * p.H_out;
-    const int grid = static_cast<int>(ceil_div64(work, 128) < 148 * 32 ? ceil_div64(work, 128) : 148 * 32);
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+    const int grid = static_cast<int>(ceil_div64(work, 128) < cap ? ceil_div64(work, 128) : cap);
     if (epi == 0) simt_gemm1_kernel<<<grid, 128, 0, st>>>(a, b, p, K);
     else simt_gemm2_kernel<<<grid, 128, 0, st>>>(a, b, p, K);
     B200MOE_LAUNCH_OK("simt_gemm_kernel");
     return B200MOE_OK;
   }
   B200MOE_REQUIRE(K % 16 == 0, B200MOE_ERR_INVALID, "TMA needs row pitches that are multiples of 16 bytes");
-  const int bn = g_block_n;
+  const int bn = (impl & B200MOE_GEMM_TILE_N128) ? 128 : 256;
+  const bool split_leftover = !(impl & B200MOE_GEMM_NO_SPLIT);
+  const bool overlap_leftover = !(impl & B200MOE_GEMM_NO_OVERLAP);
   p.n_tiles = (p.n_total + bn - 1) / bn;
   // CTA pairs need two position tiles per weight tile: always there when a block holds an even number of 128-row
   // tiles; with odd blocks (B = 128) an expert's tiles are paired across its blocks, which pays once experts have
   // several tiles on average (prefill) and not for one short tile per expert (decode)
-  const bool pair = g_cta_pair && bn == 256 && (sm_count() % 2 == 0) &&
-                    (p.B % 256 == 0 || (g_cta_pair == 2 || p.m_tiles_total >= 4 * p.E));
+  const bool pair = !(impl & B200MOE_GEMM_NO_PAIR) && bn == 256 && (sm_count() % 2 == 0) &&
+                    (p.B % 256 == 0 || (impl & B200MOE_GEMM_FORCE_PAIR) || p.m_tiles_total >= 4 * p.E);
   CUtensorMap ma[3], mb, mb128, msa, msb;  // activation boxes of 128, 64 and 32 rows; weight boxes: tile, 128 rows
   int rc = B200MOE_OK;
   for (int i = 0; i < 3 && rc == B200MOE_OK; ++i)
     rc = make_rows_map(&ma[i], a, K, static_cast<int64_t>(p.m_tiles_total) * 128, 0, kBlockM >> i);
   if (rc != B200MOE_OK) return rc;
-  // off unless asked for: on the decode shapes measured (8 experts x 14336 x 4096, 64 tokens) a distance of 6-24
-  // slabs made both contractions 8-60 % slower
-  p.prefetch = g_prefetch >= 0 ? g_prefetch : 0;
   rc = make_rows_map(&mb, b, K, p.n_total, p.E, pair ? bn / 2 : bn, nibbles);
   // the copy reports the bytes it read from global memory: a 4-bit slab is 64 bytes per row there
   p.b_tx = static_cast<uint32_t>((pair ? bn / 2 : bn) * (nibbles ? kBlockK / 2 : kBlockK));
@@ -916,19 +870,20 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
     // Two launches: the CTA-pair kernel walks the pairs of live 128-row tiles, the single-CTA kernel the one
     // tile an expert with an odd number of live tiles has left over (a half-empty pair would pay for a full
     // 256-row MMA: with ~1000 rows per expert that was one tile in five).
-    p.tile_filter = g_split_leftover ? 1 : 0;
-    p.early_successor = (g_split_leftover && g_overlap_leftover) ? 1 : 0;
+    p.tile_filter = split_leftover ? 1 : 0;
+    p.early_successor = (split_leftover && overlap_leftover) ? 1 : 0;
     rc = epi == 0 ? launch_tc<256, 6, 0, 2>(ma, mb, mb128, msa, msb, p, st) : launch_tc<256, 6, 1, 2>(ma, mb, mb128, msa, msb, p, st);
-    if (rc != B200MOE_OK || !g_split_leftover) return rc;
+    if (rc != B200MOE_OK || !split_leftover) return rc;
     GemmParams p2 = p;
     p2.tile_filter = 2;
     p2.early_successor = 0;
+    p2.wait_predecessor = overlap_leftover ? 1 : 0;
     p2.clock_probe = nullptr;
     p2.b_tx = static_cast<uint32_t>(bn * (nibbles ? kBlockK / 2 : kBlockK));
     CUtensorMap mb2;
     rc = make_rows_map(&mb2, b, K, p.n_total, p.E, bn, nibbles);
     if (rc != B200MOE_OK) return rc;
-    const bool ov = g_overlap_leftover != 0;
+    const bool ov = overlap_leftover;
     return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb2, mb128, msa, msb, p2, st, ov)
                     : launch_tc<256, 4, 1, 1>(ma, mb2, mb128, msa, msb, p2, st, ov);
   }
@@ -942,40 +897,13 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
 
 using namespace b200moe;
 
-extern "C" int b200moe_set_clock_probe(void* device_words) {
-  g_clock_probe = static_cast<unsigned long long*>(device_words);
-  return B200MOE_OK;
-}
-
-extern "C" int b200moe_set_gemm_prefetch(int slabs) {
-  B200MOE_REQUIRE(slabs >= -1 && slabs <= 64, B200MOE_ERR_INVALID, "prefetch distance must be in [-1, 64], got %d", slabs);
-  g_prefetch = slabs;
-  return B200MOE_OK;
-}
-
-extern "C" int b200moe_set_gemm_cta_pair(int enable) {
-  // bit 2 (value 4) switches the separate launch for left-over tiles off: pairs then run half empty
-  g_split_leftover = (enable >= 0 && (enable & 4)) ? 0 : 1;
-  g_overlap_leftover = (enable >= 0 && (enable & 8)) ? 0 : 1;  // bit 3 (value 8): left-over launch strictly after
-  if (enable >= 0) enable &= 3;
-  g_cta_pair = enable < 0 ? 0 : (enable > 2 ? 2 : enable);
-  return B200MOE_OK;
-}
-
-extern "C" int b200moe_set_gemm_tile_n(int block_n) {
-  B200MOE_REQUIRE(block_n == 128 || block_n == 256, B200MOE_ERR_INVALID, "tile width must be 128 or 256, got %d",
-                  block_n);
-  g_block_n = block_n;
-  return B200MOE_OK;
-}
-
 extern "C" int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_t* x_sf, const uint8_t* w1_dev,
                                             const uint8_t* w1_sf, int w_format, const float* bias_gu_dev,
                                             const int32_t* block_to_expert, const int32_t* conditions,
                                             const int32_t* tile_flags, int n_blocks, int B, int E, int H, int I,
                                             int act_fn, float gate_lo, float gate_hi, float up_lo, float up_hi,
                                             uint8_t* m_codes, uint8_t* m_sf, int32_t* status, int impl,
-                                            b200moe_stream_t stream) {
+                                            void* clock_probe, b200moe_stream_t stream) {
   B200MOE_REQUIRE(x_codes && x_sf && w1_dev && w1_sf && block_to_expert && m_codes && m_sf, B200MOE_ERR_INVALID,
                   "grouped_gemm1: null pointer argument");
   B200MOE_REQUIRE(I % 32 == 0 && I > 0, B200MOE_ERR_INVALID, "grouped_gemm1: I must be a positive multiple of 32, got %d", I);
@@ -1006,7 +934,7 @@ extern "C" int b200moe_grouped_gemm1_swiglu(const uint8_t* x_codes, const uint8_
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (I % 128 != 0)  // partially filled scale atoms along I must read as zero
     B200MOE_CUDA_OK(cudaMemsetAsync(m_sf, 0, b200moe_sf_bytes(static_cast<int64_t>(n_blocks) * B, I), st));
-  return run_gemm(0, x_codes, w1_dev, p, H, impl, st);
+  return run_gemm(0, x_codes, w1_dev, p, H, impl, clock_probe, st);
 }
 
 namespace {
@@ -1015,7 +943,7 @@ int gemm2_impl(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_de
                const int32_t* tile_flags, const int32_t* token_position_to_id, int hidden_rows, int n_blocks, int B,
                int E, int H, int I, const void* affinities, int aff_dtype, int aff_per_row, void* y_pos_bf16,
                const int32_t* row_src, void* const* peer_out, int world, int64_t peer_rows, int32_t* status, int impl,
-               b200moe_stream_t stream) {
+               void* clock_probe, b200moe_stream_t stream) {
   B200MOE_REQUIRE(m_codes && m_sf && w2_dev && w2_sf && block_to_expert && (y_pos_bf16 || row_src),
                   B200MOE_ERR_INVALID, "grouped_gemm2: null pointer argument");
   B200MOE_REQUIRE(H % 32 == 0 && H > 0, B200MOE_ERR_INVALID, "grouped_gemm2: H must be a positive multiple of 32, got %d", H);
@@ -1055,7 +983,7 @@ int gemm2_impl(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_de
     B200MOE_REQUIRE((reinterpret_cast<uintptr_t>(y_pos_bf16) & 31) == 0, B200MOE_ERR_INVALID,
                     "grouped_gemm2: y_pos must be 32-byte aligned (the epilogue stores 32 bytes at a time)");
   }
-  return run_gemm(1, m_codes, w2_dev, p, I, impl, static_cast<cudaStream_t>(stream));
+  return run_gemm(1, m_codes, w2_dev, p, I, impl, clock_probe, static_cast<cudaStream_t>(stream));
 }
 }  // namespace
 
@@ -1065,10 +993,11 @@ extern "C" int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t
                                            const int32_t* tile_flags, const int32_t* token_position_to_id,
                                            int hidden_rows, int n_blocks, int B, int E, int H, int I,
                                            const void* affinities, int aff_dtype, int aff_per_row, void* y_pos_bf16,
-                                           int32_t* status, int impl, b200moe_stream_t stream) {
+                                           int32_t* status, int impl, void* clock_probe,
+                                           b200moe_stream_t stream) {
   return gemm2_impl(m_codes, m_sf, w2_dev, w2_sf, w_format, bias_d, block_to_expert, conditions, tile_flags,
                     token_position_to_id, hidden_rows, n_blocks, B, E, H, I, affinities, aff_dtype, aff_per_row,
-                    y_pos_bf16, nullptr, nullptr, 0, 0, status, impl, stream);
+                    y_pos_bf16, nullptr, nullptr, 0, 0, status, impl, clock_probe, stream);
 }
 
 extern "C" int b200moe_ep_gemm2_scale_return(const uint8_t* m_codes, const uint8_t* m_sf, const uint8_t* w2_dev,
@@ -1081,6 +1010,6 @@ extern "C" int b200moe_ep_gemm2_scale_return(const uint8_t* m_codes, const uint8
   B200MOE_REQUIRE(row_valid && row_src && back_peers, B200MOE_ERR_INVALID, "ep_gemm2_scale_return: null pointer argument");
   return gemm2_impl(m_codes, m_sf, w2_dev, w2_sf, w_format, bias_d, block_to_expert, conditions, tile_flags, row_valid,
                     static_cast<int>(cap_rows), n_blocks, B, E_local, H, I, row_affinity, B200MOE_F32, 1, nullptr,
-                    row_src, back_peers, world, back_rows, status, impl, stream);
+                    row_src, back_peers, world, back_rows, status, impl, nullptr, stream);
 }
 

@@ -397,7 +397,7 @@ extern "C" int b200moe_indexed_flatten(const int32_t* input, int E, int T, int f
                   "indexed_flatten: row length %d must be a multiple of f_len %d", T, f_len);
   B200MOE_REQUIRE(n_row_offsets >= E, B200MOE_ERR_INVALID, "indexed_flatten: %d row offsets for %d rows",
                   n_row_offsets, E);
-  const int grid = static_cast<int>(ceil_div64(output_len, 256) < 148 * 16 ? ceil_div64(output_len, 256) : 148 * 16);
+  const int grid = static_cast<int>(ceil_div64(output_len, 256) < sm_count() * 16 ? ceil_div64(output_len, 256) : sm_count() * 16);
   indexed_flatten_kernel<<<grid > 0 ? grid : 1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       input, E, T, f_len, output_len, row_offsets, row_offsets_start_dev, padding_val, out);
   B200MOE_LAUNCH_OK("indexed_flatten_kernel");
@@ -412,7 +412,7 @@ extern "C" int b200moe_build_position_table(const int32_t* token_position_to_id,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200MOE_CUDA_OK(cudaMemsetAsync(pos_table, 0xFF, static_cast<size_t>(T) * E * 4, st));
   const int64_t n_pos = static_cast<int64_t>(n_blocks) * B;
-  const int grid = static_cast<int>(ceil_div64(n_pos, 256) < 148 * 8 ? ceil_div64(n_pos, 256) : 148 * 8);
+  const int grid = static_cast<int>(ceil_div64(n_pos, 256) < sm_count() * 8 ? ceil_div64(n_pos, 256) : sm_count() * 8);
   position_table_kernel<<<grid, 256, 0, st>>>(token_position_to_id, block_to_expert, conditions, n_pos, B, T, E,
                                               pos_table);
   B200MOE_LAUNCH_OK("position_table_kernel");

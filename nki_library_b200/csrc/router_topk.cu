@@ -20,7 +20,6 @@ int router_tc_run(const void* x, const void* w, int T, int H, int E, void* works
 namespace {
 
 constexpr size_t kWsHeader = 256;  // workspace bytes in front of the scratch: int32 status word, then padding
-int g_router_path = 0;             // 0 = by shape, 1 = split-K mma.sync path, 2 = tcgen05 path when eligible
 constexpr int kTcMinTokens = 8192;
 
 constexpr int kKC = 64;           // hidden slab per pipeline stage
@@ -374,16 +373,11 @@ extern "C" size_t b200moe_router_workspace_bytes(int T, int H, int E) {
   return kWsHeader + (split_k > tc ? split_k : tc);
 }
 
-extern "C" int b200moe_set_router_path(int path) {
-  B200MOE_REQUIRE(path >= 0 && path <= 2, B200MOE_ERR_INVALID, "router path must be 0, 1 or 2, got %d", path);
-  g_router_path = path;
-  return B200MOE_OK;
-}
-
 extern "C" int b200moe_router_topk(const void* x, int x_is_TH, const void* w, const void* w_bias, int T, int H, int E,
                                    int k, int act_fn, int router_pre_norm, int norm_topk_prob, void* router_logits,
                                    int logits_dtype, uint32_t* expert_index, void* expert_affinities, int aff_dtype,
-                                   void* workspace, size_t workspace_bytes, b200moe_stream_t stream) {
+                                   int path, void* workspace, size_t workspace_bytes, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(path >= 0 && path <= 2, B200MOE_ERR_INVALID, "router_topk: path must be 0, 1 or 2, got %d", path);
   B200MOE_REQUIRE(x && w, B200MOE_ERR_INVALID, "router_topk: x and w must not be null");
   B200MOE_REQUIRE(T > 0 && H > 0, B200MOE_ERR_INVALID, "router_topk: T and H must be positive");
   B200MOE_REQUIRE(E >= 1 && E <= 512, B200MOE_ERR_INVALID, "router_topk: E must be in [1, 512], got %d", E);
@@ -398,7 +392,7 @@ extern "C" int b200moe_router_topk(const void* x, int x_is_TH, const void* w, co
   const RouterPlan p = plan_router(T, H, E, x_is_TH);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool use_tc = router_tc_eligible(x_is_TH, T, H, E) &&
-                      (g_router_path == 2 || (g_router_path == 0 && T >= kTcMinTokens));
+                      (path == 2 || (path == 0 && T >= kTcMinTokens));
   const size_t need = kWsHeader + (use_tc ? router_tc_workspace_bytes(T, H, E)
                                           : static_cast<size_t>(p.splits) * T * E * sizeof(float));
   B200MOE_REQUIRE(workspace != nullptr && workspace_bytes >= need, B200MOE_ERR_WORKSPACE,

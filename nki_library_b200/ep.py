@@ -73,7 +73,7 @@ class CudaOps:
                          device=dev)
         _lib.call("b200moe_router_topk", _lib.ptr(hidden), 1, _lib.ptr(self.w), _lib.ptr(self.bias), T, self.H, self.E,
                   self.K, self.router_act.value, int(self.pre_norm), int(self.l1), None, _lib.F32, _lib.ptr(idx),
-                  _lib.ptr(aff), _lib.F32, _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
+                  _lib.ptr(aff), _lib.F32, 0, _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
         self.launches += 2
         return idx, aff
 
@@ -310,7 +310,7 @@ class PeerExpertParallelMoE:
 
         _lib.call("b200moe_router_topk", _lib.ptr(hidden), 1, _lib.ptr(ops.w), _lib.ptr(ops.bias), T, H, E, K,
                   ops.router_act.value, int(ops.pre_norm), int(ops.l1), None, _lib.F32, _lib.ptr(self.idx),
-                  _lib.ptr(self.aff), _lib.F32, _lib.ptr(self.rws), self.rws.numel(), st)
+                  _lib.ptr(self.aff), _lib.F32, 0, _lib.ptr(self.rws), self.rws.numel(), st)
         # block size 1 turns the grouping kernel into "sort the (token, k) pairs by expert, stable in the token id"
         _lib.call("b200moe_group_tokens", _lib.ptr(self.idx), _lib.ROUTING_INDEX, _lib.I32, T, E, K, 1, T * K, 1, 1,
                   _lib.ptr(self.pair_token), _lib.ptr(self.pair_expert), _lib.ptr(self.pair_cond), _lib.ptr(self.counts),
@@ -329,7 +329,7 @@ class PeerExpertParallelMoE:
         _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(self.xq), _lib.ptr(self.sf), _lib.ptr(w.w1),
                   _lib.ptr(w.w1_sf), w.w_format, _lib.ptr(w.bias_gu), _lib.ptr(self.b2e), _lib.ptr(self.cond),
                   _lib.ptr(self.tile_flags), self.n_blocks_cap, B, E_L, H, I, ops.act_fn.value, nan, nan, nan, nan,
-                  _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(self.status[1:]), 0, st)
+                  _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(self.status[1:]), 0, None, st)
         mark("t2")
         if self.fuse_return:
             # the down contraction's epilogue stores every row into the GPU its token came from
@@ -343,7 +343,7 @@ class PeerExpertParallelMoE:
             _lib.call("b200moe_grouped_gemm2_scale", _lib.ptr(self.mq), _lib.ptr(self.m_sf), _lib.ptr(w.w2),
                       _lib.ptr(w.w2_sf), w.w_format, _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond),
                       _lib.ptr(self.tile_flags), _lib.ptr(self.row_valid), self.cap_rows, self.n_blocks_cap, B, E_L,
-                      H, I, _lib.ptr(self.row_aff), _lib.F32, 1, _lib.ptr(self.y_pos), _lib.ptr(self.status[2:]), 0, st)
+                      H, I, _lib.ptr(self.row_aff), _lib.F32, 1, _lib.ptr(self.y_pos), _lib.ptr(self.status[2:]), 0, None, st)
             mark("t3")
             _lib.call("b200moe_ep_return_rows", _lib.ptr(self.y_pos), _lib.ptr(self.row_valid),
                       _lib.ptr(self.row_src), self.p_back, G, self.cap_rows, H, T * K, st)

@@ -24,8 +24,13 @@ class MoELayer:
     def __init__(self, router_w: torch.Tensor, weights: ExpertWeights, top_k: int, block_size: int,
                  max_tokens: int, router_bias: Optional[torch.Tensor] = None,
                  router_act: RouterActFnType = RouterActFnType.SOFTMAX, router_pre_norm: bool = True,
-                 norm_topk_prob: bool = True, act_fn: ActFnType = ActFnType.SiLU):
+                 norm_topk_prob: bool = True, act_fn: ActFnType = ActFnType.SiLU, router_path: int = 0,
+                 gemm_variant: int = 0):
+        """``router_path`` / ``gemm_variant`` are the per-call variant words of the router and of the grouped
+        contractions (0 = the library's own choice)."""
         _lib.require_cuda(router_w, router_bias)
+        self.router_path, self.gemm_variant = int(router_path), int(gemm_variant)
+        self.clock_probe = None  # optional int64[4] device tensor: {cycles, ns} of the gate/up and down contractions
         self.w = router_w.to(torch.bfloat16).contiguous()
         self.bias = None if router_bias is None else router_bias.reshape(-1).to(torch.bfloat16).contiguous()
         self.weights = weights
@@ -52,10 +57,12 @@ class MoELayer:
         # launches per forward pass: router (logits + ranking, or weight transpose + tcgen05 logits + ranking for
         # large T), grouping (3, or 1 up to 256 tokens), quantise, the contractions (CTA-pair launch + left-over launch each when the
         # library takes its pair path, else one each), combine -- mirrors the library's own shape rules
-        router_launches = 3 if (T >= 8192 and E <= 256 and self.H % 64 == 0) else 2
-        pair_path = B % 256 == 0 or self.N * (B // 128) >= 4 * E
+        tc_ok = E <= 256 and self.H % 64 == 0
+        router_launches = 3 if (tc_ok and (router_path == 2 or (router_path == 0 and T >= 8192))) else 2
+        pair_path = not (gemm_variant & (_lib.GEMM_NO_PAIR | _lib.GEMM_TILE_N128)) and (
+            B % 256 == 0 or bool(gemm_variant & _lib.GEMM_FORCE_PAIR) or self.N * (B // 128) >= 4 * E)
         group_launches = 1 if T <= 256 else 3  # one 256-token chunk: the three grouping phases share a CTA
-        self.kernels_per_forward = router_launches + group_launches + 1 + (4 if pair_path else 2) + 1
+        self.kernels_per_forward = router_launches + group_launches + 1 + (2 if not pair_path else (2 if gemm_variant & _lib.GEMM_NO_SPLIT else 4)) + 1
 
     def forward(self, hidden: torch.Tensor, timers: Optional[dict] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -84,7 +91,7 @@ class MoELayer:
         timed("router_topk", lambda: _lib.call(
             "b200moe_router_topk", _lib.ptr(hidden), 1, _lib.ptr(self.w), _lib.ptr(self.bias), T, H, E, K,
             self.router_act.value, int(self.pre_norm), int(self.l1), None, _lib.F32, _lib.ptr(self.idx),
-            _lib.ptr(self.aff), _lib.F32, _lib.ptr(self.rws), self.rws.numel(), st))
+            _lib.ptr(self.aff), _lib.F32, self.router_path, _lib.ptr(self.rws), self.rws.numel(), st))
         timed("group_tokens", lambda: _lib.call(
             "b200moe_group_tokens", _lib.ptr(self.idx), _lib.ROUTING_INDEX, _lib.I32, T, E, K, B, N, 1, 1,
             _lib.ptr(self.tpi), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(self.counts), _lib.ptr(self.inv),
@@ -97,11 +104,13 @@ class MoELayer:
         timed("gemm1_swiglu", lambda: _lib.call(
             "b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(w.w1), _lib.ptr(w.w1_sf), w.w_format,
             _lib.ptr(w.bias_gu), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(ws.tile_flags), N, B, E, H, I,
-            self.act_fn.value, nan, nan, nan, nan, _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(ws.status[1:]), 0, st))
+            self.act_fn.value, nan, nan, nan, nan, _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(ws.status[1:]),
+            self.gemm_variant, None if self.clock_probe is None else _lib.ptr(self.clock_probe[0:]), st))
         timed("gemm2_scale", lambda: _lib.call(
             "b200moe_grouped_gemm2_scale", _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(w.w2), _lib.ptr(w.w2_sf), w.w_format,
             _lib.ptr(w.bias_d), _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(ws.tile_flags), _lib.ptr(self.tpi),
-            T, N, B, E, H, I, _lib.ptr(self.aff), _lib.F32, 0, _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), 0, st))
+            T, N, B, E, H, I, _lib.ptr(self.aff), _lib.F32, 0, _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]),
+            self.gemm_variant, None if self.clock_probe is None else _lib.ptr(self.clock_probe[2:]), st))
         timed("combine", lambda: _lib.call(
             "b200moe_combine", _lib.ptr(ws.y_pos), _lib.ptr(self.inv), T, K, H, _lib.ptr(out), st))
         return out

@@ -89,13 +89,13 @@ def run_blocks(hidden: torch.Tensor, hidden_rows: int, weights: ExpertWeights, t
               _lib.ptr(weights.w1_sf), weights.w_format, _lib.ptr(weights.bias_gu), _lib.ptr(block_to_expert), _lib.ptr(conditions),
               _lib.ptr(ws.tile_flags), n_blocks, block_size, E, H, I, act_fn, _clamp(gate_clamp[0]),
               _clamp(gate_clamp[1]), _clamp(up_clamp[0]), _clamp(up_clamp[1]), _lib.ptr(ws.mq), _lib.ptr(ws.m_sf),
-              _lib.ptr(ws.status[1:]), impl, st)
+              _lib.ptr(ws.status[1:]), impl, None, st)
     mark("t2")
     _lib.call("b200moe_grouped_gemm2_scale", _lib.ptr(ws.mq), _lib.ptr(ws.m_sf), _lib.ptr(weights.w2),
               _lib.ptr(weights.w2_sf), weights.w_format, _lib.ptr(weights.bias_d), _lib.ptr(block_to_expert), _lib.ptr(conditions),
               _lib.ptr(ws.tile_flags), _lib.ptr(token_position_to_id), hidden_rows, n_blocks, block_size, E, H, I,
               _lib.ptr(affinities), _lib.F32 if affinities is None else _lib.dtype_code(affinities),
-              int(aff_per_row), _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), impl, st)
+              int(aff_per_row), _lib.ptr(ws.y_pos), _lib.ptr(ws.status[2:]), impl, None, st)
     mark("t3")
     _lib.call("b200moe_combine", _lib.ptr(ws.y_pos), _lib.ptr(table), out.shape[0], table.shape[1], H, _lib.ptr(out), st)
     if check_status:

@@ -19,6 +19,8 @@ quantised to e4m3, as the reference's ``quantize_mx`` does
 
 from __future__ import annotations
 
+import threading
+import weakref
 from dataclasses import dataclass
 from typing import Optional
 
@@ -132,19 +134,31 @@ def prepare_from_nki(gate_up_proj_weight, gate_up_proj_scale, down_proj_weight, 
                     gate_and_up_proj_bias, down_proj_bias, _lib.LAYOUT_NKI_X4, E, H, I, fmt)
 
 
-_cache: dict = {}
+_cache: dict = {}  # key -> (weak references to the source tensors, prepared weights)
+_cache_lock = threading.Lock()
+
+
+def _evict(key) -> None:
+    with _cache_lock:
+        _cache.pop(key, None)
 
 
 def prepare_from_nki_cached(gate_up_proj_weight, gate_up_proj_scale, down_proj_weight, down_proj_scale,
                             gate_and_up_proj_bias=None, down_proj_bias=None, w_format=None) -> ExpertWeights:
-    """Memoised on the identity and version of the source tensors (weights are static during inference)."""
+    """Memoised on the identity and version of the source tensors (weights are static during inference).
+
+    An entry lives exactly as long as its source tensors: each is held by a weak reference whose callback drops
+    the entry, so a freed allocation that is handed out again can never be mistaken for the old weights, and a
+    model with any number of layers keeps one prepared copy per layer (no size limit, no thrashing)."""
     srcs = (gate_up_proj_weight, gate_up_proj_scale, down_proj_weight, down_proj_scale, gate_and_up_proj_bias,
             down_proj_bias)
-    key = tuple((t.data_ptr(), tuple(t.shape), t._version) if t is not None else None for t in srcs) + (w_format,)
-    hit = _cache.get(key)
-    if hit is None:
-        if len(_cache) > 8:
-            _cache.clear()
-        hit = prepare_from_nki(*srcs, w_format=w_format)
-        _cache[key] = hit
-    return hit
+    key = tuple((id(t), t.data_ptr(), tuple(t.shape), t._version) if t is not None else None for t in srcs) + (w_format,)
+    with _cache_lock:
+        hit = _cache.get(key)
+    if hit is not None and all(r is None or r() is s for r, s in zip(hit[0], srcs)):
+        return hit[1]
+    prepared = prepare_from_nki(*srcs, w_format=w_format)
+    refs = tuple(None if t is None else weakref.ref(t, lambda _r, k=key: _evict(k)) for t in srcs)
+    with _cache_lock:
+        _cache[key] = (refs, prepared)
+    return prepared

@@ -130,3 +130,159 @@ def routing_mask(T, E, K, seed=0):
     m = np.zeros((T, E), dtype=np.int32)
     m[np.arange(T)[:, None], idx] = 1
     return m
+
+
+# ---------------------------------------------------------------------------
+# MX fixtures: seeded inputs for the reference's MX CPU code (quantize_to_mx,
+# mx_matmul, the projection goldens, the prefill block loop and the decode
+# reference).  Everything is drawn from numpy Generators, so the fixture
+# generator and the tests rebuild identical arrays.
+# ---------------------------------------------------------------------------
+def bf16_round(a):
+    """fp32 values rounded to the bf16 grid (returned as fp32)."""
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy()
+
+
+def mx_quantize_input(P=128, F=512, seed=7):
+    """``[P, F]`` fp32 with 8 x 4 blocks of very different magnitude and the awkward cases in known blocks:
+    an all-zero block, one with a single subnormal, exact rounding ties of the e4m3 grid, block maxima whose
+    scaled value exceeds 448 and must clip, negative zero, and bf16-valued gaussian data elsewhere."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((P, F)).astype(np.float32)
+    mag = np.exp2(rng.integers(-24, 20, (P // 8, F // 4))).astype(np.float32)
+    x = bf16_round(x * np.repeat(np.repeat(mag, 8, 0), 4, 1))
+    x[0:8, 0:4] = 0.0
+    x[0:8, 4:8] = 0.0
+    x[3, 5] = np.float32(1e-41)                       # fp32 subnormal: biased exponent 0
+    x[8:16, 0:4] = np.float32(1.0625)                 # tie between 1.0 and 1.125 -> even (1.0)
+    x[8:16, 4:8] = np.float32(1.1875)                 # tie between 1.125 and 1.25 -> even (1.25)
+    x[8, 4] = np.float32(1.5)
+    x[16:24, 0:4] = np.float32(1.96875)               # 1.96875 * 2^8 = 504 > 448: clips
+    x[16:24, 4:8] = np.float32(-1.9375)               # -496: clips to -448
+    x[24:32, 0:4] = np.float32(-0.0)
+    x[24, 1] = np.float32(3.0)
+    x[32:40, 0:4] = np.float32(2.0 ** -9) * np.arange(32, dtype=np.float32).reshape(8, 4)  # subnormal codes after scaling
+    x[40:48, 0:4] = np.float32(2.0 ** 100)
+    x[40:48, 4:8] = np.float32(2.0 ** -120)
+    return x
+
+
+def mx_matmul_input(P=64, SF=24, MF=16, seed=11):
+    """Random finite e4m3 codes ``[P, 4*SF]`` / ``[P, 4*MF]`` with block scales ``[P/8, SF]`` / ``[P/8, MF]``."""
+    rng = np.random.default_rng(seed)
+
+    def codes(n):
+        c = rng.integers(0, 256, (P, 4 * n), dtype=np.uint8)
+        c[(c & 0x7F) == 0x7F] = 0x3C  # NaN patterns -> 1.5
+        return c
+
+    return (codes(SF), codes(MF), rng.integers(118, 132, (P // 8, SF), dtype=np.uint8),
+            rng.integers(118, 132, (P // 8, MF), dtype=np.uint8))
+
+
+def mx_encode_rows(values):
+    """Plain block-32 MXFP8 encoding of ``[R, K]`` used to fabricate *weights* (inputs, not results):
+    scale byte = block's largest biased exponent - 8, codes = value / 2^(scale-127) cast by ml_dtypes."""
+    import ml_dtypes
+
+    v = np.ascontiguousarray(values, dtype=np.float32)
+    R, K = v.shape
+    vb = v.reshape(R, K // 32, 32)
+    e = ((vb.view(np.uint32) >> 23) & 0xFF).astype(np.int32).max(axis=2)
+    s = np.clip(e - 8, 0, 255)
+    q = np.clip(vb / np.exp2((s - 127).astype(np.float64))[:, :, None], -448, 448).astype(np.float32)
+    return q.astype(ml_dtypes.float8_e4m3fn).view(np.uint8).reshape(R, K), s.astype(np.uint8)
+
+
+# name: dict(T, H, I, E, K, B, act, bias, clamps (gate_hi, gate_lo, up_hi, up_lo), skip_token, dynamic, sample)
+# ``sample`` = number of token rows of the reference output kept in the fixture (None = all rows).
+MX_LAYER_CASES = {
+    # BASELINE configuration 1, plain
+    "c1_plain": dict(T=256, H=512, I=1024, E=4, K=2, B=128, act="silu", bias=False, clamps=(None, None, None, None),
+                     skip_token=True, dynamic=False, sample=None),
+    # the same layer in the style of the reference's unit vectors: bias, Swish, one-sided gate clamp, pad row T
+    "c1_bias_swish_clamp": dict(T=256, H=512, I=1024, E=4, K=2, B=128, act="swish", bias=True,
+                                clamps=(7.0, None, 7.0, -7.0), skip_token=False, dynamic=True, sample=None),
+    # test_moe_bwmm_mx_cte.py:72 at a reduced token count (T = 10240 there): H=3072, I=384, E=128, B=256, top-4
+    "ref_h3072_i384_e128_b256_k4": dict(T=1024, H=3072, I=384, E=128, K=4, B=256, act="swish", bias=True,
+                                        clamps=(7.0, None, 7.0, -7.0), skip_token=True, dynamic=False, sample=48),
+    # test_moe_bwmm_mx_cte.py:85 at a reduced token count (T = 4096 there): dynamic loop, n_static_blocks = 2
+    "ref_h3072_i384_e2_b256_k2_dynamic": dict(T=1024, H=3072, I=384, E=2, K=2, B=256, act="silu", bias=True,
+                                              clamps=(7.0, None, 7.0, -7.0), skip_token=True, dynamic=True,
+                                              sample=48),
+}
+
+
+def _case_seed(name):
+    return sum(map(ord, name))
+
+
+def mx_layer_routing(name):
+    """Seeded routing of a prefill case: ``expert_index [T, K]``, 0/1 ``mask [T, E]`` and bf16-valued masked
+    affinities ``[rows, E]`` (rows = T, or T + 1 with a zero pad row when the case keeps the pad token)."""
+    c = MX_LAYER_CASES[name]
+    T, E, K = c["T"], c["E"], c["K"]
+    rng = np.random.default_rng(_case_seed(name) + 2)
+    idx = np.argsort(-rng.random((T, E)), axis=1, kind="stable")[:, :K].astype(np.int32)
+    mask = np.zeros((T, E), dtype=np.int32)
+    mask[np.arange(T)[:, None], idx] = 1
+    rows = T if c["skip_token"] else T + 1
+    aff = np.zeros((rows, E), dtype=np.float32)
+    aff[:T] = bf16_round(rng.random((T, E)) * mask)
+    return idx, mask, aff
+
+
+def mx_layer_inputs(name):
+    """Everything one prefill case needs, in plain rows form (the generator script converts the weights to the
+    reference's storage with pure permutations).  Values the reference holds in bf16 are bf16-exact fp32."""
+    c = MX_LAYER_CASES[name]
+    T, H, I, E = c["T"], c["H"], c["I"], c["E"]
+    rows = T if c["skip_token"] else T + 1
+    hidden = bf16_round(np.random.default_rng(_case_seed(name)).standard_normal((rows, H)))
+    if not c["skip_token"]:
+        hidden[T] = 0
+    rng = np.random.default_rng(_case_seed(name) + 1)
+    c1, s1 = mx_encode_rows((rng.standard_normal((E * 2 * I, H), dtype=np.float32) * np.float32(0.02)))
+    c2, s2 = mx_encode_rows((rng.standard_normal((E * H, I), dtype=np.float32) * np.float32(0.02)))
+    idx, mask, aff = mx_layer_routing(name)
+    out = dict(case=c, hidden=hidden, aff=aff, expert_index=idx, mask=mask,
+               w1_codes=c1.reshape(E, 2, I, H), w1_scales=s1.reshape(E, 2, I, H // 32),
+               w2_codes=c2.reshape(E, H, I), w2_scales=s2.reshape(E, H, I // 32), bias_gu=None, bias_d=None)
+    if c["bias"]:
+        rng = np.random.default_rng(_case_seed(name) + 3)
+        out["bias_gu"] = bf16_round(rng.uniform(-2.0625, 0.52, (E, 2, I)))   # ranges of test_utils.py:430-433
+        out["bias_d"] = bf16_round(rng.uniform(-1.632, 1.4375, (E, H)))
+    return out
+
+
+MX_DECODE_CASES = {
+    # name: (T, H, I, E, K, act, all_expert)
+    "sel_t8_h512_i256_e4_k2_swish": (8, 512, 256, 4, 2, "swish", False),
+    "all_t16_h512_i256_e4_silu": (16, 512, 256, 4, 2, "silu", True),
+    # test_moe_tkg.py "=== MXFP8" selective row at fewer experts (E = 128 there): T=2, H=3072, I=1536, top-8
+    "sel_t2_h3072_i1536_e16_k8_silu": (2, 3072, 1536, 16, 8, "silu", False),
+}
+
+
+def mx_decode_inputs(name):
+    T, H, I, E, K, act, all_expert = MX_DECODE_CASES[name]
+    rng = np.random.default_rng(sum(map(ord, name)))
+    hidden = bf16_round(rng.standard_normal((T, H)))
+    w1 = (rng.standard_normal((E * 2 * I, H)) * 0.02).astype(np.float32)
+    w2 = (rng.standard_normal((E * H, I)) * 0.02).astype(np.float32)
+    c1, s1 = mx_encode_rows(w1)
+    c2, s2 = mx_encode_rows(w2)
+    idx = np.argsort(-rng.random((T, E)), axis=1, kind="stable")[:, :K].astype(np.int32)
+    aff = bf16_round(rng.random((T, E)))
+    return dict(T=T, H=H, I=I, E=E, K=K, act=act, all_expert=all_expert, hidden=hidden, aff=aff, expert_index=idx,
+                w1_codes=c1.reshape(E, 2, I, H), w1_scales=s1.reshape(E, 2, I, H // 32),
+                w2_codes=c2.reshape(E, H, I), w2_scales=s2.reshape(E, H, I // 32),
+                bias_gu=bf16_round(rng.uniform(-2.0625, 0.52, (E, 2, I))),
+                bias_d=bf16_round(rng.uniform(-1.632, 1.4375, (E, H))),
+                clamps=(7.0, None, 7.0, -7.0))
+
+
+def sample_rows(name, n_rows, count):
+    """The token rows of a large case whose reference outputs are kept (seeded choice, ascending)."""
+    rng = np.random.default_rng(sum(map(ord, name)) + 1)
+    return np.sort(rng.choice(n_rows, size=count, replace=False))

@@ -44,10 +44,10 @@ def test_sf_bytes_query():
 def test_invalid_arguments_return_status_and_message():
     from nki_library_b200 import _lib
     lib = _lib.load_library()
-    rc = lib.b200moe_router_topk(None, 1, None, None, 4, 128, 8, 2, 1, 1, 0, None, 0, None, None, 0, None, 0, None)
+    rc = lib.b200moe_router_topk(None, 1, None, None, 4, 128, 8, 2, 1, 1, 0, None, 0, None, None, 0, 0, None, 0, None)
     assert rc == -1 and b"must not be null" in lib.b200moe_last_error()
-    rc = lib.b200moe_set_gemm_tile_n(64)
-    assert rc == -1 and b"128 or 256" in lib.b200moe_last_error()
+    rc = lib.b200moe_router_topk(1, 1, 1, None, 4, 128, 8, 2, 1, 1, 0, None, 0, None, None, 0, 7, None, 0, None)
+    assert rc == -1 and b"path must be 0, 1 or 2" in lib.b200moe_last_error()
     with pytest.raises(AssertionError, match=r"\[INTERNAL_ERROR\] \[NCC_INKI016\] Kernel validation exception"):
         _lib.call("b200moe_combine", None, None, 1, 1, 8, None, None)
 

@@ -36,7 +36,7 @@ def _run_gemm1(m, weights, x_np, b2e_np, B, impl, act=0, clamps=(None,) * 4):
     _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(weights.w1),
               _lib.ptr(weights.w1_sf), weights.w_format, _lib.ptr(weights.bias_gu), _lib.ptr(b2e), None, _lib.ptr(ws.tile_flags),
               len(b2e_np), B, weights.E, H, weights.I, act, c[0], c[1], c[2], c[3], _lib.ptr(ws.mq), _lib.ptr(ws.m_sf),
-              _lib.ptr(ws.status[1:]), impl, st)
+              _lib.ptr(ws.status[1:]), impl, None, st)
     torch.cuda.synchronize()
     assert ws.status.cpu().tolist()[1] == 0, "a device-side wait expired"
     return ws.mq.cpu().numpy(), sf_atoms_to_rows(ws.m_sf.cpu().numpy(), n_pos, weights.I)
@@ -46,29 +46,27 @@ def _run_gemm1(m, weights, x_np, b2e_np, B, impl, act=0, clamps=(None,) * 4):
 def test_gate_up_swiglu_requantise_vs_oracle(impl, tile_n):
     import nki_library_b200 as m
     from nki_library_b200 import _lib
-    _lib.call("b200moe_set_gemm_tile_n", tile_n)
-    try:
-        E, H, I, B = 3, 512, 384, 128
-        w_np = make_rows_weights(E, H, I, seed=1)
-        rng = np.random.default_rng(0)
-        bgu = rng.uniform(-1, 0.5, (E, 2, I)).astype(np.float32)
-        weights = _prep(m, w_np, bgu)
-        b2e = np.array([0, 2, 2, 1])
-        x = bf16_values(rng.standard_normal((len(b2e) * B, H)).astype(np.float32))
-        mq, ms = _run_gemm1(m, weights, x, b2e, B, impl, act=moe.SWISH, clamps=(-7.0, 7.0, -7.0, 7.0))
-        got = mx.dequantize_mx_rows(mq, ms)
-        for b, e in enumerate(b2e):
-            ew = moe.ExpertWeights(*w_np, e)
-            _, parts = moe.expert_mlp_rows(x[b * B:(b + 1) * B], ew, bgu[e], None, act=moe.SWISH,
-                                           gate_clamp=(-7, 7), up_clamp=(-7, 7), return_parts=True)
-            ref = mx.dequantize_mx_rows(parts["mq"], parts["ms"])
-            sl = slice(b * B, (b + 1) * B)
-            assert max_rel(got[sl], ref) <= TOL
-            # identical quantised inputs and fp32 accumulation: nearly every code and scale is identical
-            assert (ms[sl] == parts["ms"]).mean() > 0.99
-            assert (mq[sl] == parts["mq"]).mean() > 0.97
-    finally:
-        _lib.call("b200moe_set_gemm_tile_n", 256)
+    if tile_n == 128:
+        impl |= _lib.GEMM_TILE_N128
+    E, H, I, B = 3, 512, 384, 128
+    w_np = make_rows_weights(E, H, I, seed=1)
+    rng = np.random.default_rng(0)
+    bgu = rng.uniform(-1, 0.5, (E, 2, I)).astype(np.float32)
+    weights = _prep(m, w_np, bgu)
+    b2e = np.array([0, 2, 2, 1])
+    x = bf16_values(rng.standard_normal((len(b2e) * B, H)).astype(np.float32))
+    mq, ms = _run_gemm1(m, weights, x, b2e, B, impl, act=moe.SWISH, clamps=(-7.0, 7.0, -7.0, 7.0))
+    got = mx.dequantize_mx_rows(mq, ms)
+    for b, e in enumerate(b2e):
+        ew = moe.ExpertWeights(*w_np, e)
+        _, parts = moe.expert_mlp_rows(x[b * B:(b + 1) * B], ew, bgu[e], None, act=moe.SWISH,
+                                       gate_clamp=(-7, 7), up_clamp=(-7, 7), return_parts=True)
+        ref = mx.dequantize_mx_rows(parts["mq"], parts["ms"])
+        sl = slice(b * B, (b + 1) * B)
+        assert max_rel(got[sl], ref) <= TOL
+        # identical quantised inputs and fp32 accumulation: nearly every code and scale is identical
+        assert (ms[sl] == parts["ms"]).mean() > 0.99
+        assert (mq[sl] == parts["mq"]).mean() > 0.97
 
 
 def _cte_case(T, H, I, E, K, B, seed, bias, act, clamp, zipf=None):
@@ -137,14 +135,13 @@ def test_moe_cte_cta_pair_mode(B, T, scatter):
     args = (torch.from_numpy(hidden).to(torch.bfloat16).cuda(), torch.from_numpy(aff).cuda().reshape(-1, 1), weights,
             None, tpi, b2e, B, m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx))
     kw = dict(conditions=cond, skip_dma=m.SkipMode(True, False), _check_status=True)
-    _lib.call("b200moe_set_gemm_cta_pair", 0)
-    try:
-        single = m.moe_cte(*args, **kw)
-        _lib.call("b200moe_set_gemm_cta_pair", 2)
-        paired = m.moe_cte(*args, **kw)
-        paired2 = m.moe_cte(*args, **kw)
-    finally:
-        _lib.call("b200moe_set_gemm_cta_pair", 1)
+    single = m.moe_cte(*args, _impl=_lib.GEMM_NO_PAIR, **kw)
+    paired = m.moe_cte(*args, _impl=_lib.GEMM_FORCE_PAIR, **kw)
+    paired2 = m.moe_cte(*args, _impl=_lib.GEMM_FORCE_PAIR, **kw)
+    # the same tiles with the left-over launch folded into half-empty pairs, and with it run strictly afterwards
+    folded = m.moe_cte(*args, _impl=_lib.GEMM_FORCE_PAIR | _lib.GEMM_NO_SPLIT, **kw)
+    serial = m.moe_cte(*args, _impl=_lib.GEMM_FORCE_PAIR | _lib.GEMM_NO_OVERLAP, **kw)
+    assert torch.equal(paired, folded) and torch.equal(paired, serial)
     ref = _oracle_cte(hidden, aff, w_np, tpi.cpu().numpy(), b2e.cpu().numpy(), cond.cpu().numpy(), B, bgu, bd,
                       moe.SILU, None)
     assert max_rel(paired.float().cpu().numpy(), ref) <= TOL

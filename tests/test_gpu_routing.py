@@ -35,10 +35,7 @@ def digests():
 def router_path(request):
     """Runs a router test on the split-K path and with the single-kernel tcgen05 path forced wherever the shape
     is eligible for it (x [T, H], E <= 256, H % 64 == 0; other shapes fall back by themselves)."""
-    from nki_library_b200 import _lib
-    _lib.call("b200moe_set_router_path", 1 if request.param == "split_k" else 2)
-    yield request.param
-    _lib.call("b200moe_set_router_path", 0)
+    return request.param
 
 
 @pytest.mark.parametrize("name", list(gi.ROUTER_CASES))
@@ -55,7 +52,8 @@ def test_router_topk_vs_reference_fixture(lib, name, x_layout, router_path):
     aff = torch.empty((T, E), dtype=torch.float32, device="cuda")
     idx = torch.empty((T, k), dtype=torch.int32, device="cuda")
     outs = lib.router_topk(xd, w.cuda(), None if b is None else b.cuda(), logits, aff, idx, act_e, k, x_layout, 0,
-                           router_pre_norm=pre_norm, norm_topk_prob=l1, use_indirect_dma_scatter=True)
+                           router_pre_norm=pre_norm, norm_topk_prob=l1, use_indirect_dma_scatter=True,
+                           _path=1 if router_path == "split_k" else 2)
     assert outs[0] is logits and outs[1] is idx and outs[2] is aff
     lg = logits.cpu().numpy()
     # bf16 products are exact in fp32; only the summation order (tensor-core tree, split-K) differs
