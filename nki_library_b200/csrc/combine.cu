@@ -6,12 +6,12 @@
 namespace b200moe {
 namespace {
 
-constexpr int kMaxRows = 64;
+constexpr int kMaxCandidates = 8192;  // table width limit: the row list of one token lives in shared memory
 
 __global__ void __launch_bounds__(128) combine_kernel(const __nv_bfloat16* __restrict__ y_pos,
                                                       const int32_t* __restrict__ table, int T, int n_cand, int H,
                                                       __nv_bfloat16* __restrict__ out) {
-  __shared__ int32_t s_rows[kMaxRows];
+  extern __shared__ int32_t s_rows[];  // n_cand entries: every candidate may be valid (all-expert decode)
   __shared__ int s_n;
   const int t = blockIdx.x;
   if (threadIdx.x < 32) {
@@ -21,10 +21,10 @@ __global__ void __launch_bounds__(128) combine_kernel(const __nv_bfloat16* __res
       const int32_t p = c < n_cand ? table[static_cast<int64_t>(t) * n_cand + c] : -1;
       const unsigned m = __ballot_sync(0xffffffffu, p >= 0);
       const int slot = base + __popc(m & ((1u << threadIdx.x) - 1u));
-      if (p >= 0 && slot < kMaxRows) s_rows[slot] = p;
+      if (p >= 0) s_rows[slot] = p;
       base += __popc(m);
     }
-    if (threadIdx.x == 0) s_n = base < kMaxRows ? base : kMaxRows;
+    if (threadIdx.x == 0) s_n = base;
   }
   __syncthreads();
   const int n = s_n;
@@ -59,7 +59,9 @@ extern "C" int b200moe_combine(const void* y_pos_bf16, const int32_t* table, int
   B200MOE_REQUIRE(y_pos_bf16 && table && out_bf16, B200MOE_ERR_INVALID, "combine: null pointer argument");
   B200MOE_REQUIRE(T > 0 && n_cand > 0 && H > 0 && H % 8 == 0, B200MOE_ERR_INVALID,
                   "combine: need T, n_cand > 0 and H %% 8 == 0");
-  combine_kernel<<<T, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  B200MOE_REQUIRE(n_cand <= kMaxCandidates, B200MOE_ERR_INVALID, "combine: at most %d candidates per row, got %d",
+                  kMaxCandidates, n_cand);
+  combine_kernel<<<T, 128, static_cast<size_t>(n_cand) * sizeof(int32_t), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(y_pos_bf16), table, T, n_cand, H, static_cast<__nv_bfloat16*>(out_bf16));
   B200MOE_LAUNCH_OK("combine_kernel");
   return B200MOE_OK;

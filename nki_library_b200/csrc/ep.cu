@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(256) ep_return_rows_kernel(const __nv_bfloat16
     const int32_t src = row_src[r];
     const int d = (src >> 24) & 0x7f;
     const int64_t p = src & 0xffffff;
-    if (d >= kMaxRanks || p >= back_rows) continue;
+    if (d >= kMaxRanks || p >= back_rows || back.p[d] == nullptr) continue;  // ranks past `world` hold no buffer
     const uint4 val = __ldg(reinterpret_cast<const uint4*>(y_pos + r * H) + v);
     reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(back.p[d]) + p * H)[v] = val;
   }

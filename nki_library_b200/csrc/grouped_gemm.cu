@@ -12,9 +12,9 @@
 //   warps 8..15 epilogue: two warps per TMEM lane quadrant, each thread pulls half of
 //               its accumulator row into registers with tcgen05.ld, hands the TMEM
 //               buffer back to the MMA warp at once, then works from registers
-//               EPI 0: + bias, clamp, act(gate) * up, bf16 rounding, MXFP8
-//                      re-quantisation (32 consecutive intermediates live in one
-//                      thread), codes + scale atoms out
+//               EPI 0: + bias, clamp, act(gate) * up in fp32, MXFP8 re-quantisation
+//                      of the fp32 product (32 consecutive intermediates live in
+//                      one thread), codes + scale atoms out
 //               EPI 1: + bias, x routing affinity, bf16 rows out
 // Tiles are (128 positions) x (BLOCK_N weight rows); a tile's expert comes from
 // block_to_expert, padded / inactive tiles are skipped.  Tiles are enumerated
@@ -520,14 +520,14 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float sg = __fdividef(g[j], 1.0f + __expf(-g[j]));
-              const float m = __bfloat162float(__float2bfloat16_rn(sg * u[j]));
+              const float m = sg * u[j];
               g[j] = m;
               mx = max(mx, __float_as_uint(m) & 0x7fffffffu);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float m = __bfloat162float(__float2bfloat16_rn(apply_act(g[j], p.act) * u[j]));
+              const float m = apply_act(g[j], p.act) * u[j];
               g[j] = m;
               mx = max(mx, __float_as_uint(m) & 0x7fffffffu);
             }
@@ -680,7 +680,7 @@ __global__ void simt_gemm1_kernel(const uint8_t* x, const uint8_t* w, GemmParams
       if (p.gate_hi == p.gate_hi) gv = fminf(gv, p.gate_hi);
       if (p.up_lo == p.up_lo) uv = fmaxf(uv, p.up_lo);
       if (p.up_hi == p.up_hi) uv = fminf(uv, p.up_hi);
-      m[j] = __bfloat162float(__float2bfloat16_rn(apply_act(gv, p.act) * uv));
+      m[j] = apply_act(gv, p.act) * uv;
       mx = max(mx, __float_as_uint(m[j]) & 0x7fffffffu);
     }
     float f1, f2;

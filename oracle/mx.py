@@ -12,13 +12,15 @@ of MX quantisation and of the MX block-scaled matmul:
 * x4 packing (byte j of a 32-bit word = element j) core/utils/mx_torch_common.py:114-124
 * weight / activation "swizzled" layouts ..... test/integration/nkilib/core/mlp/test_mlp_common.py:550-682
 
-The fp32 -> e4m3 rounding itself happens inside a third-party package that the
-reference does not vendor (``neuron_dtypes.static_cast``); the rule adopted
-here is IEEE round-to-nearest-even onto the e4m3fn grid after the +-448 clip
-(what ``ml_dtypes.float8_e4m3fn`` and the GPU's ``cvt.rn.satfinite.e4m3x2.f32``
-both do).  That single choice is "parity unpinned" with respect to Trainium
-hardware; everything else in this file is pinned by the reference's own
-source.
+Pinned: ``quantize_to_mx_ref_blocks`` reproduces the reference's own
+``quantize_to_mx`` bit for bit and the contraction its ``mx_matmul`` to 1e-6 on
+the fixtures in tests/golden/mx_ref.npz (tests/test_oracle_golden.py), which
+were produced by running the reference's code with two stand-in packages
+(tests/golden/standins).  One declared assumption remains: the fp32 -> e4m3
+rounding lives in ``neuron_dtypes.static_cast``, a package the reference does
+not vendor; the stand-in and this file use IEEE round-to-nearest-even onto the
+e4m3fn grid after the +-448 clip (what ``ml_dtypes.float8_e4m3fn`` and the
+GPU's ``cvt.rn.satfinite.e4m3x2.f32`` both do).
 """
 
 from __future__ import annotations

@@ -17,6 +17,9 @@ toolchain (``router_topk_torch_ref``, ``find_nonzero_indices_torch_ref``,
 reference's own tests (``test_router_topk_common.py:30-49``,
 ``test_find_nonzero_indices.py:29-45,63-82``, ``test_indexed_flatten.py:28-70``)
 and stores their outputs: small cases in full, large ones as SHA-256 digests.
+The MX CPU code (``quantize_to_mx``, ``mx_matmul``, the projection goldens,
+``generate_blockwise_numpy_golden``, ``_moe_tkg_mx_ref``) is run by
+``make_golden_mx.py``, which this script calls last.
 Inputs are not stored; ``tests/golden_inputs.py`` regenerates them from the
 same seeds.  The tests then check the CPU oracle (and, on a GPU, the CUDA
 path) against these files without needing the reference checkout.
@@ -137,6 +140,10 @@ def main(ref_root: str) -> None:
     with open(os.path.join(HERE, "grouping_ref_digests.json"), "w") as f:
         json.dump(digests, f, indent=1, sort_keys=True)
     print("wrote fixtures to", HERE)
+    # MX arithmetic (quantise, block-scaled matmul, projections, prefill block loop, decode): needs the two
+    # stand-in packages under tests/golden/standins, see make_golden_mx.py
+    import make_golden_mx
+    make_golden_mx.main(ref_root)
 
 
 if __name__ == "__main__":

@@ -182,16 +182,23 @@ def mx_matmul_input(P=64, SF=24, MF=16, seed=11):
 
 def mx_encode_rows(values):
     """Plain block-32 MXFP8 encoding of ``[R, K]`` used to fabricate *weights* (inputs, not results):
-    scale byte = block's largest biased exponent - 8, codes = value / 2^(scale-127) cast by ml_dtypes."""
+    scale byte = block's largest biased exponent - 8, codes = value / 2^(scale-127) cast by ml_dtypes
+    (a power-of-two scaling, exact in fp32).  Works through the rows in slices to bound memory."""
     import ml_dtypes
 
     v = np.ascontiguousarray(values, dtype=np.float32)
     R, K = v.shape
-    vb = v.reshape(R, K // 32, 32)
-    e = ((vb.view(np.uint32) >> 23) & 0xFF).astype(np.int32).max(axis=2)
-    s = np.clip(e - 8, 0, 255)
-    q = np.clip(vb / np.exp2((s - 127).astype(np.float64))[:, :, None], -448, 448).astype(np.float32)
-    return q.astype(ml_dtypes.float8_e4m3fn).view(np.uint8).reshape(R, K), s.astype(np.uint8)
+    codes = np.empty((R, K), dtype=np.uint8)
+    scales = np.empty((R, K // 32), dtype=np.uint8)
+    step = max(1, (1 << 24) // K)
+    for r0 in range(0, R, step):
+        vb = v[r0:r0 + step].reshape(-1, K // 32, 32)
+        e = ((vb.view(np.uint32) >> 23) & 0xFF).astype(np.int32).max(axis=2)
+        s = np.clip(e - 8, 0, 255)
+        q = np.clip(np.ldexp(vb, (127 - s)[:, :, None]), -448, 448).astype(np.float32)
+        codes[r0:r0 + step] = q.astype(ml_dtypes.float8_e4m3fn).view(np.uint8).reshape(-1, K)
+        scales[r0:r0 + step] = s.astype(np.uint8)
+    return codes, scales
 
 
 # name: dict(T, H, I, E, K, B, act, bias, clamps (gate_hi, gate_lo, up_hi, up_lo), skip_token, dynamic, sample)

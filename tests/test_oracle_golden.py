@@ -188,3 +188,153 @@ def test_rows_oracle_equals_reference_layout_recipe(I):
         y = moe.expert_mlp_rows(hid[:, mx.hidden_packed_order(H)], moe.ExpertWeights(c1, s1, c2, s2, e), bgu[e], bd[e],
                                 act=moe.SWISH, gate_clamp=(-7, 7), up_clamp=(-7, 7), round_inter_bf16=False)
         assert np.abs(y - y_ref).max() <= 1e-5 * np.abs(y_ref).max()
+
+
+# ---------------------------------------------------------------------------
+# MX arithmetic against outputs of the reference's own CPU code
+# (tests/golden/mx_ref.npz, written by tests/golden/make_golden_mx.py)
+# ---------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def mx_gold():
+    return np.load(os.path.join(GOLD, "mx_ref.npz"))
+
+
+def _rel(a, ref):
+    return float(np.abs(np.asarray(a, np.float64) - np.asarray(ref, np.float64)).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def test_mx_quantize_matches_reference_quantize_to_mx(mx_gold):
+    """Codes and scales of ``quantize_to_mx`` (core/utils/mx_torch_common.py:157-221), bit for bit, on data with
+    zero blocks, fp32 subnormals, e4m3 rounding ties, clipping block maxima and 44 binades of dynamic range."""
+    x = gi.mx_quantize_input()
+    codes, scales = mx.quantize_to_mx_ref_blocks(x)
+    assert np.array_equal(scales, mx_gold["quantize/scales"])
+    assert np.array_equal(codes, mx_gold["quantize/codes"])
+    # the 1 x 32 block form the CUDA kernels use is the same arithmetic on the transposed-and-folded view
+    xb = gi.bf16_round(np.random.default_rng(3).standard_normal((64, 256)))
+    c2, s2 = mx.quantize_to_mx_ref_blocks(xb)
+    assert np.array_equal(c2, mx_gold["quantize/bf16_codes"]) and np.array_equal(s2, mx_gold["quantize/bf16_scales"])
+
+
+def test_mx_quantize_test_twin_differs_only_on_tiny_blocks(mx_gold):
+    """test/utils/mx_utils.py:56-99 is the same rule except that a block whose largest biased exponent is below 8
+    (all zeros, fp32 subnormals, magnitudes under 2^-119) gets the wrapped byte ``(e_max - 8) mod 256`` where the
+    src/ function clips to 0; the oracle follows src/."""
+    codes, scales = mx.quantize_to_mx_ref_blocks(gi.mx_quantize_input())
+    twin_s = mx_gold["quantize/test_twin_scales"]
+    differs = twin_s != scales
+    assert differs.sum() > 0 and np.all(twin_s[differs] >= 248) and np.all(scales[differs] == 0)
+    keep = np.repeat(np.repeat(~differs, 8, 0), 4, 1)
+    assert np.array_equal(codes[keep], mx_gold["quantize/test_twin_codes"][keep])
+
+
+def test_mx_matmul_matches_reference(mx_gold):
+    sc, mc, ss, ms = gi.mx_matmul_input()
+    got = moe._ref_mx_contract(sc, mc, ss, ms)
+    assert _rel(got, mx_gold["matmul/mx_matmul"]) <= 1e-6
+    assert _rel(got, mx_gold["matmul/nc_matmul_mx_golden"]) <= 1e-6
+
+
+def _projection_inputs(I):
+    """The seeded inputs of ``projection_fixture`` in tests/golden/make_golden_mx.py."""
+    import math
+    H, R = 512, 16
+    rng = np.random.default_rng(100 + I)
+    c1, s1 = gi.mx_encode_rows((rng.standard_normal((2 * I, H)) * 0.05).astype(np.float32))
+    c2, s2 = gi.mx_encode_rows((rng.standard_normal((H, I)) * 0.05).astype(np.float32))
+    gw, gs = mx.rows_to_ref_gate_up(c1.reshape(1, 2, I, H), s1.reshape(1, 2, I, H // 32))
+    dw, ds = mx.rows_to_ref_down(c2.reshape(1, H, I), s2.reshape(1, H, I // 32))
+    hidden = gi.bf16_round(rng.standard_normal((R, H)))
+    P = 128 if I > 512 else I // 4
+    nt = math.ceil(I / 512)
+    bias_g = gi.bf16_round(rng.uniform(-1, 1, (P, nt, 4)))
+    bias_d = gi.bf16_round(rng.uniform(-1, 1, (1, H)))
+    inter = (rng.standard_normal((128, nt, R, 4)) * 0.5).astype(np.float32)
+    if I < 512:
+        inter[I // 4:] = 0
+    return dict(H=H, I=I, R=R, gw=mx._as_bytes_x4(gw[0]), gs=gs[0], dw=mx._as_bytes_x4(dw[0]), ds=ds[0],
+                hidden=hidden, bias_g=bias_g, bias_d=bias_d, inter=inter, rows=(c1, s1, c2, s2))
+
+
+@pytest.mark.parametrize("I", [256, 1024])
+def test_projection_goldens_match_reference(I, mx_gold):
+    """``_gate_up_proj_golden_mx`` / ``_down_proj_golden_mx`` (test_mlp_common.py:550-682) and the src torch
+    references ``gate_up_proj_mxfp4_torch_ref`` / ``down_proj_mxfp4_torch_ref`` (mlp_proj_mxfp4_torch.py:52-187)."""
+    p = _projection_inputs(I)
+    gate = moe.ref_layout_gate_or_up(p["hidden"], p["gw"][:, 0], p["gs"][:, 0], p["bias_g"], p["H"], I)
+    assert _rel(gate, mx_gold[f"proj/i{I}/gate_test_golden"]) <= 1e-6
+    assert _rel(gate, mx_gold[f"proj/i{I}/gate_src_ref"]) <= 1e-6
+    down = moe.ref_layout_down(p["inter"], p["dw"], p["ds"], p["bias_d"], p["H"], I)
+    assert _rel(down, mx_gold[f"proj/i{I}/down_test_golden"]) <= 1e-6
+    assert _rel(down, mx_gold[f"proj/i{I}/down_src_ref"]) <= 1e-6
+    # ... and the plain-rows form the CUDA kernels are compared with gives the same gate values
+    c1, s1, c2, s2 = p["rows"]
+    H = p["H"]
+    ew = moe.ExpertWeights(c1.reshape(1, 2, I, H), s1.reshape(1, 2, I, H // 32), c2.reshape(1, H, I),
+                           s2.reshape(1, H, I // 32), 0)
+    xq, xs = mx.quantize_mx_rows(p["hidden"][:, mx.hidden_packed_order(H)])
+    g_rows = mx.dequantize_mx_rows(xq, xs) @ ew.w1[0].T       # [R, I] in packed I order, no bias
+    ref = mx_gold[f"proj/i{I}/gate_test_golden"] - np.pad(p["bias_g"], ((0, 128 - p["bias_g"].shape[0]), (0, 0), (0, 0)))[:, :, None, :]
+    nt = ref.shape[1]
+    P = 128 if I > 512 else I // 4
+    ref_rows = ref[:P].transpose(2, 1, 0, 3).reshape(p["R"], nt * P * 4)  # [R, (tile, p, q)] = packed I order
+    assert _rel(g_rows, ref_rows) <= 1e-5
+
+
+@pytest.mark.parametrize("name", list(gi.MX_LAYER_CASES))
+def test_block_assignment_matches_reference_generator(name, mx_gold):
+    """``generate_token_position_to_id_and_experts`` (test_moe_cte_common.py:199-264) run on the case's routing:
+    token_position_to_id, block_to_expert and the MX ``conditions`` vector, bit for bit."""
+    c = gi.MX_LAYER_CASES[name]
+    _, mask, _ = gi.mx_layer_routing(name)
+    N = routing.get_n_blocks(c["T"], c["K"], c["E"], c["B"])
+    tpi, b2e, cond, _ = routing.group_tokens(mask, c["B"], N, skip_token=c["skip_token"], mx_conditions=True)
+    assert np.array_equal(tpi, mx_gold[f"grouping/{name}/tpi"])
+    assert np.array_equal(b2e, mx_gold[f"grouping/{name}/block_to_expert"])
+    assert np.array_equal(cond, mx_gold[f"grouping/{name}/conditions"])
+
+
+_ACT = {"silu": moe.SILU, "swish": moe.SWISH}
+
+
+def _clamps(c):
+    g_hi, g_lo, u_hi, u_lo = c
+    return (g_lo, g_hi), (u_lo, u_hi)
+
+
+@pytest.mark.parametrize("name", list(gi.MX_DECODE_CASES))
+def test_decode_oracle_matches_reference_moe_tkg_mx_ref(name, mx_gold):
+    """``_moe_tkg_mx_ref`` (core/moe/moe_tkg/moe_tkg_torch.py:299-442): selective and all-expert, bias, Swish,
+    one-sided gate clamp.  Same quantised operands; only fp32 summation order differs."""
+    d = gi.mx_decode_inputs(name)
+    gc, uc = _clamps(d["clamps"])
+    out = moe.moe_tkg_rows(d["hidden"], d["aff"], d["expert_index"], d["w1_codes"], d["w1_scales"], d["w2_codes"],
+                           d["w2_scales"], d["bias_gu"], d["bias_d"], _ACT[d["act"]], gc, uc,
+                           h_order=mx.hidden_packed_order(d["H"]), round_inter_bf16=False,
+                           is_all_expert=d["all_expert"])
+    assert _rel(out, mx_gold[f"decode/{name}/out"]) <= 1e-5
+
+
+@pytest.mark.parametrize("name", list(gi.MX_LAYER_CASES))
+def test_prefill_oracle_matches_reference_blockwise_golden(name, mx_gold):
+    """``generate_blockwise_numpy_golden`` (test/integration/nkilib/core/moe/moe_cte/test_utils.py:474-735) with
+    the arguments ``golden_moe_bwmm_mx_cte`` passes.  The reference's own bar for this output is 5e-2 of the
+    output range (test_moe_bwmm_mx_cte.py:287-288); the restatement differs only in summation order and in
+    summing a token's rows in fp32 before one bf16 rounding (the golden adds bf16 to bf16 block by block)."""
+    c = gi.MX_LAYER_CASES[name]
+    inp = gi.mx_layer_inputs(name)
+    ref = torch.from_numpy(mx_gold[f"layer/{name}/out_bf16_bits"].view(np.int16)).view(torch.bfloat16).float().numpy()
+    gc, uc = _clamps(c["clamps"])
+    kw = dict(bias_gu=inp["bias_gu"], bias_d=inp["bias_d"], act=_ACT[c["act"]], gate_clamp=gc, up_clamp=uc,
+              h_order=mx.hidden_packed_order(c["H"]), round_inter_bf16=False)
+    if c["sample"] is None:
+        out = moe.moe_cte_rows(inp["hidden"], inp["aff"], inp["w1_codes"], inp["w1_scales"], inp["w2_codes"],
+                               inp["w2_scales"], mx_gold[f"grouping/{name}/tpi"],
+                               mx_gold[f"grouping/{name}/block_to_expert"], c["B"],
+                               mx_gold[f"grouping/{name}/conditions"] if c["dynamic"] else None, **kw)[:c["T"]]
+    else:
+        rows = gi.sample_rows(name, c["T"], c["sample"])
+        out = moe.moe_cte_tokens(rows, inp["hidden"], inp["aff"], inp["w1_codes"], inp["w1_scales"], inp["w2_codes"],
+                                 inp["w2_scales"], inp["expert_index"], **kw)
+    assert out.shape == ref.shape
+    assert _rel(gi.bf16_round(out), ref) <= 8e-3  # two bf16 steps at the largest output
