@@ -145,9 +145,14 @@ int b200moe_group_tokens(const void* routing, int routing_mode, int routing_dtyp
  * that loads it until the process exits), so the problem must satisfy
  * b200moe_group_tokens_workspace_bytes(T, E) <= b200moe_group_tokens_static_max_bytes();
  * larger problems are rejected with B200MOE_ERR_WORKSPACE.  Neither the call nor
- * anything it runs allocates or frees memory.  The first call on each device looks
- * up the array's device address (with that device current); make that first call
- * outside any stream capture.  All calls share the one array: nothing in it needs
+ * anything it runs allocates or frees memory -- from the second call on a device
+ * onwards.  The first call on each device looks up the array's device address (with
+ * that device current), and with CUDA's lazy module loading that lookup or the first
+ * launch may make the driver load the library's code, which allocates.  So make one
+ * warm-up call per device at start-up: before the window in which allocation is
+ * forbidden, outside any stream capture, and from one thread (the address is cached
+ * per device ordinal without a lock; the library assumes the one primary context per
+ * device that the CUDA runtime uses).  All calls share the one array: nothing in it needs
  * clearing between calls (each call overwrites what it reads), but two calls that
  * overlap on the GPU -- different streams without an ordering between them -- race. */
 size_t b200moe_group_tokens_static_max_bytes(void);
@@ -179,7 +184,9 @@ int b200moe_gather_quantize_mxfp8(const void* hidden_bf16, int hidden_rows, int 
 /* The same quantisation driven by the inverse map (inverse_map[t*K + k] = position of token t's k-th expert, or
  * negative; what b200moe_group_tokens writes): every token row is read and quantised once and stored to its K
  * positions, so hidden crosses HBM once instead of K times.  Positions that no (token, k) pair maps to are NOT
- * written -- the contractions never let such rows reach a result -- and tile_flags is filled as above.
+ * written -- the contractions never let such rows reach a result -- and tile_flags is filled as above.  K is
+ * the width of the map, not a top-k limit: the [T, E] table of b200moe_build_position_table is accepted as well
+ * (K = E, negative entries skipped), which is how moe_cte reads hidden once with only token_position_to_id given.
  * No reference counterpart (the reference gathers per block, core/moe/moe_cte/moe_cte_mx_utils.py:456-945). */
 int b200moe_scatter_quantize_mxfp8(const void* hidden_bf16, int T, int H, const int32_t* inverse_map, int K,
                                    int64_t n_pos, int h_packed_order, uint8_t* codes, uint8_t* sf_atoms,

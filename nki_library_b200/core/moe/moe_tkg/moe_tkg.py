@@ -58,6 +58,7 @@ def moe_tkg(
     token through the local experts ``[E_L * rank_id, E_L * (rank_id + 1))`` with
     the affinity columns sliced (and optionally masked by ``expert_index``) the
     way ``mask_expert_affinities`` does (core/moe/moe_tkg/moe_tkg_affinity_masking.py:31-117).
+    ``is_all_expert_dynamic`` computes, per local expert, only the tokens whose masked affinity is non-zero.
     Weights are the reference's x4-packed MXFP8 tensors with their scales, or a
     prepared :class:`~nki_library_b200.weights.ExpertWeights` passed as
     ``expert_gate_up_weights``.  Only the MX path exists; inputs that select the
@@ -117,29 +118,44 @@ def moe_tkg(
                             _check_status)
     else:
         E = expert_affinities.shape[1]
-        rank = 0
         if post_scale:
             A(rank_id is not None, f"{_PREFIX} rank_id is required for all-expert mode with affinity scaling")
-        if rank_id is not None:
-            rank = int(rank_id.reshape(-1)[0].item())
-        n_sub = math.ceil(T / _BLOCK)
-        Tpad = n_sub * _BLOCK
-        ids = torch.full((Tpad,), -1, dtype=torch.int32, device=dev)
-        ids[:T] = torch.arange(T, dtype=torch.int32, device=dev)
-        tpi = ids.repeat(E_L)
-        b2e = torch.arange(E_L, dtype=torch.int32, device=dev).repeat_interleave(n_sub)
-        table = (torch.arange(E_L, dtype=torch.int32, device=dev)[None, :] * Tpad +
-                 torch.arange(T, dtype=torch.int32, device=dev)[:, None]).contiguous()
+        # local expert columns [E_L * rank_id, E_L * (rank_id + 1)), taken with a device-side index so that the
+        # rank tensor never has to travel to the host (moe_tkg_affinity_masking.py:31-117)
         aff = None
-        if post_scale:
-            aff = expert_affinities[:, rank * E_L:(rank + 1) * E_L].float()
+        if post_scale or is_all_expert_dynamic:
+            cols = torch.arange(E_L, dtype=torch.int64, device=dev)
+            if rank_id is not None:
+                cols = cols + rank_id.reshape(-1)[:1].to(torch.int64) * E_L
+            aff = expert_affinities.float().index_select(1, cols)
             if mask_unselected_experts:
-                sel = torch.zeros((T, E), dtype=torch.bool, device=dev)
-                sel.scatter_(1, expert_index.to(torch.int64), True)
-                aff = aff * sel[:, rank * E_L:(rank + 1) * E_L]
+                sel = torch.zeros((T, E), dtype=torch.float32, device=dev)
+                sel.scatter_(1, expert_index.to(torch.int64), 1.0)
+                aff = aff * sel.index_select(1, cols)
             aff = aff.contiguous()
-        pipeline.run_blocks(hidden, T, weights, tpi, b2e, None, _BLOCK, aff, table, out, activation_fn.value,
-                            clamps[0], clamps[1], _impl, _check_status)
+        if is_all_expert_dynamic:
+            # dynamic control flow: per expert only the tokens routed to it (non-zero masked affinity) are
+            # gathered into blocks and computed (all_expert_mx_impl.py:276-350); the block bookkeeping is the
+            # prefill grouping on the masked affinities, and the blocks of experts nobody chose never run
+            A(block_size > 0 and T % block_size == 0, f"{_PREFIX} block_size must evenly divide T")
+            n_blocks = E_L * math.ceil(T / _BLOCK)
+            g = moe_group_tokens(aff, E_L, _BLOCK, n_blocks, skip_token=True, want_inverse=False)
+            tpi, b2e, cond = g["token_position_to_id"], g["block_to_expert"], g["conditions"]
+            table = torch.empty((T, E_L), dtype=torch.int32, device=dev)
+            _lib.call("b200moe_build_position_table", _lib.ptr(tpi), _lib.ptr(b2e), _lib.ptr(cond), n_blocks, _BLOCK,
+                      T, E_L, _lib.ptr(table), _lib.stream_ptr())
+        else:
+            n_sub = math.ceil(T / _BLOCK)
+            Tpad = n_sub * _BLOCK
+            ids = torch.full((Tpad,), -1, dtype=torch.int32, device=dev)
+            ids[:T] = torch.arange(T, dtype=torch.int32, device=dev)
+            tpi = ids.repeat(E_L)
+            b2e = torch.arange(E_L, dtype=torch.int32, device=dev).repeat_interleave(n_sub)
+            cond = None
+            table = (torch.arange(E_L, dtype=torch.int32, device=dev)[None, :] * Tpad +
+                     torch.arange(T, dtype=torch.int32, device=dev)[:, None]).contiguous()
+        pipeline.run_blocks(hidden, T, weights, tpi, b2e, cond, _BLOCK, aff if post_scale else None, table, out,
+                            activation_fn.value, clamps[0], clamps[1], _impl, _check_status)
     if output_dtype is not None and output_dtype != torch.bfloat16:
         return out.to(output_dtype)
     return out

@@ -90,15 +90,12 @@ __global__ void __launch_bounds__(256) scatter_quantize_kernel(const __nv_bfloat
   const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (t >= T) return;
   const int64_t k_atoms = (H + 127) >> 7;
-  int my_pos = -1;
-  if (lane < K) {
-    my_pos = inverse_map[static_cast<int64_t>(t) * K + lane];
-    if (my_pos < 0 || my_pos >= n_pos) my_pos = -1;
-    else if (tile_flags != nullptr && blockIdx.y == 0) atomicMax(&tile_flags[my_pos >> 7], (my_pos & 127) + 1);
-  }
-  int pos[8];
-#pragma unroll
-  for (int k = 0; k < 8; ++k) pos[k] = __shfl_sync(0xffffffffu, my_pos, k);
+  const int32_t* my_map = inverse_map + static_cast<int64_t>(t) * K;
+  if (tile_flags != nullptr && blockIdx.y == 0)
+    for (int k = lane; k < K; k += 32) {
+      const int p = my_map[k];
+      if (p >= 0 && p < n_pos) atomicMax(&tile_flags[p >> 7], (p & 127) + 1);
+    }
   const __nv_bfloat16* row = hidden + static_cast<int64_t>(t) * H;
   const int passes = (H + 255) >> 8;
   const int q = lane & 3, blk = lane >> 2;
@@ -155,11 +152,18 @@ __global__ void __launch_bounds__(256) scatter_quantize_kernel(const __nv_bfloat
       uint32_t cell = col < H ? static_cast<uint32_t>(mx_block_scale_byte(mx)) << (8 * (blk & 3)) : 0u;
       cell |= __shfl_xor_sync(0xffffffffu, cell, 4);
       cell |= __shfl_xor_sync(0xffffffffu, cell, 8);
-      if (col < H) {
+      // the token's positions, eight at a time (a top-k list is one round; a [T, E] position table has E / 8)
+      for (int k0 = 0; k0 < K; k0 += 8) {
+        int my_pos = -1;
+        if (lane < 8 && k0 + lane < K) {
+          my_pos = my_map[k0 + lane];
+          if (my_pos >= n_pos) my_pos = -1;
+        }
+        if (__ballot_sync(0xffffffffu, my_pos >= 0) == 0u) continue;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          if (k >= K || pos[k] < 0) continue;
-          const int64_t p = pos[k];
+          const int64_t p = __shfl_sync(0xffffffffu, my_pos, k);
+          if (p < 0 || col >= H) continue;
           *reinterpret_cast<uint2*>(codes + p * H + col) = make_uint2(w0, w1);
           if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sf + sf_atom_offset(p, col >> 5, k_atoms)) = cell;
         }
@@ -354,7 +358,7 @@ extern "C" int b200moe_scatter_quantize_mxfp8(const void* hidden_bf16, int T, in
                   "scatter_quantize: null pointer argument");
   B200MOE_REQUIRE(T > 0 && H > 0 && H % 32 == 0 && n_pos > 0, B200MOE_ERR_INVALID,
                   "scatter_quantize: T, n_pos must be positive and H a positive multiple of 32 (H = %d)", H);
-  B200MOE_REQUIRE(K >= 1 && K <= 8, B200MOE_ERR_INVALID, "scatter_quantize: K must be in [1, 8], got %d", K);
+  B200MOE_REQUIRE(K >= 1 && K <= 8192, B200MOE_ERR_INVALID, "scatter_quantize: K must be in [1, 8192], got %d", K);
   B200MOE_REQUIRE(!h_packed_order || H % 512 == 0, B200MOE_ERR_INVALID,
                   "scatter_quantize: the packed hidden order needs H %% 512 == 0, got %d", H);
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -58,7 +58,8 @@ def run_blocks(hidden: torch.Tensor, hidden_rows: int, weights: ExpertWeights, t
                gate_clamp=(None, None), up_clamp=(None, None), impl: int = 0, check_status: bool = False,
                workspace: Optional[BlockWorkspace] = None, aff_per_row: bool = False,
                timers: Optional[dict] = None) -> torch.Tensor:
-    """Run the four kernels.  ``table [rows_out, n_cand]`` lists, per output row, the positions to sum.
+    """Run the four kernels.  ``table [rows_out, n_cand]`` lists, per output row (= token), the positions that
+    hold it (negative = none): the quantiser stores the token's row there and the combine sums those rows.
 
     ``hidden`` bf16 ``[>= hidden_rows, H]``; ids outside ``[0, hidden_rows)`` in
     ``token_position_to_id`` are pads.  ``affinities`` is the flat table addressed
@@ -82,8 +83,11 @@ def run_blocks(hidden: torch.Tensor, hidden_rows: int, weights: ExpertWeights, t
             timers.setdefault(name, []).append(ev)
 
     mark("t0")
-    _lib.call("b200moe_gather_quantize_mxfp8", _lib.ptr(hidden), hidden_rows, H, _lib.ptr(token_position_to_id), n_pos,
-              int(weights.h_packed_order), _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(ws.tile_flags), st)
+    # token-major quantise: ``table`` lists every token's positions, so a hidden row is read and quantised once
+    # and stored to each of them (a position-major gather would read it once per expert the token goes to)
+    _lib.call("b200moe_scatter_quantize_mxfp8", _lib.ptr(hidden), min(hidden_rows, table.shape[0]), H, _lib.ptr(table),
+              table.shape[1], n_pos, int(weights.h_packed_order), _lib.ptr(ws.xq), _lib.ptr(ws.x_sf),
+              _lib.ptr(ws.tile_flags), st)
     mark("t1")
     _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(ws.xq), _lib.ptr(ws.x_sf), _lib.ptr(weights.w1),
               _lib.ptr(weights.w1_sf), weights.w_format, _lib.ptr(weights.bias_gu), _lib.ptr(block_to_expert), _lib.ptr(conditions),

@@ -296,19 +296,26 @@ def decode_fixture(ref: Reference, out: dict) -> None:
         print(f"  decode {name}: {time.time() - t0:.1f} s", flush=True)
 
 
-def main(ref_root: str) -> None:
+PARTS = {"quantize": quantize_fixture, "matmul": matmul_fixture, "proj": projection_fixture,
+         "grouping": grouping_fixture, "decode": decode_fixture, "layer": layer_fixture}
+
+
+def main(ref_root: str, only=None) -> None:
+    """``only``: names of PARTS to regenerate, keeping the other arrays of an existing fixture file
+    (the prefill part alone takes about five minutes)."""
     ref = Reference(ref_root)
+    path = os.path.join(HERE, "mx_ref.npz")
     out: dict = {}
-    quantize_fixture(ref, out)
-    matmul_fixture(ref, out)
-    projection_fixture(ref, out)
-    grouping_fixture(ref, out)
-    decode_fixture(ref, out)
-    layer_fixture(ref, out)
+    if only:
+        with np.load(path) as old:
+            out = {k: old[k] for k in old.files if k.split("/")[0] not in only}
+    for name, fn in PARTS.items():
+        if not only or name in only:
+            fn(ref, out)
     out["meta/static_cast_rounding"] = np.array(ref.dt.ROUNDING)
-    np.savez_compressed(os.path.join(HERE, "mx_ref.npz"), **out)
-    print("wrote", os.path.join(HERE, "mx_ref.npz"))
+    np.savez_compressed(path, **out)
+    print("wrote", path)
 
 
 if __name__ == "__main__":
-    main(sys.argv[1])
+    main(sys.argv[1], set(sys.argv[2].split(",")) if len(sys.argv) > 2 else None)

@@ -145,6 +145,7 @@ def bf16_round(a):
 
 def mx_quantize_input(P=128, F=512, seed=7):
     """``[P, F]`` fp32 with 8 x 4 blocks of very different magnitude and the awkward cases in known blocks:
+    (every value is bf16-exact, so the CUDA quantiser, which takes bf16 rows, can be fed the same data)
     an all-zero block, one with a single subnormal, exact rounding ties of the e4m3 grid, block maxima whose
     scaled value exceeds 448 and must clip, negative zero, and bf16-valued gaussian data elsewhere."""
     rng = np.random.default_rng(seed)
@@ -153,7 +154,7 @@ def mx_quantize_input(P=128, F=512, seed=7):
     x = bf16_round(x * np.repeat(np.repeat(mag, 8, 0), 4, 1))
     x[0:8, 0:4] = 0.0
     x[0:8, 4:8] = 0.0
-    x[3, 5] = np.float32(1e-41)                       # fp32 subnormal: biased exponent 0
+    x[3, 5] = np.float32(2.0 ** -133)                 # smallest bf16 subnormal: biased exponent 0
     x[8:16, 0:4] = np.float32(1.0625)                 # tie between 1.0 and 1.125 -> even (1.0)
     x[8:16, 4:8] = np.float32(1.1875)                 # tie between 1.125 and 1.25 -> even (1.25)
     x[8, 4] = np.float32(1.5)
@@ -266,6 +267,8 @@ MX_DECODE_CASES = {
     # name: (T, H, I, E, K, act, all_expert)
     "sel_t8_h512_i256_e4_k2_swish": (8, 512, 256, 4, 2, "swish", False),
     "all_t16_h512_i256_e4_silu": (16, 512, 256, 4, 2, "silu", True),
+    "sel_t8_h512_i256_e4_k2_gelu": (8, 512, 256, 4, 2, "gelu", False),
+    "sel_t8_h512_i256_e4_k2_gelu_tanh": (8, 512, 256, 4, 2, "gelu_tanh", False),
     # test_moe_tkg.py "=== MXFP8" selective row at fewer experts (E = 128 there): T=2, H=3072, I=1536, top-8
     "sel_t2_h3072_i1536_e16_k8_silu": (2, 3072, 1536, 16, 8, "silu", False),
 }

@@ -412,3 +412,48 @@ def test_host_pipeline_matches_direct_forward():
         ref = layer.forward(a.to(dev)).clone()
         torch.cuda.synchronize()
         assert torch.equal(b, ref.cpu())
+
+
+def test_moe_tkg_all_expert_with_128_local_experts():
+    """All-expert decode with more local experts than the combine once held per token (64): every one of the
+    128 experts contributes to every token (the reference's all-expert mode goes to E = 128, test_moe_tkg.py:292-294)."""
+    import nki_library_b200 as m
+    T, H, I, E, K = 4, 512, 128, 128, 4
+    hidden, idx, aff, w_np, bgu, bd = _cte_case(T, H, I, E, K, 128, 91, True, moe.SILU, None)
+    rng = np.random.default_rng(92)
+    aff = bf16_values(rng.random((T, E)).astype(np.float32))  # dense: no expert is masked out
+    weights = _prep(m, w_np, bgu, bd)
+    out = m.moe_tkg(torch.from_numpy(hidden).to(torch.bfloat16).cuda(), weights, None, torch.from_numpy(aff).cuda(),
+                    torch.from_numpy(idx).cuda(), True, rank_id=torch.zeros((1, 1), dtype=torch.int32, device="cuda"),
+                    expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.POST_SCALE, _check_status=True)
+    ref = moe.moe_tkg_rows(hidden, aff, None, *w_np, bias_gu=bgu, bias_d=bd, is_all_expert=True)
+    assert max_rel(out.float().cpu().numpy(), bf16_values(ref)) <= TOL
+    # experts 64..127 alone must move the result: a combine that dropped them would return this partial sum
+    part = moe.moe_tkg_rows(hidden, aff * (np.arange(E) < 64), None, *w_np, bias_gu=bgu, bias_d=bd, is_all_expert=True)
+    assert max_rel(bf16_values(part), bf16_values(ref)) > 10 * TOL
+
+
+@pytest.mark.parametrize("dynamic", [False, True])
+@pytest.mark.parametrize("rank", [0, 1])
+def test_moe_tkg_all_expert_rank_slice(rank, dynamic):
+    """Expert-parallel slice of the all-expert mode: this rank holds experts [rank * E_L, (rank + 1) * E_L) of E,
+    affinity columns are sliced by ``rank_id`` and masked by ``expert_index`` (core/moe/moe_tkg/moe_tkg.py:100-101,
+    178-198, moe_tkg_affinity_masking.py:31-117); summing the ranks' outputs gives the full layer.  ``dynamic`` runs
+    only the tokens routed to each expert (core/moe/moe_tkg/all_expert_mx_impl.py:276-350): same result."""
+    import nki_library_b200 as m
+    T, H, I, E, K, G = 96, 512, 256, 8, 2, 2
+    E_L = E // G
+    hidden, idx, aff, w_np, bgu, bd = _cte_case(T, H, I, E, K, 128, 93, True, moe.SILU, None)
+    rng = np.random.default_rng(94)
+    aff = bf16_values(rng.random((T, E)).astype(np.float32))  # dense affinities: the mask has to come from expert_index
+    sl = slice(rank * E_L, (rank + 1) * E_L)
+    local = tuple(a[sl] for a in w_np)
+    weights = _prep(m, local, bgu[sl], bd[sl])
+    out = m.moe_tkg(torch.from_numpy(hidden).to(torch.bfloat16).cuda(), weights, None, torch.from_numpy(aff).cuda(),
+                    torch.from_numpy(idx).cuda(), True, rank_id=torch.full((1, 1), rank, dtype=torch.int32, device="cuda"),
+                    mask_unselected_experts=True, expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.POST_SCALE,
+                    is_all_expert_dynamic=dynamic, block_size=32 if dynamic else None, _check_status=True)
+    masked = aff * routing.mask_from_index(idx, E)
+    ref = moe.moe_tkg_rows(hidden, masked, None, *local, bias_gu=bgu[sl], bias_d=bd[sl], is_all_expert=True,
+                           expert_offset=rank * E_L)
+    assert max_rel(out.float().cpu().numpy(), bf16_values(ref)) <= TOL

@@ -294,7 +294,7 @@ def test_block_assignment_matches_reference_generator(name, mx_gold):
     assert np.array_equal(cond, mx_gold[f"grouping/{name}/conditions"])
 
 
-_ACT = {"silu": moe.SILU, "swish": moe.SWISH}
+_ACT = {"silu": moe.SILU, "swish": moe.SWISH, "gelu": moe.GELU, "gelu_tanh": moe.GELU_TANH}
 
 
 def _clamps(c):
