@@ -5,11 +5,21 @@
 A step is one pass of the MoE layer (router top-K -> token grouping -> MXFP8
 activation quantisation -> grouped gate/up contraction + SwiGLU -> grouped down
 contraction + affinity -> combine) over one batch of seeded synthetic tokens.
-Rank 0 prints one JSON line.  ``value`` is tokens/s with inputs resident in HBM;
-``e2e`` is the same metric through the public API with host buffers (pinned
-host -> device copy of the tokens and device -> host copy of the result inside
-the timed region).  ``--impl reference`` times the reference's CPU algorithm
-(the oracle restatement) on this host's cores instead.
+Rank 0 prints one JSON line:
+
+* ``value``      tokens/s with inputs resident in HBM (the captured launch sequence replayed)
+* ``e2e``        the same through host buffers (pinned host -> device and device -> host copies timed)
+* ``api_path``   the same step through the drop-in entry points ``router_topk`` -> ``moe_group_tokens`` ->
+                 ``moe_cte`` (prefill) and ``router_topk`` -> ``moe_tkg`` (decode), eager, resident inputs
+* ``sustained``  the replay again for a few seconds (power-capped clocks), against the sustained peak
+* ``roofline``   the dominant kernel against the measured peak; ``kernel_ms`` every kernel's device time
+* ``decode`` / ``decode_mxfp4_weights`` / ``finegrained_prefill`` / ``ep_prefill``  the other single-GPU
+                 configurations, each with its own ``kernel_ms`` and roofline fraction
+* ``cpu_baseline``  the reference's CPU algorithm (the oracle restatement) timed on this host on a bounded
+                 sample of the same inputs; the same sample checks the GPU's rows (``parity_sample``)
+
+``--impl reference`` times only that CPU algorithm.  With ``--gpus N`` > 1 the experts are split over the ranks
+(expert parallelism, T tokens per rank) and the line adds ``ep_prefill_strong`` (32768 tokens in total).
 """
 
 from __future__ import annotations
@@ -32,15 +42,15 @@ WORKLOADS = {
     "mixtral_decode": dict(kind="decode", T=64, H=4096, I=14336, E=8, K=2, B=128, zipf=None),
     "finegrained_prefill": dict(kind="prefill", T=8192, H=7168, I=2048, E=256, K=8, B=128, zipf=1.2),
     "ep_prefill": dict(kind="prefill", T=32768, H=4096, I=1536, E=128, K=8, B=256, zipf=None),
+    "ep_prefill_zipf": dict(kind="prefill", T=32768, H=4096, I=1536, E=128, K=8, B=256, zipf=1.2),
     "tiny_prefill": dict(kind="prefill", T=256, H=512, I=1024, E=4, K=2, B=128, zipf=None),
 }
 
-
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
-# profiles/ (one capture per workload; null where none was taken).
-NCU_TRAFFIC_BYTES = {
-    "mixtral_prefill": (1.004123e9 + 118.779392e6) + (0.486658e9 + 10.018304e6),  # CTA-pair + left-over launch
-    "mixtral_decode": 971.416576e6 + 18.775808e6,
+# profiles/ (file named beside each figure; null where no capture of the current kernel exists).
+NCU_TRAFFIC = {
+    "mixtral_prefill": {"bytes": None, "from": None},
+    "mixtral_decode": {"bytes": None, "from": None},
 }
 
 
@@ -156,7 +166,9 @@ def library_mxfp8_tflops(M, N, K):
         return None
 
 
-def make_inputs(cfg, device, seed):
+def make_inputs(cfg, seed):
+    """Seeded tokens ~N(0,1) bf16 [T,H], router weight ~N(0,0.02) bf16 [H,E], and the Zipf logit bias if the
+    workload has one (-s * ln(rank) over a seeded permutation of the experts)."""
     import torch
     g = torch.Generator()
     g.manual_seed(1234 + seed)
@@ -170,83 +182,169 @@ def make_inputs(cfg, device, seed):
     return hidden, router_w, bias
 
 
-# ------------------------------------------------------------------ CPU legs (oracle)
-def cpu_sample(cfg, steps, warmup, threads, budget_s=None):
-    """Time the oracle restatement of the reference's per-block golden loop on a bounded sample.
+# ------------------------------------------------------------------ CPU legs (the oracle: reference algorithm, CPU)
+def cpu_route(cfg, hidden, router_w, bias):
+    """Router top-K and block assignment of the whole batch on the CPU, timed (the oracle's restatements of
+    router_topk_torch_ref and of the find_nonzero_indices -> cumsum -> indexed_flatten chain)."""
+    from oracle import routing
+    T, E, K, B = cfg["T"], cfg["E"], cfg["K"], cfg["B"]
+    t0 = time.perf_counter()
+    _, idx, aff = routing.router_topk(hidden.float(), router_w.float(), None if bias is None else bias.float(), K,
+                                      routing.SOFTMAX, True, True)
+    t1 = time.perf_counter()
+    idx = idx.numpy().astype("int32")
+    N = routing.get_n_blocks(T, K, E, B)
+    routing.group_tokens(routing.mask_from_index(idx, E), B, N)
+    t2 = time.perf_counter()
+    return idx, aff.numpy(), {"router_topk_s": t1 - t0, "group_tokens_s": t2 - t1}
 
-    Sample: ``n_rows`` token-expert rows of one expert at the workload's H and I
-    (one weight dequantisation + the block recipe), which is how the reference's
-    golden walks blocks.  tokens/s = rows / K / time.
+
+def cpu_synthetic_expert(cfg, e):
+    """Seeded N(0, 0.02) weights of one expert quantised on the CPU (used when no GPU weights exist to read back)."""
+    import numpy as np
+
+    from oracle import mx
+    H, I = cfg["H"], cfg["I"]
+    rng = np.random.default_rng(7000 + e)
+    c1, s1 = mx.quantize_mx_rows((rng.standard_normal((2 * I, H), dtype=np.float32) * np.float32(0.02)))
+    c2, s2 = mx.quantize_mx_rows((rng.standard_normal((H, I), dtype=np.float32) * np.float32(0.02)))
+    return c1.reshape(1, 2, I, H), s1.reshape(1, 2, I, H // 32), c2.reshape(1, H, I), s2.reshape(1, H, I // 32)
+
+
+def cpu_block_sample(cfg, hidden_np, idx, aff, expert_weights, steps, warmup, threads, n_experts=4,
+                     blocks_per_expert=2, budget_s=None):
+    """The oracle's per-block recipe on a bounded sample: for the first ``n_experts`` experts that received tokens,
+    dequantise the expert's weights and push its first ``blocks_per_expert`` blocks of B token rows through
+    quantise -> gate/up -> SwiGLU -> re-quantise -> down -> x affinity (what the reference's golden does per block).
+
+    Returns the seconds per step, the rows covered and the rows' results (for the parity check).
     """
     import numpy as np
     import torch
 
-    from oracle import moe, mx
+    from oracle import moe
     torch.set_num_threads(threads)
-    H, I, K = cfg["H"], cfg["I"], cfg["K"]
-    n_rows = min(cfg["T"] * K // max(cfg["E"], 1), 512) if cfg["kind"] == "prefill" else max(cfg["T"] * K // cfg["E"], 1)
-    n_rows = max(n_rows, 1)
-    rng = np.random.default_rng(0)
-    c1 = rng.integers(0, 0x7E, size=(1, 2, I, H), dtype=np.uint8)
-    s1 = rng.integers(110, 120, size=(1, 2, I, H // 32), dtype=np.uint8)
-    c2 = rng.integers(0, 0x7E, size=(1, H, I), dtype=np.uint8)
-    s2 = rng.integers(110, 120, size=(1, H, I // 32), dtype=np.uint8)
-    x = torch.randn(n_rows, H).to(torch.bfloat16).float().numpy()
-    times = []
+    B, E = cfg["B"], cfg["E"]
+    plan = []
+    for e in range(E):
+        tok = np.flatnonzero((idx == e).any(axis=1))
+        if tok.size:
+            plan.append((e, tok[: blocks_per_expert * B]))
+        if len(plan) == n_experts:
+            break
+    weights = {e: expert_weights(e) for e, _ in plan}
+    times, results = [], None
     for it in range(warmup + steps):
         t0 = time.perf_counter()
-        ew = moe.ExpertWeights(c1, s1, c2, s2, 0)
-        y = moe.expert_mlp_rows(x, ew)
+        res = []
+        for e, tok in plan:
+            ew = moe.ExpertWeights(*weights[e], 0)
+            for b0 in range(0, tok.size, B):
+                t = tok[b0:b0 + B]
+                y = moe.expert_mlp_rows(hidden_np[t], ew) * aff[t, e][:, None]
+                res.append((e, t, y))
+            del ew
         dt = time.perf_counter() - t0
         if it >= warmup:
             times.append(dt)
-        del ew, y
+        results = res
         if budget_s is not None and times and sum(times) + times[-1] > budget_s:
-            break  # the next step would overrun the wall-clock budget of this leg
-    t = sum(times) / len(times)
-    return dict(value=n_rows / K / t, seconds_per_step=t, rows=n_rows, steps=len(times),
-                sample=f"{n_rows} token-expert rows through one expert (dequantise weights + quantise/gate-up/SwiGLU/"
-                       f"re-quantise/down) at H={H}, I={I}; tokens/s = rows/K/time")
+            break
+    rows = sum(t.size for _, t in plan)
+    return dict(seconds_per_step=sum(times) / len(times), steps=len(times), rows=rows,
+                blocks=sum(-(-t.size // B) for _, t in plan), experts=len(plan), results=results)
+
+
+def cpu_baseline_line(cfg, sample, route_t, threads, kind_note):
+    """tokens/s of the whole layer extrapolated from the sample: T*K token-expert rows at the sample's rate
+    (weight dequantisation included in proportion), plus the routing that was timed in full."""
+    T, K = cfg["T"], cfg["K"]
+    layer_s = sample["seconds_per_step"] * (T * K / sample["rows"]) + sum(route_t.values())
+    return {"value": T / layer_s, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "extrapolated": True, "seconds_per_sample": sample["seconds_per_step"], "routing_seconds": route_t,
+            "sample": f"extrapolated from {sample['blocks']} blocks of up to {cfg['B']} token rows over "
+                      f"{sample['experts']} experts ({sample['rows']} of {T * K} token-expert rows: dequantise the "
+                      f"expert's weights, quantise/gate-up/SwiGLU/re-quantise/down per block) at H={cfg['H']}, "
+                      f"I={cfg['I']}; router top-K and block assignment of all {T} tokens timed in full; {kind_note}"}
+
+
+def cpu_decode_full(cfg, hidden_np, idx, aff, expert_weights, steps, warmup, threads):
+    """The decode layer in full on the CPU: every expert that a token chose, dequantised and applied."""
+    import numpy as np
+    import torch
+
+    from oracle import moe
+    torch.set_num_threads(threads)
+    E = cfg["E"]
+    active = [e for e in range(E) if (idx == e).any()]
+    weights = {e: expert_weights(e) for e in active}
+    times, out = [], None
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        out = np.zeros_like(hidden_np)
+        for e in active:
+            tok = np.flatnonzero((idx == e).any(axis=1))
+            ew = moe.ExpertWeights(*weights[e], 0)
+            out[tok] += moe.expert_mlp_rows(hidden_np[tok], ew) * aff[tok, e][:, None]
+            del ew
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    return dict(seconds_per_step=sum(times) / len(times), steps=len(times), out=out,
+                sample=f"the whole decode step: {len(active)} active experts dequantised and applied to their tokens "
+                       f"(T={cfg['T']}, H={cfg['H']}, I={cfg['I']})")
 
 
 def run_reference(args, cfg, name):
+    """The reference's CPU algorithm alone (no GPU work): every step is the bounded sample of cpu_block_sample."""
     threads = os.cpu_count() or 1
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    # every step is the same bounded sample; run the K steps asked for unless that would take over ~2.5 minutes
-    warm = max(0, min(args.warmup, 2))
-    r = cpu_sample(cfg, max(1, args.steps), warm, threads, budget_s=150.0)
-    steps = r["steps"]
+    hidden, router_w, bias = make_inputs(cfg, 0)
+    idx, aff, route_t = cpu_route(cfg, hidden, router_w, bias)
+    hidden_np = hidden.float().numpy()
+    if cfg["kind"] == "decode":
+        s = cpu_decode_full(cfg, hidden_np, idx, aff, lambda e: cpu_synthetic_expert(cfg, e), max(1, args.steps),
+                            args.warmup, threads)
+        value, sec = cfg["T"] / (s["seconds_per_step"] + sum(route_t.values())), s["seconds_per_step"]
+        base = {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "extrapolated": False,
+                "sample": s["sample"]}
+    else:
+        s = cpu_block_sample(cfg, hidden_np, idx, aff, lambda e: cpu_synthetic_expert(cfg, e), max(1, args.steps),
+                             args.warmup, threads)
+        base = cpu_baseline_line(cfg, s, route_t, threads, "weights drawn and quantised on the CPU from the same "
+                                 "distribution as the GPU arm's")
+        value, sec = base["value"], s["seconds_per_step"]
     line = {
-        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": r["value"], "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": warm,
-        "ms_per_step": r["seconds_per_step"] * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "mxfp8_e4m3", "data": "synthetic", "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}},
-        "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": r["sample"]},
-        "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": s["steps"], "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8_e4m3", "data": "synthetic",
+        "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}},
+        "cpu_baseline": base,
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------ GPU leg
-def decode_leg(weights, peaks, device, w_format="e4m3"):
-    """Mixtral decode workload (T = 64 tokens, Mixtral-8x7B shapes) on the given expert weights: tokens/s and HBM fraction."""
-    import torch
+# ------------------------------------------------------------------ GPU legs
+def device_expert_rows(weights, e):
+    """One expert's device weights back on the host in the oracle's rows form (codes [1,2,I,H] / [1,H,I] + scales)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from moe_testlib import gate_up_dev_rows, sf_atoms_to_rows
+    n1, n2 = weights.w1_sf.numel() // weights.E, weights.w2_sf.numel() // weights.E
+    H, I = weights.H, weights.I
+    w1 = weights.w1[e].cpu().numpy()
+    w2 = weights.w2[e].cpu().numpy()
+    s1 = sf_atoms_to_rows(weights.w1_sf[e * n1:(e + 1) * n1].cpu().numpy(), 2 * I, H)
+    s2 = sf_atoms_to_rows(weights.w2_sf[e * n2:(e + 1) * n2].cpu().numpy(), H, I)
+    rows = gate_up_dev_rows(I)
+    c1 = np.stack([w1[rows[0]], w1[rows[1]]])[None]
+    sc1 = np.stack([s1[rows[0]], s1[rows[1]]])[None]
+    return c1, sc1, w2[None], s2[None]
 
-    from nki_library_b200.layer import MoELayer
-    cfg = WORKLOADS["mixtral_decode"]
-    T, H, E, K, B = cfg["T"], cfg["H"], cfg["E"], cfg["K"], cfg["B"]
-    hidden, router_w, _ = make_inputs(cfg, device, 99)
-    layer = MoELayer(router_w.to(device), weights, K, B, T)
-    x = hidden.to(device)
-    for _ in range(3):
-        layer.forward(x)
-    torch.cuda.synchronize()
-    layer.capture(x)
-    layer.replay()
-    steps = 100
+
+def time_replays(layer, steps):
+    import torch
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     s.record()
@@ -254,162 +352,381 @@ def decode_leg(weights, peaks, device, w_format="e4m3"):
         layer.replay()
     e.record()
     torch.cuda.synchronize()
-    ms = s.elapsed_time(e) / steps
-    if any(layer.device_status()):
-        return {"error": f"device status {layer.device_status()}"}
-    gbs = algorithmic_work(cfg, w_format)["decode_bytes"] / (ms * 1e-3) / 1e9
-    return {"workload": "mixtral_decode", "weight_format": w_format, "T": T, "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3),
-            "algorithmic_gb_per_s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
-            "steps": steps, "launch_mode": "cuda graph replay"}
+    return s.elapsed_time(e) / steps
 
 
-def run_ours(args, cfg, name):
+def roofline_block(cfg, name, per_kernel, ms_step, peaks, w_format, with_library=False):
+    work = algorithmic_work(cfg, w_format)
+    traffic = NCU_TRAFFIC.get(name, {"bytes": None, "from": None})
+    if cfg["kind"] == "prefill":
+        peak = 2.0 * peaks["bf16_tflops"]
+        achieved = work["gemm1_flops"] / (per_kernel["gemm1_swiglu"] * 1e-3) / 1e12
+        down = work["gemm2_flops"] / (per_kernel["gemm2_scale"] * 1e-3) / 1e12
+        layer = work["layer_flops"] / (ms_step * 1e-3) / 1e12
+        return {"bound": "tensor", "kernel": "grouped_mxfp8_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
+                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "frac_of_sustained_peak": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
+                "traffic": traffic["bytes"], "traffic_from": traffic["from"],
+                "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s): dense fp8/mxfp8 "
+                               f"issues at twice the bf16 rate; frac_of_sustained_peak uses 2 x the sustained figure "
+                               f"({peaks['bf16_tflops_sustained']} TF/s)",
+                "down_tflops": down, "down_frac": down / peak, "layer_tflops": layer, "layer_frac": layer / peak,
+                "library_dense_mxfp8_tflops": library_mxfp8_tflops(min(cfg["T"] * cfg["K"], 8192), 2 * cfg["I"], cfg["H"])
+                if with_library else None}
+    peak = peaks["hbm_gbs"]
+    achieved = work["gemm1_weight_bytes"] / (per_kernel["gemm1_swiglu"] * 1e-3) / 1e9
+    down = work["gemm2_weight_bytes"] / (per_kernel["gemm2_scale"] * 1e-3) / 1e9
+    layer = work["decode_bytes"] / (ms_step * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "grouped_mxfp8_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
+            "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic["bytes"],
+            "traffic_from": traffic["from"], "peak_source": f"{peaks['source']} copy bandwidth",
+            "down_gbs": down, "down_frac": down / peak, "layer_gbs": layer, "layer_frac": layer / peak}
+
+
+def gpu_leg(name, cfg, dev, peaks, steps, w_format="e4m3", weights=None, router_path=0, gemm_variant=0, seed=0):
+    """One workload on one GPU through the fused layer: graph replay (ms/step) and an eager pass with CUDA events
+    around every kernel.  Returns the summary and the live objects."""
     import torch
-    import torch.distributed as dist
+
+    from nki_library_b200.layer import MoELayer, random_expert_weights
+    T, H, I, E, K, B = (cfg[k] for k in "THIEKB")
+    hidden_h, router_w, bias = make_inputs(cfg, seed)
+    if weights is None:
+        weights = random_expert_weights(E, H, I, dev, seed=7, w_format=W_FORMATS[w_format])
+    layer = MoELayer(router_w.to(dev), weights, K, B, T, None if bias is None else bias.to(dev),
+                     router_path=router_path, gemm_variant=gemm_variant)
+    x = hidden_h.to(dev)
+    for _ in range(3):
+        layer.forward(x)
+    torch.cuda.synchronize()
+    layer.capture(x)
+    layer.replay()
+    ms = time_replays(layer, steps)
+    timers = {}
+    for _ in range(max(3, min(steps, 10))):
+        layer.forward(x, timers)
+    torch.cuda.synchronize()
+    per_kernel = {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in timers.items()}
+    status = layer.device_status()
+    out = {"workload": name, **{k: cfg[k] for k in "THIEKB"}, "zipf": cfg["zipf"], "weight_format": w_format,
+           "n_blocks": layer.N, "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "kernel_ms": per_kernel,
+           "steps": steps, "launches_per_step": layer.kernels_per_forward, "launch_mode": "cuda graph replay",
+           "roofline": roofline_block(cfg, name, per_kernel, ms, peaks, w_format)}
+    if any(status):
+        out["error"] = f"device status {status}"
+    return out, layer, x, (hidden_h, router_w, bias)
+
+
+def api_path_leg(cfg, layer, x, steps, ms_value):
+    """The same step through the drop-in entry points with the reference's argument lists (eager, inputs resident):
+    router_topk -> moe_group_tokens -> moe_cte for prefill, router_topk -> moe_tkg for decode."""
+    import torch
 
     import nki_library_b200 as m
-    from nki_library_b200.layer import MoELayer, random_expert_weights
+    T, E, K, B = cfg["T"], cfg["E"], cfg["K"], cfg["B"]
+    dev = x.device
+    logits = torch.empty((T, E), dtype=torch.float32, device=dev)
+    aff = torch.empty((T, E), dtype=torch.float32, device=dev)
+    idx = torch.empty((T, K), dtype=torch.int32, device=dev)
+    spec = m.MoECTESpec(m.MoECTEImplementation.shard_on_block_mx)
+    N = m.get_n_blocks(T, K, E, B)
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    peaks = load_peaks()
+    def step():
+        m.router_topk(x, layer.w, layer.bias, logits, aff, idx, m.RouterActFnType.SOFTMAX, K, 1, 0,
+                      router_pre_norm=True, norm_topk_prob=True, use_indirect_dma_scatter=True)
+        if cfg["kind"] == "decode":
+            return m.moe_tkg(x, layer.weights, None, aff, idx, False,
+                             expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.POST_SCALE)
+        g = m.moe_group_tokens(idx, E, B, N)
+        return m.moe_cte(x, aff.reshape(-1, 1), layer.weights, None, g["token_position_to_id"], g["block_to_expert"], B,
+                         spec, conditions=g["conditions"], skip_dma=m.SkipMode(True, False))
+
+    for _ in range(3):
+        out = step()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        out = step()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / steps
+    same = bool(torch.equal(out, layer.replay()))
+    return {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "vs_value": ms_value / ms,
+            "calls": "router_topk -> moe_tkg" if cfg["kind"] == "decode" else "router_topk -> moe_group_tokens -> moe_cte",
+            "launch_mode": "eager, per-call allocations included, prepared weights passed (cache hit)",
+            "output_equals_fused_layer": same}
+
+
+def parity_and_cpu(cfg, layer, inputs, threads, steps=2, warmup=1):
+    """CPU baseline on the GPU run's own inputs (routing from the GPU, sampled experts' weights read back from the
+    device) and, on the same rows, the GPU's per-position results against the CPU's."""
+    import numpy as np
+    import torch
+    hidden_h, router_w, bias = inputs
+    hidden_np = hidden_h.float().numpy()
+    _, _, route_t = cpu_route(cfg, hidden_h, router_w, bias)
+    idx = layer.idx.cpu().numpy()
+    aff = layer.aff.cpu().numpy()
+    inv = layer.inv.cpu().numpy()
+    s = cpu_block_sample(cfg, hidden_np, idx, aff, lambda e: device_expert_rows(layer.weights, e), steps, warmup, threads)
+    y_pos = layer.ws.y_pos
+    worst, scale, n = 0.0, 0.0, 0
+    for e, tok, y in s["results"]:
+        k = (idx[tok] == e).argmax(axis=1)
+        pos = torch.from_numpy(inv[tok, k].astype(np.int64)).to(y_pos.device)
+        got = y_pos[pos].float().cpu().numpy()
+        ref = torch.from_numpy(y).to(torch.bfloat16).float().numpy()
+        worst = max(worst, float(np.abs(got - ref).max()))
+        scale = max(scale, float(np.abs(ref).max()))
+        n += tok.size
+    parity = {"rows": n, "experts": s["experts"], "max_abs_err": worst, "max_abs_ref": scale,
+              "max_rel_err": worst / max(scale, 1e-30), "tolerance": 2e-2, "ok": worst / max(scale, 1e-30) <= 2e-2,
+              "what": "bf16(y * affinity) rows of the down contraction at the sampled positions vs the CPU oracle "
+                      "on the same tokens, routing and device weights"}
+    base = cpu_baseline_line(cfg, s, route_t, threads, "tokens, routing and the sampled experts' weights are the "
+                             "GPU run's own (weights read back from the device)")
+    return base, parity
+
+
+def decode_leg(weights, peaks, dev, w_format, threads, with_cpu):
+    """BASELINE's decode configuration (T = 64, Mixtral-8x7B shapes) on the given expert weights."""
+    import numpy as np
+    cfg = WORKLOADS["mixtral_decode"]
+    out, layer, x, inputs = gpu_leg("mixtral_decode", cfg, dev, peaks, 100, w_format, weights, seed=99)
+    out["algorithmic_gb_per_s"] = out["roofline"]["layer_gbs"]
+    out["frac_of_hbm_peak"] = out["roofline"]["layer_frac"]
+    out["api_path"] = api_path_leg(cfg, layer, x, 50, out["ms_per_step"])
+    if with_cpu and w_format == "e4m3":
+        idx, aff = layer.idx.cpu().numpy(), layer.aff.cpu().numpy()
+        s = cpu_decode_full(cfg, inputs[0].float().numpy(), idx, aff, lambda e: device_expert_rows(weights, e), 1, 1,
+                            threads)
+        got = layer.replay().float().cpu().numpy()
+        ref = s["out"]
+        err = float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+        out["cpu_baseline"] = {"value": cfg["T"] / s["seconds_per_step"], "unit": "tokens/s", "cores": threads,
+                               "kind": "port", "extrapolated": False, "sample": s["sample"]}
+        out["parity_sample"] = {"rows": cfg["T"], "max_rel_err": err, "tolerance": 2e-2, "ok": err <= 2e-2,
+                                "what": "the whole [T, H] output vs the CPU oracle on the same tokens, routing and "
+                                        "device weights"}
+    return out
+
+
+def run_single(args, cfg, name, dev, peaks):
+    import torch
+
+    from nki_library_b200.layer import HostPipeline, random_expert_weights
+    threads = os.cpu_count() or 1
     T, H, I, E, K, B = (cfg[k] for k in "THIEKB")
-
-    hidden_h, router_w, bias = make_inputs(cfg, dev, rank)
-    hidden_pin = hidden_h.pin_memory()
-    out_pin = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
-    hidden_d = hidden_h.to(dev)
-    bias_d = None if bias is None else bias.to(dev)
-    if world == 1:
-        weights = random_expert_weights(E, H, I, dev, seed=7, w_format=W_FORMATS[args.weight_format])
-        layer = MoELayer(router_w.to(dev), weights, K, B, T, bias_d, router_path=args.router_path,
-                         gemm_variant=args.gemm_variant)
-        n_blocks = layer.N
-
-        def forward(h, timers=None):
-            return layer.forward(h, timers)
-
-        def device_status():
-            return layer.device_status()
-
-        def launches_per_step():
-            return layer.kernels_per_forward
-    else:
-        # Expert parallelism: every rank keeps its own T tokens (weak scaling) and E / world experts;
-        # token rows travel to the owning rank and back through NCCL all-to-all.
-        from nki_library_b200.ep import CudaOps, ExpertParallelMoE, PeerExpertParallelMoE
-        if E % world != 0:
-            raise SystemExit(f"workload has {E} experts, not divisible by {world} ranks")
-        weights = random_expert_weights(E // world, H, I, dev, seed=7 + rank, w_format=W_FORMATS[args.weight_format])
-        n_blocks = None
-        if args.ep_backend == "peer":
-            # dispatch / combine by this library's own kernels storing into peer GPUs' memory (NVLink)
-            layer = PeerExpertParallelMoE(router_w.to(dev), weights, E, K, B, T, router_bias=bias_d,
-                                          capacity_factor=args.capacity_factor, fuse_return={"auto": None, "on": True, "off": False}[args.fuse_return])
-
-            def forward(h, timers=None):
-                layer.timers = timers
-                return layer.forward(h)
-
-            def device_status():
-                return layer.device_status()
-
-            def launches_per_step():
-                return layer.kernels_per_forward
-        else:
-            ops = CudaOps(router_w.to(dev), weights, E, K, B, bias_d)
-            ep = ExpertParallelMoE(ops, E)
-
-            def forward(h, timers=None):
-                ops.timers = timers
-                return ep.forward(h)
-
-            def device_status():
-                from nki_library_b200 import pipeline
-                return [int(v) for ws in pipeline._workspaces.values() for v in ws.status.cpu().tolist()[1:3]]
-
-            _count = {"n": 0}
-
-            def launches_per_step():
-                return _count["n"]
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    steps = args.steps
+    main_leg, layer, x, inputs = gpu_leg(name, cfg, dev, peaks, steps, args.weight_format, None, args.router_path,
+                                         args.gemm_variant)
+    if "error" in main_leg:
+        raise RuntimeError(main_leg["error"])
+    # the timed region proper: W warm-up replays, then exactly K
     for _ in range(max(args.warmup, 3)):
-        forward(hidden_d)
-    barrier()
-    if world > 1 and args.ep_backend != "peer":
-        ops.launches = 0
-        forward(hidden_d)
-        _count["n"] = ops.launches
-        barrier()
-    status = device_status()
-    if any(status):
-        raise RuntimeError(f"device status after warm-up: {status}")
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    # -------- resident-input leg (value): the captured launch sequence (single GPU) or eager steps (EP)
-    use_graph = (world == 1 or args.ep_backend == "peer") and not args.no_graph
-    if use_graph:
-        layer.capture(hidden_d)
         layer.replay()
-    barrier()
-    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_start.record()
-    for _ in range(args.steps):
-        if use_graph:
-            layer.replay()
-        else:
-            forward(hidden_d)
-    t_end.record()
-    barrier()
-    ms_total = t_start.elapsed_time(t_end)
-    status = device_status()
-    if any(status):
-        raise RuntimeError(f"device status after the timed steps: {status}")
-    # -------- the same steps again, eagerly, with CUDA events around every kernel (roofline input)
+    ms_step = time_replays(layer, steps)
+    # in-kernel clock probe over an eager pass
     probe = torch.zeros(4, dtype=torch.int64, device=dev)
-    if world == 1:
-        layer.clock_probe = probe
-    timers = {}
-    barrier()
-    for _ in range(args.steps):
-        forward(hidden_d, timers)
-    barrier()
-    if world == 1:
-        layer.clock_probe = None
+    layer.clock_probe = probe
+    layer.forward(x)
+    torch.cuda.synchronize()
+    layer.clock_probe = None
     pr = probe.cpu().tolist()
     kernel_sm_mhz = {"gemm1_swiglu": round(1e3 * pr[0] / pr[1], 1) if pr[1] else None,
                      "gemm2_scale": round(1e3 * pr[2] / pr[3], 1) if pr[3] else None}
-    if world == 1:
-        per_kernel = {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in timers.items()}
-    else:
-        n = len(timers["t0"])
-        names = ("dispatch" if args.ep_backend == "peer" else "gather_quantize", "gemm1_swiglu", "gemm2_scale")
-        per_kernel = {nm: sum(timers[f"t{i}"][j].elapsed_time(timers[f"t{i + 1}"][j]) for j in range(n)) / n
-                      for i, nm in enumerate(names)}
-    forward(hidden_d)  # drops the event hooks again
-    barrier()
-    status = device_status()
-    if any(status):
-        raise RuntimeError(f"device status after the instrumented steps: {status}")
-    # -------- end-to-end leg: host buffers through the public layer call
-    barrier()
+    roofline = roofline_block(cfg, name, main_leg["kernel_ms"], ms_step, peaks, args.weight_format, with_library=True)
+    # -------- CPU baseline + parity on the same rows (outside every timed region)
+    cpu = parity = None
+    if not args.skip_cpu and cfg["kind"] == "prefill" and args.weight_format == "e4m3":
+        layer.replay()
+        torch.cuda.synchronize()
+        cpu, parity = parity_and_cpu(cfg, layer, inputs, threads)
+    # -------- drop-in entry points
+    api = api_path_leg(cfg, layer, x, steps, ms_step)
+    # -------- sustained: the same replay for a few seconds
+    sustained = None
+    if args.sustained_s > 0:
+        n = max(steps, int(args.sustained_s * 1e3 / ms_step))
+        ms_s = time_replays(layer, n)
+        sustained = {"seconds": ms_s * n * 1e-3, "steps": n, "ms_per_step": ms_s, "tokens_per_s": T / (ms_s * 1e-3)}
+        if cfg["kind"] == "prefill":
+            tf = algorithmic_work(cfg, args.weight_format)["layer_flops"] / (ms_s * 1e-3) / 1e12
+            sustained.update(layer_tflops=tf, layer_frac_of_sustained_peak=tf / (2.0 * peaks["bf16_tflops_sustained"]),
+                             layer_frac_of_burst_peak=tf / (2.0 * peaks["bf16_tflops"]))
+    # -------- end to end through host buffers
+    hidden_pin = inputs[0].pin_memory()
+    out_pins = [torch.empty((T, H), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    pipe = HostPipeline(layer)
+    pipe.submit(hidden_pin, out_pins[0])
+    pipe.drain()
+    pipe.step = 0
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e_start.record()
+    for i in range(steps):
+        pipe.submit(hidden_pin, out_pins[i & 1])
+    pipe.drain()
+    e_end.record()
+    torch.cuda.synchronize()
+    ms_e2e = e_start.elapsed_time(e_end) / steps
+    status = layer.device_status()
+    if any(status):
+        raise RuntimeError(f"device status after the timed steps: {status}")
+    clocks = sampler.stop()
+    weights_bytes = layer.weights.nbytes()
+    # -------- the other single-GPU configurations
+    secondary = {}
+    if name == "mixtral_prefill" and not args.no_secondary:
+        secondary["decode"] = decode_leg(layer.weights, peaks, dev, args.weight_format, threads, not args.skip_cpu)
+        if args.weight_format == "e4m3":
+            w4 = random_expert_weights(E, H, I, dev, seed=8, w_format=W_FORMATS["e2m1"])
+            secondary["decode_mxfp4_weights"] = decode_leg(w4, peaks, dev, "e2m1", threads, False)
+            del w4
+        del pipe, layer
+        torch.cuda.empty_cache()
+        for other in ("finegrained_prefill", "ep_prefill"):
+            o, lay, _, _ = gpu_leg(other, WORKLOADS[other], dev, peaks, 10, args.weight_format)
+            secondary[other] = o
+            del lay
+            torch.cuda.empty_cache()
+    line = {
+        "metric": "moe_layer_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8_e4m3",
+        "data": "synthetic",
+        "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}, "n_blocks": main_leg["n_blocks"],
+                   "weight_format": args.weight_format, "tokens_per_gpu": T, "experts_per_gpu": E,
+                   "parallelism": "single",
+                   "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)" % (weights_bytes / 1e9)},
+        "roofline": roofline,
+        "kernel_ms": main_leg["kernel_ms"],
+        "kernel_sm_mhz": kernel_sm_mhz,
+        "api_path": api,
+        "sustained": sustained,
+        "parity_sample": parity,
+        **secondary,
+        "cpu_baseline": cpu if cpu is not None else {"value": None, "unit": "tokens/s", "cores": threads,
+                                                     "kind": "port", "sample": "skipped"},
+        "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2,
+                "d2h_bytes_per_step": T * H * 2},
+        "gpu_launches": main_leg["launches_per_step"] * steps,
+        "launch_mode": "cuda graph replay (value, e2e, sustained) + eager instrumented pass (kernel_ms) + eager "
+                       "drop-in calls (api_path)",
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_multi(args, cfg, name, dev, peaks, world, rank):
+    """Expert parallelism: every rank keeps its own T tokens (weak scaling) and E / world experts; token rows
+    travel to the owning rank and back through this library's peer-memory kernels (or NCCL all-to-all)."""
+    import torch
+    import torch.distributed as dist
+
+    from nki_library_b200.ep import CudaOps, ExpertParallelMoE, PeerExpertParallelMoE
+    from nki_library_b200.layer import HostPipeline, MoELayer, random_expert_weights
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def build(cfg_, tokens, seed):
+        H_, I_, E_, K_, B_ = cfg_["H"], cfg_["I"], cfg_["E"], cfg_["K"], cfg_["B"]
+        hidden_h, router_w, bias = make_inputs(dict(cfg_, T=tokens), seed)
+        w = random_expert_weights(E_ // world, H_, I_, dev, seed=7 + rank, w_format=W_FORMATS[args.weight_format])
+        bias_d = None if bias is None else bias.to(dev)
+        if args.ep_backend == "peer":
+            lay = PeerExpertParallelMoE(router_w.to(dev), w, E_, K_, B_, tokens, router_bias=bias_d,
+                                        capacity_factor=args.capacity_factor,
+                                        fuse_return={"auto": None, "on": True, "off": False}[args.fuse_return])
+        else:
+            lay = ExpertParallelMoE(CudaOps(router_w.to(dev), w, E_, K_, B_, bias_d), E_)
+        return lay, hidden_h, router_w, bias
+
+    def timed(lay, x, steps, use_graph):
+        for _ in range(max(args.warmup, 3)):
+            lay.forward(x)
+        barrier()
+        if use_graph:
+            lay.capture(x)
+            lay.replay()
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            lay.replay() if use_graph else lay.forward(x)
+        e.record()
+        barrier()
+        t = torch.tensor([s.elapsed_time(e)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item() / steps
+
+    T, H, I, E, K, B = (cfg[k] for k in "THIEKB")
+    if E % world != 0:
+        raise SystemExit(f"workload has {E} experts, not divisible by {world} ranks")
+    use_graph = args.ep_backend == "peer" and not args.no_graph
+    layer, hidden_h, router_w, bias = build(cfg, T, rank)
+    x = hidden_h.to(dev)
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(layer, x, args.steps, use_graph)
+    status = layer.device_status() if hasattr(layer, "device_status") else []
+    if any(status):
+        raise RuntimeError(f"device status after the timed steps: {status}")
+    # eager pass with events around the phases
+    per_kernel = None
+    if args.ep_backend == "peer":
+        timers = {}
+        layer.timers = timers
+        for _ in range(args.steps):
+            layer.forward(x)
+        barrier()
+        layer.timers = None
+        n = len(timers["t0"])
+        per_kernel = {nm: sum(timers[f"t{i}"][j].elapsed_time(timers[f"t{i + 1}"][j]) for j in range(n)) / n
+                      for i, nm in enumerate(("dispatch", "gemm1_swiglu", "gemm2_scale"))}
+    # parity: rank 0's output against the single-GPU fused layer on the same tokens and all ranks' weights
+    parity = None
+    out_ep = layer.forward(x).clone()
+    barrier()
+    if rank == 0 and not args.skip_cpu:
+        from nki_library_b200.weights import ExpertWeights
+        parts = [random_expert_weights(E // world, H, I, dev, seed=7 + r, w_format=W_FORMATS[args.weight_format])
+                 for r in range(world)]
+        full = ExpertWeights(E, H, I, torch.cat([p.w1 for p in parts]), torch.cat([p.w1_sf for p in parts]),
+                             torch.cat([p.w2 for p in parts]), torch.cat([p.w2_sf for p in parts]), None, None, False,
+                             parts[0].w_format)
+        del parts
+        single = MoELayer(router_w.to(dev), full, K, B, T, None if bias is None else bias.to(dev))
+        ref = single.forward(x).float()
+        err = float((out_ep.float() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+        parity = {"rows": T, "max_rel_err": err, "tolerance": 1e-2, "ok": err <= 1e-2,
+                  "what": "rank 0's expert-parallel output vs the single-GPU fused layer on the same tokens and all "
+                          "ranks' weights (same kernels; a token's rows are summed in a different order)"}
+        del single, full, ref
+        torch.cuda.empty_cache()
+    barrier()
+    # end to end through host buffers
+    hidden_pin = hidden_h.pin_memory()
+    out_pins = [torch.empty((T, H), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # the copy engine alone (all ranks at once), for the ceiling of the host link per rank
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    c0.record()
+    for _ in range(5):
+        x.copy_(hidden_pin, non_blocking=True)
+    c1.record()
+    torch.cuda.synchronize()
+    h2d_alone = 5 * T * H * 2 / (c0.elapsed_time(c1) * 1e-3) / 1e9
+    pipe = None
     if use_graph:
-        from nki_library_b200.layer import HostPipeline
         pipe = HostPipeline(layer)
-        out_pins = [out_pin, torch.empty_like(out_pin).pin_memory()]
         pipe.submit(hidden_pin, out_pins[0])
         pipe.drain()
         pipe.step = 0
@@ -420,89 +737,95 @@ def run_ours(args, cfg, name):
         pipe.drain()
         e_end.record()
     else:
+        barrier()
         e_start.record()
-        for _ in range(args.steps):
-            hidden_d.copy_(hidden_pin, non_blocking=True)
-            out = forward(hidden_d)
-            out_pin.copy_(out, non_blocking=True)
+        for i in range(args.steps):
+            x.copy_(hidden_pin, non_blocking=True)
+            out = layer.forward(x)
+            out_pins[i & 1].copy_(out, non_blocking=True)
         e_end.record()
     barrier()
-    ms_e2e = e_start.elapsed_time(e_end)
+    t = torch.tensor([e_start.elapsed_time(e_end)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_e2e = t.item() / args.steps
     clocks = sampler.stop() if rank == 0 else None
-
-    if world > 1:
-        t = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, ms_e2e = t.tolist()
-    status = device_status()
-    if any(status):
-        raise RuntimeError(f"device status after the end-to-end steps: {status}")
-
+    launches = getattr(layer, "kernels_per_forward", 12)
+    # strong scaling of the large expert-parallel configuration: 32768 tokens in total, split over the ranks
+    strong = {}
+    if name == "mixtral_prefill" and not args.no_secondary and args.ep_backend == "peer":
+        del layer, pipe
+        torch.cuda.empty_cache()
+        for wl in ("ep_prefill", "ep_prefill_zipf"):
+            c5 = WORKLOADS[wl]
+            if c5["E"] % world or c5["T"] % world:
+                continue
+            try:
+                lay5, h5, _, _ = build(c5, c5["T"] // world, 100 + rank)
+                ms5 = timed(lay5, h5.to(dev), 10, use_graph)
+                st5 = lay5.device_status()
+                strong[wl] = {"total_tokens": c5["T"], "tokens_per_gpu": c5["T"] // world,
+                              "experts_per_gpu": c5["E"] // world, "ms_per_step": ms5,
+                              "tokens_per_s": c5["T"] / (ms5 * 1e-3), "device_status": st5,
+                              "capacity_factor": args.capacity_factor,
+                              "layer_tflops_per_gpu": algorithmic_work(c5)["layer_flops"] / world / (ms5 * 1e-3) / 1e12}
+                del lay5
+            except Exception as exc:  # reported in the line, never hidden
+                strong[wl] = {"error": str(exc)[:300]}
+            torch.cuda.empty_cache()
+            barrier()
     if rank == 0:
         work = algorithmic_work(cfg, args.weight_format)
-        ms_step = ms_total / args.steps
-        if cfg["kind"] == "prefill":
-            dom = "gemm1_swiglu"
+        roofline = None
+        if per_kernel is not None:
             peak = 2.0 * peaks["bf16_tflops"]
-            achieved = work["gemm1_flops"] / (per_kernel[dom] * 1e-3) / 1e12
-            roofline = {"bound": "tensor", "kernel": "grouped_mxfp8_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
-                        "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                        "frac_of_sustained_peak": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
-                        "traffic": NCU_TRAFFIC_BYTES.get(name) if world == 1 else None,
-                        "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s); "
-                                       "dense fp8/mxfp8 issues at twice the bf16 rate; frac_of_sustained_peak "
-                                       f"uses 2 x the sustained bf16 figure ({peaks['bf16_tflops_sustained']} TF/s)",
-                        "layer_tflops": work["layer_flops"] / (ms_step * 1e-3) / 1e12,
-                        "library_dense_mxfp8_tflops": library_mxfp8_tflops(min(T * K, 8192), 2 * I, H)
-                        if world == 1 else None}
-        else:
-            dom = "gemm1_swiglu"
-            peak = peaks["hbm_gbs"]
-            achieved = work["gemm1_weight_bytes"] / (per_kernel[dom] * 1e-3) / 1e9
-            roofline = {"bound": "hbm", "kernel": "grouped_mxfp8_gemm_kernel<gate_up+SwiGLU>", "achieved": achieved,
-                        "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                        "traffic": NCU_TRAFFIC_BYTES.get(name) if world == 1 else None,
-                        "peak_source": f"{peaks['source']} copy bandwidth",
-                        "layer_gbs": work["decode_bytes"] / (ms_step * 1e-3) / 1e9}
-        cpu = (dict(value=None, sample="skipped (--skip-cpu)") if args.skip_cpu
-               else cpu_sample(cfg, 4, 1, os.cpu_count() or 1))
-        decode = decode_mxfp4 = None
-        if world == 1 and name == "mixtral_prefill" and not args.no_decode_leg:
-            decode = decode_leg(weights, peaks, dev, args.weight_format)
-            if args.weight_format == "e4m3":
-                # the same decode step with MXFP4 (e2m1) expert weights: half the bytes to stream
-                w4 = random_expert_weights(E, H, I, dev, seed=8, w_format=W_FORMATS["e2m1"])
-                decode_mxfp4 = decode_leg(w4, peaks, dev, "e2m1")
-                del w4
+            ach = work["gemm1_flops"] / (per_kernel["gemm1_swiglu"] * 1e-3) / 1e12
+            roofline = {"bound": "tensor", "kernel": "grouped_mxfp8_gemm_kernel<gate_up+SwiGLU>", "achieved": ach,
+                        "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                        "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s)",
+                        "layer_tflops_per_gpu": work["layer_flops"] / (ms_step * 1e-3) / 1e12}
         line = {
             "metric": "moe_layer_tokens_per_s", "value": world * T / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8_e4m3",
             "data": "synthetic",
-            "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}, "n_blocks": n_blocks,
-                       "weight_format": args.weight_format,
+            "config": {"workload": name, **{k: cfg[k] for k in "THIEKB"}, "weight_format": args.weight_format,
                        "tokens_per_gpu": T, "experts_per_gpu": E // world,
-                       "parallelism": "single" if world == 1 else
-                       (f"ep{world} (peer-memory dispatch/combine kernels over NVLink)" if args.ep_backend == "peer"
-                        else f"ep{world} (NCCL all-to-all dispatch/combine)"),
-                       "l2": "inputs larger than L2 (expert weights %.2f GB streamed every step)" % (weights.nbytes() / 1e9)},
+                       "parallelism": (f"ep{world} (peer-memory dispatch/combine kernels over NVLink)"
+                                       if args.ep_backend == "peer" else f"ep{world} (NCCL all-to-all dispatch/combine)"),
+                       "l2": "inputs larger than L2 (expert weights streamed every step)"},
             "roofline": roofline,
-            "decode": decode,
-            "decode_mxfp4_weights": decode_mxfp4,
             "kernel_ms": per_kernel,
-            "kernel_sm_mhz": kernel_sm_mhz,
-            "cpu_baseline": {"value": cpu["value"], "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
-                             "sample": cpu["sample"]},
-            "e2e": {"value": world * T / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2},
-            "gpu_launches": launches_per_step() * args.steps * 3,
-            "launch_mode": "cuda graph replay (value, e2e) + eager instrumented pass (kernel_ms)" if use_graph
-                           else "eager",
+            "parity_sample": parity,
+            "ep_prefill_strong": strong or None,
+            "cpu_baseline": {"value": None, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+                             "sample": "timed at N=1 only"},
+            "e2e": {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2,
+                    "d2h_bytes_per_step": T * H * 2,
+                    "per_rank_gb_per_s": {"h2d": T * H * 2 / (ms_e2e * 1e-3) / 1e9,
+                                          "d2h": T * H * 2 / (ms_e2e * 1e-3) / 1e9,
+                                          "h2d_copy_alone_all_ranks_at_once": h2d_alone}},
+            "gpu_launches": launches * args.steps,
+            "launch_mode": "cuda graph replay" if use_graph else "eager",
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    dist.destroy_process_group()
+
+
+def run_ours(args, cfg, name):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    peaks = load_peaks()
+    if world == 1:
+        run_single(args, cfg, name, dev, peaks)
+    else:
+        dist.init_process_group("nccl", device_id=dev)
+        run_multi(args, cfg, name, dev, peaks, world, rank)
 
 
 def main():
@@ -512,7 +835,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mixtral_prefill", choices=sorted(WORKLOADS))
-    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline and parity legs (profiling runs)")
     ap.add_argument("--weight-format", default="e4m3", choices=sorted(W_FORMATS),
                     help="element type of the expert weights (activations are always MXFP8 e4m3)")
     ap.add_argument("--ep-backend", default="peer", choices=["peer", "nccl"],
@@ -525,7 +848,9 @@ def main():
     ap.add_argument("--fuse-return", default="auto", choices=["auto", "on", "off"],
                     help="expert parallelism: let the down contraction's epilogue store result rows into their GPUs "
                          "(on), copy them in a separate kernel (off), or choose by rank count (auto)")
-    ap.add_argument("--no-decode-leg", action="store_true", help="omit the secondary decode measurements (profiling runs)")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="omit the other configurations' measurements (profiling runs)")
+    ap.add_argument("--sustained-s", type=float, default=2.0, help="length of the sustained replay leg in seconds (0 = off)")
     ap.add_argument("--router-path", type=int, default=0, help="1 split-K router, 2 tcgen05 router (0 = by shape)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]

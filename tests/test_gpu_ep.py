@@ -1,4 +1,5 @@
-"""Expert parallelism on real GPUs: 2 ranks over NCCL against the single-GPU layer and the CPU oracle."""
+"""Expert parallelism on real GPUs: 2, 4 and 8 ranks (as many as the machine has) against the single-GPU layer and
+the CPU oracle, uniform and Zipf-skewed routing, receive buffers that suffice and ones that must report overflow."""
 
 import os
 import sys
@@ -27,7 +28,14 @@ def _inputs(rank):
     return hidden, router_w, make_rows_weights(E, H, I, seed=9)
 
 
-def _worker(rank, world, port, results, backend):
+def _zipf_bias(s=1.2):
+    """Router logit bias -s * ln(rank) over a seeded permutation of the experts: expected load ~ rank^-s."""
+    from moe_testlib import bf16_values
+    rank = np.random.default_rng(17).permutation(E) + 1
+    return bf16_values((-s * np.log(rank)).astype(np.float32))
+
+
+def _worker(rank, world, port, results, backend, zipf=False, capacity_factor=2.5):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -45,14 +53,19 @@ def _worker(rank, world, port, results, backend):
             out2 = layer.forward(x).clone()
             rows = layer.last_rows_received
         else:
+            bias = torch.from_numpy(_zipf_bias()).cuda() if zipf else None
             layer = PeerExpertParallelMoE(torch.from_numpy(router_w).cuda(), local, E, K, B, T_LOCAL,
+                                          router_bias=bias, capacity_factor=capacity_factor,
                                           fuse_return=backend == "peer")
             out = layer.forward(x).clone()
             out2 = layer.forward(x).clone()
             out3 = layer.forward(x).clone()
-            assert not any(layer.device_status()), layer.device_status()
-            assert torch.equal(out2, out3)
+            status = layer.device_status()
+            if capacity_factor >= 2.5:
+                assert not any(status), status
+                assert torch.equal(out2, out3)
             rows = int((layer.row_valid >= 0).sum().item())
+            results[("status", rank)] = list(status)
         torch.cuda.synchronize()
         results[rank] = (out.float().cpu().numpy(), bool(torch.equal(out, out2)), rows)
     finally:
@@ -92,18 +105,16 @@ def test_peer_memory_exchange_single_rank(fuse_return):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("backend", ["nccl", "peer", "peer_unfused"])
-def test_expert_parallel_two_gpus_matches_oracle_and_single_gpu(backend):
+def _need(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+
+
+def _check_against_single_gpu_and_oracle(results, world, bias=None):
     import nki_library_b200 as m
     from moe_testlib import bf16_values, max_rel
     from nki_library_b200.layer import MoELayer
     from oracle import moe, routing
-    world = 2
-    mgr = mp.Manager()
-    results = mgr.dict()
-    port = {"nccl": 29711, "peer": 29712, "peer_unfused": 29713}[backend]
-    mp.spawn(_worker, args=(world, port, results, backend), nprocs=world, join=True)
     rows = 0
     for rank in range(world):
         hidden, router_w, w_np = _inputs(rank)
@@ -112,12 +123,52 @@ def test_expert_parallel_two_gpus_matches_oracle_and_single_gpu(backend):
         assert deterministic
         # single-GPU layer with all experts on the same tokens
         full = m.prepare_from_rows(*(torch.from_numpy(a).cuda() for a in w_np))
-        single = MoELayer(torch.from_numpy(router_w).cuda(), full, K, B, T_LOCAL)
+        single = MoELayer(torch.from_numpy(router_w).cuda(), full, K, B, T_LOCAL,
+                          None if bias is None else torch.from_numpy(bias).cuda())
         ref_gpu = single.forward(torch.from_numpy(hidden).to(torch.bfloat16).cuda()).float().cpu().numpy()
         assert max_rel(got, ref_gpu) <= 1e-2
         # CPU oracle of the whole layer
-        _, idx, aff = routing.router_topk(torch.from_numpy(hidden), torch.from_numpy(router_w), None, K,
+        _, idx, aff = routing.router_topk(torch.from_numpy(hidden), torch.from_numpy(router_w),
+                                          None if bias is None else torch.from_numpy(bias), K,
                                           routing.SOFTMAX, True, True)
         ref = moe.moe_tkg_rows(hidden, aff.numpy(), idx.numpy(), *w_np)
         assert max_rel(got, bf16_values(ref)) <= 2e-2
     assert rows == world * T_LOCAL * K
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("backend", ["nccl", "peer", "peer_unfused"])
+def test_expert_parallel_matches_oracle_and_single_gpu(backend, world):
+    _need(world)
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 29700 + 10 * world + {"nccl": 1, "peer": 2, "peer_unfused": 3}[backend]
+    mp.spawn(_worker, args=(world, port, results, backend), nprocs=world, join=True)
+    _check_against_single_gpu_and_oracle(results, world)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("backend", ["peer", "peer_unfused"])
+def test_expert_parallel_zipf_routing_fits_full_capacity(backend, world):
+    """Zipf(1.2)-skewed routing: with receive buffers of ``world`` x the fair share (all pairs of all ranks would
+    fit on one GPU) nothing can overflow, and the result still matches the single-GPU layer and the oracle."""
+    _need(world)
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 29800 + 10 * world + {"peer": 2, "peer_unfused": 3}[backend]
+    mp.spawn(_worker, args=(world, port, results, backend, True, max(2.5, float(world))), nprocs=world, join=True)
+    _check_against_single_gpu_and_oracle(results, world, _zipf_bias())
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_overflow_is_reported(world):
+    """The same skewed routing with receive buffers of 0.6 x the fair share: the GPUs that own the popular experts
+    must report status 21 (rows beyond the buffer are dropped, nothing is written out of bounds) and the run ends
+    with a usable context."""
+    _need(world)
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, 29900 + world, results, "peer_unfused", True, 0.6), nprocs=world, join=True)
+    statuses = [results[("status", r)] for r in range(world)]
+    assert any(s[0] == 21 for s in statuses), statuses
+    assert all(s[0] in (0, 21) and not any(s[1:]) for s in statuses), statuses

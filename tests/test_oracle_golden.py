@@ -338,3 +338,13 @@ def test_prefill_oracle_matches_reference_blockwise_golden(name, mx_gold):
                                  inp["w2_scales"], inp["expert_index"], **kw)
     assert out.shape == ref.shape
     assert _rel(gi.bf16_round(out), ref) <= 8e-3  # two bf16 steps at the largest output
+
+
+def test_large_operand_dequantise_equals_table_lookup():
+    """The torch conversion used for operands of a million elements or more gives the bytes of the lookup table."""
+    rng = np.random.default_rng(5)
+    codes = rng.integers(0, 256, (2048, 1024), dtype=np.uint8)
+    scales = rng.integers(100, 140, (2048, 32), dtype=np.uint8)
+    fast = mx.dequantize_mx_rows(codes, scales)
+    slow = np.concatenate([mx.dequantize_mx_rows(codes[i:i + 256], scales[i:i + 256]) for i in range(0, 2048, 256)])
+    assert np.array_equal(fast, slow, equal_nan=True)
