@@ -44,6 +44,12 @@ WORKLOADS = {
     "ep_prefill": dict(kind="prefill", T=32768, H=4096, I=1536, E=128, K=8, B=256, zipf=None),
     "ep_prefill_zipf": dict(kind="prefill", T=32768, H=4096, I=1536, E=128, K=8, B=256, zipf=1.2),
     "tiny_prefill": dict(kind="prefill", T=256, H=512, I=1024, E=4, K=2, B=128, zipf=None),
+    # cut-down shapes for profiler captures: the Mixtral block geometry with I = 2048 (201 MB of weights, larger
+    # than L2, a few hundred MB on the device) and the fine-grained / expert-parallel shapes with fewer experts
+    "profile_prefill": dict(kind="prefill", T=4096, H=4096, I=2048, E=8, K=2, B=512, zipf=None),
+    "profile_decode": dict(kind="decode", T=64, H=4096, I=2048, E=8, K=2, B=128, zipf=None),
+    "profile_finegrained": dict(kind="prefill", T=2048, H=7168, I=2048, E=32, K=8, B=128, zipf=1.2),
+    "profile_ep_prefill": dict(kind="prefill", T=8192, H=4096, I=1536, E=32, K=8, B=256, zipf=None),
 }
 
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
@@ -200,15 +206,20 @@ def cpu_route(cfg, hidden, router_w, bias):
 
 
 def cpu_synthetic_expert(cfg, e):
-    """Seeded N(0, 0.02) weights of one expert quantised on the CPU (used when no GPU weights exist to read back)."""
+    """Seeded weights of one expert for the CPU-only arm (no GPU weights exist to read back): uniformly random finite
+    e4m3 codes with block scales of 2^-12 .. 2^-9, which puts the weights at the N(0, 0.02) order of magnitude.  The
+    oracle's arithmetic (table lookup, power-of-two scaling, fp32 matmul) takes the same time whatever the values."""
     import numpy as np
-
-    from oracle import mx
     H, I = cfg["H"], cfg["I"]
     rng = np.random.default_rng(7000 + e)
-    c1, s1 = mx.quantize_mx_rows((rng.standard_normal((2 * I, H), dtype=np.float32) * np.float32(0.02)))
-    c2, s2 = mx.quantize_mx_rows((rng.standard_normal((H, I), dtype=np.float32) * np.float32(0.02)))
-    return c1.reshape(1, 2, I, H), s1.reshape(1, 2, I, H // 32), c2.reshape(1, H, I), s2.reshape(1, H, I // 32)
+
+    def codes(shape):
+        c = rng.integers(0, 256, shape, dtype=np.uint8)
+        c[(c & 0x7F) == 0x7F] = 0x38  # the two NaN patterns -> 1.0
+        return c
+
+    return (codes((1, 2, I, H)), rng.integers(115, 119, (1, 2, I, H // 32), dtype=np.uint8),
+            codes((1, H, I)), rng.integers(115, 119, (1, H, I // 32), dtype=np.uint8))
 
 
 def cpu_block_sample(cfg, hidden_np, idx, aff, expert_weights, steps, warmup, threads, n_experts=4,
@@ -311,8 +322,8 @@ def run_reference(args, cfg, name):
     else:
         s = cpu_block_sample(cfg, hidden_np, idx, aff, lambda e: cpu_synthetic_expert(cfg, e), max(1, args.steps),
                              args.warmup, threads)
-        base = cpu_baseline_line(cfg, s, route_t, threads, "weights drawn and quantised on the CPU from the same "
-                                 "distribution as the GPU arm's")
+        base = cpu_baseline_line(cfg, s, route_t, threads, "tokens and router as in the GPU arm, expert weights "
+                                 "random e4m3 codes of the same magnitude (the GPU arm's are quantised on the device)")
         value, sec = base["value"], s["seconds_per_step"]
     line = {
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",

@@ -253,6 +253,35 @@ int b200moe_grouped_gemm2_scale(const uint8_t* m_codes, const uint8_t* m_sf, con
                                 int aff_per_row, void* y_pos_bf16, int32_t* status, int impl,
                                 void* clock_probe, b200moe_stream_t stream);
 
+/* ---- dense (non-MX) expert contractions ----------------------------------------------------
+ * The reference's bf16 and fp8-row expert kernels (core/moe/moe_cte/bwmm_shard_on_block.py:72,
+ * core/moe/moe_cte/bwmm_shard_on_I.py:2014, core/moe/moe_tkg/all_expert_impl.py:65,
+ * core/moe/moe_tkg/selective_expert_impl.py:45; CPU definition core/moe/moe_cte/moe_cte_torch.py:26-242):
+ * bf16 activations x bf16 weights with fp32 accumulation on the same grouped tcgen05 kernel
+ * (kind::f16 instead of the block-scaled kind).  Weights are K-major bf16 rows: gate/up
+ * [E, 2I, H] with the 32 / 32 gate / up row interleave of the MX layout, down [E, H, I].
+ * fp8-row weights are passed dequantised to bf16 together with their per-row factors
+ * (w*_col_scale fp32 [E, 2I] in the interleaved row order / [E, H]; NULL = none), which the
+ * epilogues apply to the accumulator before the bias, as the reference does.
+ *
+ * scatter_rows: the bf16 row of token t is copied to every position table[t*K + k] >= 0
+ * (table as for b200moe_scatter_quantize_mxfp8); with pre_scale_affinities (flat [T*E] table,
+ * PRE_SCALE mode) it is first multiplied by the affinity of the position's expert.
+ * dense_gemm1: out m_bf16 [n_blocks*B, I] = act(gate) * up; dense_gemm2: bf16 y_pos rows. */
+int b200moe_scatter_rows_bf16(const void* hidden_bf16, int T, int H, const int32_t* table, int K, int64_t n_pos,
+                              const int32_t* block_to_expert, int B, int E, const void* pre_scale_affinities,
+                              int aff_dtype, void* out_bf16, int32_t* tile_flags, b200moe_stream_t stream);
+int b200moe_dense_gemm1_swiglu(const void* x_bf16, const void* w1_bf16, const float* w1_col_scale,
+                               const float* bias_gu_dev, const int32_t* block_to_expert, const int32_t* conditions,
+                               const int32_t* tile_flags, int n_blocks, int B, int E, int H, int I, int act_fn,
+                               float gate_lo, float gate_hi, float up_lo, float up_hi, void* m_bf16, int32_t* status,
+                               int impl, b200moe_stream_t stream);
+int b200moe_dense_gemm2_scale(const void* m_bf16, const void* w2_bf16, const float* w2_col_scale, const float* bias_d,
+                              const int32_t* block_to_expert, const int32_t* conditions, const int32_t* tile_flags,
+                              const int32_t* token_position_to_id, int hidden_rows, int n_blocks, int B, int E, int H,
+                              int I, const void* affinities, int aff_dtype, int aff_per_row, void* y_pos_bf16,
+                              int32_t* status, int impl, b200moe_stream_t stream);
+
 /* combine = the accumulate-and-scatter tail of the block loop
  * (core/moe/moe_cte/bwmm_shard_on_block_mx.py:1303-1347): out[t,:] = sum over the
  * valid entries p = table[t, j] (j ascending) of y_pos[p,:], fp32 accumulation,
@@ -267,6 +296,15 @@ int b200moe_combine(const void* y_pos_bf16, const int32_t* table, int T, int n_c
  * also written to residual_out (may be NULL).  gamma [H] fp32 / bf16 or NULL. */
 int b200moe_rmsnorm(const void* inp_bf16, const void* residual_bf16, const void* gamma, int gamma_dtype, int T, int H,
                     int hidden_actual, float eps, void* out_bf16, void* residual_out_bf16, b200moe_stream_t stream);
+/* The same RMSNorm fused with the MXFP8 activation quantisation -- rmsnorm_mx_quantize_tkg
+ * (core/subkernels/rmsnorm_mx_quantize_tkg.py:29-80), which moe_block_tkg uses in MX all-expert mode
+ * (core/moe_block/moe_block_tkg.py:199-218): besides the normalised bf16 rows (out, for the router) it
+ * writes the rows' MXFP8 codes and scale atoms to every position table[t*K + k] >= 0 and fills
+ * tile_flags, i.e. what b200moe_scatter_quantize_mxfp8 would produce from `out`.  H % 128 == 0. */
+int b200moe_rmsnorm_quantize_mxfp8(const void* inp_bf16, const void* residual_bf16, const void* gamma, int gamma_dtype,
+                                   int T, int H, int hidden_actual, float eps, void* out_bf16, void* residual_out_bf16,
+                                   const int32_t* table, int K, int64_t n_pos, int h_packed_order, uint8_t* codes,
+                                   uint8_t* sf_atoms, int32_t* tile_flags, b200moe_stream_t stream);
 
 /* ---- expert parallelism over peer memory -------------------------------------------------------
  * One process per GPU.  The reference's expert-parallel mode slices experts by rank_id

@@ -68,9 +68,20 @@ SIGNATURES = {
     "b200moe_grouped_gemm2_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                             c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "b200moe_scatter_rows_bf16": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_void_p, c_int, c_int,
+                                          c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200moe_dense_gemm1_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                           c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
+                                           c_void_p, c_void_p, c_int, c_void_p]),
+    "b200moe_dense_gemm2_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                                          c_void_p, c_int, c_void_p]),
     "b200moe_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "b200moe_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
                                 c_void_p]),
+    "b200moe_rmsnorm_quantize_mxfp8": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                               c_void_p, c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                               c_void_p]),
     "b200moe_ipc_export": (c_int, [c_void_p, c_void_p, c_void_p]),
     "b200moe_ipc_open": (c_int, [c_void_p, c_int64, c_void_p]),
     "b200moe_ipc_close": (c_int, [c_void_p, c_int64]),

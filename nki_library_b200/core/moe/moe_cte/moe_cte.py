@@ -10,7 +10,7 @@ from typing import Any, Optional
 import torch
 
 from .... import _lib, pipeline
-from ....weights import ExpertWeights, prepare_from_nki_cached
+from ....weights import DenseExpertWeights, ExpertWeights, prepare_dense_cached, prepare_from_nki_cached
 from ...utils.common_types import ActFnType, ExpertAffinityScaleMode
 from ...utils.kernel_call import kernel_entry
 from .moe_cte_utils import BlockShardStrategy, SkipMode
@@ -49,6 +49,8 @@ class ShardOnIConfig:
     num_static_block: Optional[int] = None
     n_block_per_iter: int = 1
     is_hybrid: bool = False
+    checkpoint_activation: bool = False
+    expert_affinity_multiply_on_I: bool = False
 
 
 @dataclass
@@ -107,19 +109,30 @@ def moe_cte(
     ``[rows, H]``; with ``compat_lnc_slabs`` the reference's ``[2, rows, H]``
     (slab 1 zero, bwmm_shard_on_block_mx.py:309-313,495-514).
 
-    Only the MX implementations exist here (``shard_on_block_mx``,
-    ``shard_on_i_mx``, ``shard_on_i_mx_hybrid`` all map to the same kernels).
+    The MX implementations (``shard_on_block_mx``, ``shard_on_i_mx``, ``shard_on_i_mx_hybrid``) all map to the
+    block-scaled kernels.  The non-MX implementations (``shard_on_block``, ``shard_on_i``, ``shard_on_i_hybrid``,
+    ``shard_on_i_dropping``: bf16 weights ``[E, H, 2, I]`` / ``[E, I, H]``, or fp8 weights with per-row factors in
+    ``quantization_config``) map to the dense bf16 kernels, which also take ``PRE_SCALE`` (hidden rows multiplied
+    by the affinity before the first projection; CPU definition core/moe/moe_cte/moe_cte_torch.py:26-242).  The
+    sum over a token's blocks is always taken in fp32 and rounded once, whatever
+    ``is_tensor_update_accumulating`` says (with it off the reference lets the last block win, which is the same
+    thing whenever a token sits in one block only); ``compute_dtype`` other than bf16 is rejected.
     """
     _lib.kernel_assert(isinstance(spec, MoECTESpec), "spec must be a MoECTESpec")
-    _lib.kernel_assert(spec.implementation in _MX_IMPLEMENTATIONS,
-                       f"implementation {spec.implementation.name} is not available: only the MX variants are built")
+    _lib.kernel_assert(compute_dtype in (torch.bfloat16, None), "compute_dtype must be bfloat16")
     _lib.kernel_assert(gate_up_activations_T is None and down_activations is None,
-                       "activation checkpoint outputs are not supported by the MX variant")
-    _lib.kernel_assert(expert_affinities_scaling_mode in (ExpertAffinityScaleMode.POST_SCALE,
-                                                          ExpertAffinityScaleMode.NO_SCALE),
-                       "only POST_SCALE and NO_SCALE affinity scaling are supported")
+                       "activation checkpoint outputs (training) are not supported")
     _lib.kernel_assert(block_size % 128 == 0, f"block_size ({block_size}) must be a multiple of 128")
     _lib.require_cuda(hidden_states, expert_affinities_masked, token_position_to_id, block_to_expert, conditions)
+    if spec.implementation not in _MX_IMPLEMENTATIONS or isinstance(gate_up_proj_weight, DenseExpertWeights):
+        return _moe_cte_dense(hidden_states, expert_affinities_masked, gate_up_proj_weight, down_proj_weight,
+                              token_position_to_id, block_to_expert, block_size, spec, conditions,
+                              gate_and_up_proj_bias, down_proj_bias, quantization_config, activation_function, skip_dma,
+                              expert_affinities_scaling_mode, (gate_clamp_lower_limit, gate_clamp_upper_limit),
+                              (up_clamp_lower_limit, up_clamp_upper_limit), compat_lnc_slabs, _impl, _check_status)
+    _lib.kernel_assert(expert_affinities_scaling_mode in (ExpertAffinityScaleMode.POST_SCALE,
+                                                          ExpertAffinityScaleMode.NO_SCALE),
+                       "only POST_SCALE and NO_SCALE affinity scaling are supported by the MX variants")
 
     if isinstance(gate_up_proj_weight, ExpertWeights):
         weights = gate_up_proj_weight
@@ -154,6 +167,50 @@ def moe_cte(
     pipeline.run_blocks(hidden, hidden_rows, weights, tpi, b2e, conditions, block_size, aff, table, out,
                         activation_function.value, (gate_clamp_lower_limit, gate_clamp_upper_limit),
                         (up_clamp_lower_limit, up_clamp_upper_limit), _impl, _check_status)
+    if compat_lnc_slabs:
+        return torch.stack([out, torch.zeros_like(out)])
+    return out
+
+
+def _moe_cte_dense(hidden_states, expert_affinities_masked, gate_up_proj_weight, down_proj_weight, token_position_to_id,
+                   block_to_expert, block_size, spec, conditions, gate_and_up_proj_bias, down_proj_bias,
+                   quantization_config, activation_function, skip_dma, scaling_mode, gate_clamp, up_clamp,
+                   compat_lnc_slabs, impl, check_status):
+    """The non-MX implementations: bf16 (or fp8-row) weights through the dense contractions."""
+    if isinstance(gate_up_proj_weight, DenseExpertWeights):
+        weights = gate_up_proj_weight
+    else:
+        q = quantization_config or QuantizationConfig()
+        weights = prepare_dense_cached(gate_up_proj_weight, down_proj_weight, gate_and_up_proj_bias, down_proj_bias,
+                                       q.gate_up_proj_scale, q.down_proj_scale)
+    E, H = weights.E, weights.H
+    rows = hidden_states.shape[0]
+    hidden_rows = rows if skip_dma.skip_token else rows - 1
+    N = block_to_expert.numel()
+    b2e = block_to_expert.reshape(-1).to(torch.int32).contiguous()
+    tpi = token_position_to_id.reshape(-1).to(torch.int32).contiguous()
+    # only the hybrid implementation reads ``conditions``; the others run every block
+    if spec.implementation == MoECTEImplementation.shard_on_i_hybrid and conditions is not None:
+        conditions = conditions.reshape(-1).to(torch.int32).contiguous()
+        _lib.kernel_assert(conditions.numel() >= N, "conditions must cover every block")
+    else:
+        conditions = None
+    aff = None
+    pre_scale = scaling_mode in (ExpertAffinityScaleMode.PRE_SCALE, ExpertAffinityScaleMode.PRE_SCALE_DELAYED)
+    if scaling_mode != ExpertAffinityScaleMode.NO_SCALE:
+        aff = expert_affinities_masked.reshape(-1).contiguous()
+        if aff.dtype not in (torch.float32, torch.bfloat16):
+            aff = aff.float()
+        _lib.kernel_assert(aff.numel() >= hidden_rows * E, "expert_affinities_masked must hold rows * E values")
+    hidden = hidden_states.to(torch.bfloat16).contiguous()
+    out = torch.empty((rows, H), dtype=torch.bfloat16, device=hidden.device)
+    table = torch.empty((rows, E), dtype=torch.int32, device=hidden.device)
+    _lib.call("b200moe_build_position_table", _lib.ptr(tpi), _lib.ptr(b2e), _lib.ptr(conditions), N, block_size,
+              hidden_rows, E, _lib.ptr(table), _lib.stream_ptr())
+    if rows != hidden_rows:
+        table[hidden_rows:].fill_(-1)
+    pipeline.run_blocks_dense(hidden, hidden_rows, weights, tpi, b2e, conditions, block_size, aff, table, out,
+                              activation_function.value, gate_clamp, up_clamp, impl, check_status, pre_scale)
     if compat_lnc_slabs:
         return torch.stack([out, torch.zeros_like(out)])
     return out

@@ -9,7 +9,7 @@ from typing import Optional
 import torch
 
 from .... import _lib, pipeline
-from ....weights import ExpertWeights, prepare_from_nki_cached
+from ....weights import DenseExpertWeights, ExpertWeights, prepare_dense_cached, prepare_from_nki_cached
 from ...utils.common_types import ActFnType, ExpertAffinityScaleMode
 from ...utils.kernel_call import kernel_entry
 from ..moe_cte.group_tokens import moe_group_tokens
@@ -49,6 +49,7 @@ def moe_tkg(
     block_size: int = None,
     _impl: int = 0,
     _check_status: bool = False,
+    _prequantized=None,
 ) -> torch.Tensor:
     """Decode MoE expert layer, ``[T, H]`` in, ``[T, H]`` out.
 
@@ -61,9 +62,9 @@ def moe_tkg(
     ``is_all_expert_dynamic`` computes, per local expert, only the tokens whose masked affinity is non-zero.
     Weights are the reference's x4-packed MXFP8 tensors with their scales, or a
     prepared :class:`~nki_library_b200.weights.ExpertWeights` passed as
-    ``expert_gate_up_weights``.  Only the MX path exists; inputs that select the
-    bf16 / fp8-row paths, SBUF-resident tensors or pre-quantised hidden states
-    are rejected.
+    ``expert_gate_up_weights``.  Non-MX weights -- 4-D ``[E_L, H, 2, I]`` bf16, or fp8 with the per-row factors
+    ``[E_L, 2, I]`` / ``[E_L, H]`` in the two scale arguments -- run on the dense bf16 kernels.  SBUF-resident
+    tensors, pre-quantised hidden states and static (per-tensor input) quantisation are rejected.
     """
     A = _lib.kernel_assert
     A(not output_in_sbuf, f"{_PREFIX} output_in_sbuf has no meaning on a GPU")
@@ -87,7 +88,15 @@ def moe_tkg(
     A(T <= 128 or is_all_expert,
       f"{_PREFIX} Currently only batch size * seq len <= 128 is supported (except for all-expert mode)")
 
-    if isinstance(expert_gate_up_weights, ExpertWeights):
+    dense = isinstance(expert_gate_up_weights, DenseExpertWeights) or (
+        isinstance(expert_gate_up_weights, torch.Tensor) and expert_gate_up_weights.dim() == 4)
+    if dense:
+        # non-MX weights: bf16 [E_L, H, 2, I] / [E_L, I, H], or fp8 with per-row factors [E_L, 2, I] / [E_L, H]
+        # (core/moe/moe_tkg/all_expert_impl.py:65, selective_expert_impl.py:45; CPU definition moe_tkg_torch.py:226-290)
+        weights = expert_gate_up_weights if isinstance(expert_gate_up_weights, DenseExpertWeights) else \
+            prepare_dense_cached(expert_gate_up_weights, expert_down_weights, expert_gate_up_bias, expert_down_bias,
+                                 expert_gate_up_weights_scale, expert_down_weights_scale)
+    elif isinstance(expert_gate_up_weights, ExpertWeights):
         weights = expert_gate_up_weights
     else:
         A(expert_gate_up_weights_scale is not None and expert_down_weights_scale is not None,
@@ -113,9 +122,8 @@ def moe_tkg(
             aff = expert_affinities.contiguous()
             if aff.dtype not in (torch.float32, torch.bfloat16):
                 aff = aff.float()
-        pipeline.run_blocks(hidden, T, weights, g["token_position_to_id"], g["block_to_expert"], g["conditions"],
-                            _BLOCK, aff, g["inverse_map"], out, activation_fn.value, clamps[0], clamps[1], _impl,
-                            _check_status)
+        _run(weights, hidden, T, weights, g["token_position_to_id"], g["block_to_expert"], g["conditions"],
+             _BLOCK, aff, g["inverse_map"], out, activation_fn.value, clamps[0], clamps[1], _impl, _check_status)
     else:
         E = expert_affinities.shape[1]
         if post_scale:
@@ -145,17 +153,35 @@ def moe_tkg(
             _lib.call("b200moe_build_position_table", _lib.ptr(tpi), _lib.ptr(b2e), _lib.ptr(cond), n_blocks, _BLOCK,
                       T, E_L, _lib.ptr(table), _lib.stream_ptr())
         else:
-            n_sub = math.ceil(T / _BLOCK)
-            Tpad = n_sub * _BLOCK
-            ids = torch.full((Tpad,), -1, dtype=torch.int32, device=dev)
-            ids[:T] = torch.arange(T, dtype=torch.int32, device=dev)
-            tpi = ids.repeat(E_L)
-            b2e = torch.arange(E_L, dtype=torch.int32, device=dev).repeat_interleave(n_sub)
+            tpi, b2e, table = all_expert_layout(T, E_L, dev)
             cond = None
-            table = (torch.arange(E_L, dtype=torch.int32, device=dev)[None, :] * Tpad +
-                     torch.arange(T, dtype=torch.int32, device=dev)[:, None]).contiguous()
-        pipeline.run_blocks(hidden, T, weights, tpi, b2e, cond, _BLOCK, aff if post_scale else None, table, out,
-                            activation_fn.value, clamps[0], clamps[1], _impl, _check_status)
+        kw = {}
+        if _prequantized is not None and not is_all_expert_dynamic and not dense:
+            # the caller (moe_block_tkg) has run the fused RMSNorm + quantise kernel into this workspace
+            kw = dict(workspace=_prequantized, prequantized=True)
+        _run(weights, hidden, T, weights, tpi, b2e, cond, _BLOCK, aff if post_scale else None, table, out,
+             activation_fn.value, clamps[0], clamps[1], _impl, _check_status, **kw)
     if output_dtype is not None and output_dtype != torch.bfloat16:
         return out.to(output_dtype)
     return out
+
+
+def all_expert_layout(T: int, E_L: int, device):
+    """Static block layout of the all-expert mode: every local expert owns ceil(T / 128) blocks that hold tokens
+    0..T-1 in order.  Returns ``(token_position_to_id, block_to_expert, table [T, E_L])``."""
+    n_sub = math.ceil(T / _BLOCK)
+    Tpad = n_sub * _BLOCK
+    ids = torch.full((Tpad,), -1, dtype=torch.int32, device=device)
+    ids[:T] = torch.arange(T, dtype=torch.int32, device=device)
+    tpi = ids.repeat(E_L)
+    b2e = torch.arange(E_L, dtype=torch.int32, device=device).repeat_interleave(n_sub)
+    table = (torch.arange(E_L, dtype=torch.int32, device=device)[None, :] * Tpad +
+             torch.arange(T, dtype=torch.int32, device=device)[:, None]).contiguous()
+    return tpi, b2e, table
+
+
+def _run(weights, *args, **kw):
+    """MX weights go through the block-scaled kernels, dense weights through the bf16 ones."""
+    if isinstance(weights, DenseExpertWeights):
+        return pipeline.run_blocks_dense(*args, **kw)
+    return pipeline.run_blocks(*args, **kw)

@@ -7,8 +7,11 @@ from typing import Optional
 
 import torch
 
-from ... import _lib
-from ..moe.moe_tkg.moe_tkg import moe_tkg
+import math
+
+from ... import _lib, pipeline
+from ...weights import ExpertWeights, prepare_from_nki_cached
+from ..moe.moe_tkg.moe_tkg import all_expert_layout, moe_tkg
 from ..router_topk.router_topk import router_topk
 from ..utils.common_types import ActFnType, ExpertAffinityScaleMode, RouterActFnType
 from ..utils.kernel_call import kernel_entry
@@ -79,9 +82,32 @@ def moe_block_tkg(
         A(g.numel() == H, "gamma must have H elements")
     normed = torch.empty_like(x)
     residual_out = torch.empty_like(x) if res is not None else None
-    _lib.call("b200moe_rmsnorm", _lib.ptr(x), _lib.ptr(res), _lib.ptr(g), _lib.F32 if g is None else _lib.dtype_code(g),
-              T, H, 0 if hidden_actual is None else int(hidden_actual), float(eps), _lib.ptr(normed),
-              _lib.ptr(residual_out), _lib.stream_ptr())
+    g_code = _lib.F32 if g is None else _lib.dtype_code(g)
+    h_act = 0 if hidden_actual is None else int(hidden_actual)
+    # MX weights in all-expert mode: every token's positions are known before the router runs (token t sits at
+    # position e * T_pad + t of every local expert), so the normalised rows are quantised by the kernel that
+    # produces them -- the reference's rmsnorm_mx_quantize_tkg step (moe_block_tkg.py:199-218)
+    prequantized = None
+    mx_weights = isinstance(expert_gate_up_weights, ExpertWeights) or (
+        isinstance(expert_gate_up_weights, torch.Tensor) and expert_gate_up_weights.dim() == 5)
+    if is_all_expert and mx_weights and H % 128 == 0:
+        if not isinstance(expert_gate_up_weights, ExpertWeights):
+            A(expert_gate_up_weights_scale is not None and expert_down_weights_scale is not None,
+              "Scales must be set when using MX weights")
+            expert_gate_up_weights = prepare_from_nki_cached(
+                expert_gate_up_weights, expert_gate_up_weights_scale, expert_down_weights, expert_down_weights_scale,
+                expert_gate_up_bias, expert_down_bias)
+        w = expert_gate_up_weights
+        _, _, table = all_expert_layout(T, w.E, x.device)
+        n_pos = w.E * math.ceil(T / 128) * 128
+        prequantized = pipeline.get_workspace(n_pos, H, w.I, x.device)
+        _lib.call("b200moe_rmsnorm_quantize_mxfp8", _lib.ptr(x), _lib.ptr(res), _lib.ptr(g), g_code, T, H, h_act,
+                  float(eps), _lib.ptr(normed), _lib.ptr(residual_out), _lib.ptr(table), table.shape[1], n_pos,
+                  int(w.h_packed_order), _lib.ptr(prequantized.xq), _lib.ptr(prequantized.x_sf),
+                  _lib.ptr(prequantized.tile_flags), _lib.stream_ptr())
+    else:
+        _lib.call("b200moe_rmsnorm", _lib.ptr(x), _lib.ptr(res), _lib.ptr(g), g_code, T, H, h_act, float(eps),
+                  _lib.ptr(normed), _lib.ptr(residual_out), _lib.stream_ptr())
 
     E = router_weights.shape[1]
     logits = torch.empty((T, E), dtype=torch.float32, device=x.device)
@@ -95,7 +121,8 @@ def moe_block_tkg(
                   expert_down_weights_scale=expert_down_weights_scale, mask_unselected_experts=router_pre_norm,
                   expert_affinities_scaling_mode=expert_affinities_scaling_mode, activation_fn=hidden_act_fn,
                   gate_clamp_upper_limit=gate_clamp_upper_limit, gate_clamp_lower_limit=gate_clamp_lower_limit,
-                  up_clamp_upper_limit=up_clamp_upper_limit, up_clamp_lower_limit=up_clamp_lower_limit)
+                  up_clamp_upper_limit=up_clamp_upper_limit, up_clamp_lower_limit=up_clamp_lower_limit,
+                  _prequantized=prequantized)
     outputs = [out]
     if not skip_router_logits:
         outputs.append(logits)

@@ -68,6 +68,8 @@ struct GemmParams {
   void* peer_out[8];
   int32_t* status;
   unsigned long long* clock_probe;  // optional: CTA 0 writes {SM cycles, nanoseconds} spent in the kernel
+  const float* col_scale;  // dense (bf16) variant: per-expert, per-weight-row dequantisation factors [E, n_total]
+                           // of fp8-row weights (NULL = none), applied to the accumulator before the bias
   int w_format;     // element format of the weight operand (B200MOE_W_*); activations are e4m3
   uint32_t b_tx;    // bytes one weight-tile copy reports to its mbarrier
   int early_successor;  // 1: let the next launch in the stream begin as soon as SMs free up (it touches other rows)
@@ -239,7 +241,11 @@ struct SmemLayout {
   static constexpr int kBytes = kOffSched + static_cast<int>(sizeof(Sched)) + 1024;  // + alignment slack
 };
 
-template <int BLOCK_N, int STAGES, int EPI, int CTAS>
+// KIND 0: MXFP8 activations x MX weights, block-scaled MMAs (kind::mxf8f6f4.block_scale).
+// KIND 1: bf16 activations x bf16 weights (kind::f16), the reference's non-MX variants: no scale atoms travel, the
+//         four scale-mover warps idle, the gate/up epilogue writes bf16 intermediates instead of MX codes.  Operand
+//         rows are addressed in bytes, so a 128-byte slab is 64 bf16 elements = four K = 16 MMAs.
+template <int BLOCK_N, int STAGES, int EPI, int CTAS, int KIND = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64,
                           const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_b,
@@ -252,10 +258,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   constexpr int kAcc = (BLOCK_N <= 128) ? 2 : 1;
   constexpr int kSfCol = kAcc * BLOCK_N;  // TMEM columns: accumulators, then SFA (4), then SFB
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kIdesc = make_idesc(kBlockM * CTAS, BLOCK_N);
+  constexpr uint32_t kIdesc = KIND == 0 ? make_idesc(kBlockM * CTAS, BLOCK_N) : make_idesc_bf16(kBlockM * CTAS, BLOCK_N);
   // operand bytes per stage (scale atoms report to sf_full) depend on the tile: short activation boxes, and
   // 4-bit weights that land in the same padded 128-byte rows but report their packed size
-  const uint32_t idesc_base = kIdesc | (static_cast<uint32_t>(p.w_format) << 10);
+  const uint32_t idesc_base = KIND == 0 ? (kIdesc | (static_cast<uint32_t>(p.w_format) << 10)) : kIdesc;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -348,12 +354,14 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
           // scale atoms of this CTA's rows and of the whole weight tile -> this CTA's own barrier
           // (rows past the end of the atom table read as zero and still count their bytes)
-          mbar_expect_tx(&sf_full[stage], L::kSfa + L::kSfb);
-          tma_load_2d(smem + L::kOffSfa + stage * L::kSfa, &tmap_sfa, 0, m_tile * p.k_blocks + kb, &sf_full[stage]);
+          if constexpr (KIND == 0) {
+            mbar_expect_tx(&sf_full[stage], L::kSfa + L::kSfb);
+            tma_load_2d(smem + L::kOffSfa + stage * L::kSfa, &tmap_sfa, 0, m_tile * p.k_blocks + kb, &sf_full[stage]);
 #pragma unroll
-          for (int j = 0; j < L::kSfbAtoms; ++j)
-            tma_load_2d(smem + L::kOffSfb + stage * L::kSfb + j * 512, &tmap_sfb, 0,
-                        (e * p.b_row_atoms + atom0 + j) * p.k_blocks + kb, &sf_full[stage]);
+            for (int j = 0; j < L::kSfbAtoms; ++j)
+              tma_load_2d(smem + L::kOffSfb + stage * L::kSfb + j * 512, &tmap_sfb, 0,
+                          (e * p.b_row_atoms + atom0 + j) * p.k_blocks + kb, &sf_full[stage]);
+          }
           if constexpr (CTAS == 2) {
             // operand tiles of both CTAs complete on the even CTA's barrier
             if (cta_rank == 0) mbar_expect_tx(&full[stage], stage_bytes);
@@ -395,7 +403,8 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                                               : idesc_base;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
-          if (!mbar_wait(&sf_ready[stage], phase, abort_flag, p.status, 5)) { ok = false; break; }
+          if constexpr (KIND == 0)
+            if (!mbar_wait(&sf_ready[stage], phase, abort_flag, p.status, 5)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sfa_tmem = tmem_base + kSfCol + stage * 16;
           const uint32_t sfb_tmem = sfa_tmem + 4 + sfb_off;
@@ -403,11 +412,16 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           const uint64_t b_desc = desc_sw128(smem_u32(smem + L::kOffB + stage * L::kB));
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint32_t idesc = idesc_tile | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
-            if constexpr (CTAS == 2)
-              tc2_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
-            else
-              tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (KIND == 0) {
+              const uint32_t idesc = idesc_tile | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
+              if constexpr (CTAS == 2)
+                tc2_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
+              else
+                tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0 ? 1u : 0u);
+            } else {
+              if constexpr (CTAS == 2) tc2_mma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc_tile, (kb | k) != 0 ? 1u : 0u);
+              else tc_mma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc_tile, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           if constexpr (CTAS == 2) tc2_commit_pair(&empty[stage]);
           else tc_commit(&empty[stage]);
@@ -430,7 +444,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
+    for (int tile = unit; KIND == 0 && tile < total_tiles && ok; tile += n_units) {
       int m_tile, n_tile, e, second, part;
       if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) continue;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -504,6 +518,13 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           float g[32], u[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) { g[j] = __uint_as_float(raw[2 * c][j]); u[j] = __uint_as_float(raw[2 * c + 1][j]); }
+          if constexpr (KIND == 1) {
+            if (p.col_scale != nullptr) {
+              const float* cs = p.col_scale + static_cast<int64_t>(e) * p.n_total + n0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) { g[j] *= cs[j]; u[j] *= cs[32 + j]; }
+            }
+          }
           if (bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) { g[j] += bias[n0 + j]; u[j] += bias[n0 + 32 + j]; }
@@ -531,6 +552,19 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               g[j] = m;
               mx = max(mx, __float_as_uint(m) & 0x7fffffffu);
             }
+          }
+          if constexpr (KIND == 1) {
+            // dense variant: the intermediate stays bf16 (the next contraction's operand type)
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const __nv_bfloat162 b2 = __floats2bfloat162_rn(g[2 * j], g[2 * j + 1]);
+              o[j] = *reinterpret_cast<const uint32_t*>(&b2);
+            }
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.m_codes) + row * p.I + i0;
+            st_global_256(dst, o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]);
+            st_global_256(dst + 16, o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]);
+            continue;
           }
           uint32_t w[8];
           const int e_max = static_cast<int>(mx >> 23);
@@ -564,6 +598,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           aff = load_as_float(p.aff, p.aff_per_row ? static_cast<int64_t>(tok) : static_cast<int64_t>(tok) * p.E + e,
                               p.aff_dtype);
         const float* bias = p.bias ? p.bias + static_cast<int64_t>(e) * p.H_out : nullptr;
+        const float* cs = (KIND == 1 && p.col_scale) ? p.col_scale + static_cast<int64_t>(e) * p.H_out : nullptr;
 #pragma unroll
         for (int l = 0; l < kLd; ++l) {
           const int col0 = n_row0 + half * kCW + l * 32;
@@ -572,6 +607,7 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             float a0 = __uint_as_float(raw[l][2 * j]), a1 = __uint_as_float(raw[l][2 * j + 1]);
+            if (cs) { a0 *= cs[col0 + 2 * j]; a1 *= cs[col0 + 2 * j + 1]; }
             if (bias) { a0 += bias[col0 + 2 * j]; a1 += bias[col0 + 2 * j + 1]; }
             const __nv_bfloat162 b2 = __floats2bfloat162_rn(a0 * aff, a1 * aff);
             o[j] = *reinterpret_cast<const uint32_t*>(&b2);
@@ -724,6 +760,66 @@ __global__ void simt_gemm2_kernel(const uint8_t* m, const uint8_t* w, GemmParams
   }
 }
 
+// Dense (bf16 x bf16) counterparts of the two validation kernels: one thread per output element.
+__device__ float dense_dot(const __nv_bfloat16* a, const __nv_bfloat16* b, int K) {
+  float acc = 0.f;
+  for (int k = 0; k < K; ++k) acc += __bfloat162float(a[k]) * __bfloat162float(b[k]);
+  return acc;
+}
+
+__global__ void simt_dense_gemm1_kernel(const __nv_bfloat16* x, const __nv_bfloat16* w, GemmParams p, int K) {
+  const int64_t total = static_cast<int64_t>(p.m_tiles_total) * 128 * p.I;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int i = static_cast<int>(idx % p.I);
+    const int64_t row = idx / p.I;
+    const int m_tile = static_cast<int>(row >> 7);
+    const int block = m_tile / (p.B >> 7);
+    if (!block_is_active(p, block)) continue;
+    if (p.tile_flags && p.tile_flags[m_tile] == 0) continue;
+    const int e = p.block_to_expert[block];
+    if (e < 0 || e >= p.E) continue;
+    const int n_g = (i >> 5) * 64 + (i & 31), n_u = n_g + 32;
+    const __nv_bfloat16* we = w + static_cast<int64_t>(e) * p.n_total * K;
+    float gv = dense_dot(x + row * K, we + static_cast<int64_t>(n_g) * K, K);
+    float uv = dense_dot(x + row * K, we + static_cast<int64_t>(n_u) * K, K);
+    if (p.col_scale) {
+      gv *= p.col_scale[static_cast<int64_t>(e) * p.n_total + n_g];
+      uv *= p.col_scale[static_cast<int64_t>(e) * p.n_total + n_u];
+    }
+    if (p.bias) { gv += p.bias[static_cast<int64_t>(e) * p.n_total + n_g]; uv += p.bias[static_cast<int64_t>(e) * p.n_total + n_u]; }
+    if (p.gate_lo == p.gate_lo) gv = fmaxf(gv, p.gate_lo);
+    if (p.gate_hi == p.gate_hi) gv = fminf(gv, p.gate_hi);
+    if (p.up_lo == p.up_lo) uv = fmaxf(uv, p.up_lo);
+    if (p.up_hi == p.up_hi) uv = fminf(uv, p.up_hi);
+    reinterpret_cast<__nv_bfloat16*>(p.m_codes)[row * p.I + i] = __float2bfloat16_rn(apply_act(gv, p.act) * uv);
+  }
+}
+
+__global__ void simt_dense_gemm2_kernel(const __nv_bfloat16* m, const __nv_bfloat16* w, GemmParams p, int K) {
+  const int64_t total = static_cast<int64_t>(p.m_tiles_total) * 128 * p.H_out;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int h = static_cast<int>(idx % p.H_out);
+    const int64_t row = idx / p.H_out;
+    const int m_tile = static_cast<int>(row >> 7);
+    const int block = m_tile / (p.B >> 7);
+    if (!block_is_active(p, block)) continue;
+    if (p.tile_flags && p.tile_flags[m_tile] == 0) continue;
+    const int e = p.block_to_expert[block];
+    if (e < 0 || e >= p.E) continue;
+    const int tok = p.tpi ? p.tpi[row] : static_cast<int>(row);
+    if (tok < 0 || tok >= p.hidden_rows) continue;
+    float y = dense_dot(m + row * K, w + (static_cast<int64_t>(e) * p.n_total + h) * K, K);
+    if (p.col_scale) y *= p.col_scale[static_cast<int64_t>(e) * p.H_out + h];
+    if (p.bias) y += p.bias[static_cast<int64_t>(e) * p.H_out + h];
+    if (p.aff)
+      y *= load_as_float(p.aff, p.aff_per_row ? static_cast<int64_t>(tok) : static_cast<int64_t>(tok) * p.E + e,
+                         p.aff_dtype);
+    p.y_pos[row * p.H_out + h] = __float2bfloat16_rn(y);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 // Rows of K elements, one byte each, or (nibbles) two per byte: the 4-bit map type expands every 8 packed
 // bytes to a 16-byte shared-memory chunk, which is the padded form the f8f6f4 MMA reads 4-bit operands in,
@@ -762,11 +858,11 @@ int make_atoms_map(CUtensorMap* map, const void* base, int64_t n_atoms) {
   return B200MOE_OK;
 }
 
-template <int BLOCK_N, int STAGES, int EPI, int CTAS>
+template <int BLOCK_N, int STAGES, int EPI, int CTAS, int KIND = 0>
 int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorMap& mb128, const CUtensorMap& msa,
               const CUtensorMap& msb, const GemmParams& p, cudaStream_t st, bool overlap_predecessor = false) {
   using L = SmemLayout<BLOCK_N, STAGES, CTAS>;
-  auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI, CTAS>;
+  auto kern = grouped_mxfp8_gemm_kernel<BLOCK_N, STAGES, EPI, CTAS, KIND>;
   B200MOE_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kBytes));
   // only sizes the grid; a left-over launch has at most one tile per expert and weight tile
   const int total = p.tile_filter == 2 ? p.E * p.n_tiles : ((p.m_tiles_total + CTAS - 1) / CTAS) * p.n_tiles;
@@ -808,8 +904,10 @@ int launch_tc(const CUtensorMap (&ma)[3], const CUtensorMap& mb, const CUtensorM
 
 // `impl` is the per-call variant word of the entry points: bit 0 selects the CUDA-core validation kernels, the
 // B200MOE_GEMM_* bits restrict the tile shapes the tensor-core path may pick.  Nothing here is process state.
+// `kind`: 0 = MX (a and b are element codes, K counts elements = bytes, or nibbles for e2m1 weights); 1 = dense
+// bf16 operands (K counts bf16 elements; the copies address rows in bytes).
 int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, int impl, void* clock_probe,
-             cudaStream_t st) {
+             cudaStream_t st, int kind = 0) {
   B200MOE_REQUIRE((impl & ~(B200MOE_IMPL_SIMT | B200MOE_GEMM_TILE_N128 | B200MOE_GEMM_NO_PAIR | B200MOE_GEMM_FORCE_PAIR |
                             B200MOE_GEMM_NO_SPLIT | B200MOE_GEMM_NO_OVERLAP)) == 0,
                   B200MOE_ERR_INVALID, "unknown bits in the variant word 0x%x", impl);
@@ -817,6 +915,8 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
                   "the clock probe buffer must be 8-byte aligned");
   B200MOE_REQUIRE(p.B > 0 && p.B % 128 == 0, B200MOE_ERR_INVALID, "block size must be a multiple of 128, got %d", p.B);
   B200MOE_REQUIRE(K % 32 == 0 && K >= 32, B200MOE_ERR_INVALID, "contraction length must be a multiple of 32, got %d", K);
+  B200MOE_REQUIRE(kind == 0 || !(impl & B200MOE_GEMM_TILE_N128), B200MOE_ERR_INVALID,
+                  "the dense contraction has no 128-row weight tile");
   B200MOE_REQUIRE(p.n_blocks > 0 && p.E > 0 && p.E <= kMaxExperts, B200MOE_ERR_INVALID,
                   "need at least one block and between 1 and %d experts", kMaxExperts);
   B200MOE_REQUIRE(p.status != nullptr, B200MOE_ERR_INVALID, "status pointer must not be null");
@@ -827,7 +927,8 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
                   "e2m1 weights need a contraction length that is a multiple of 128, got %d", K);
   p.m_tiles_total = p.n_blocks * (p.B / 128);
   p.clock_probe = static_cast<unsigned long long*>(clock_probe);
-  p.k_blocks = (K + kBlockK - 1) / kBlockK;
+  const int Kb = kind == 1 ? 2 * K : K;  // row pitch the copies see, in element-code bytes
+  p.k_blocks = (Kb + kBlockK - 1) / kBlockK;
   p.b_row_atoms = (p.n_total + 127) / 128;
   p.b_sf_expert_stride = static_cast<int64_t>(p.b_row_atoms) * p.k_blocks * 512;
   B200MOE_CUDA_OK(cudaMemsetAsync(p.status, 0, 4, st));
@@ -836,7 +937,12 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
                                   : static_cast<int64_t>(p.m_tiles_total) * 128 * p.H_out;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
     const int grid = static_cast<int>(ceil_div64(work, 128) < cap ? ceil_div64(work, 128) : cap);
-    if (epi == 0) simt_gemm1_kernel<<<grid, 128, 0, st>>>(a, b, p, K);
+    if (kind == 1) {
+      const auto* ab = reinterpret_cast<const __nv_bfloat16*>(a);
+      const auto* bb = reinterpret_cast<const __nv_bfloat16*>(b);
+      if (epi == 0) simt_dense_gemm1_kernel<<<grid, 128, 0, st>>>(ab, bb, p, K);
+      else simt_dense_gemm2_kernel<<<grid, 128, 0, st>>>(ab, bb, p, K);
+    } else if (epi == 0) simt_gemm1_kernel<<<grid, 128, 0, st>>>(a, b, p, K);
     else simt_gemm2_kernel<<<grid, 128, 0, st>>>(a, b, p, K);
     B200MOE_LAUNCH_OK("simt_gemm_kernel");
     return B200MOE_OK;
@@ -854,25 +960,33 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
   CUtensorMap ma[3], mb, mb128, msa, msb;  // activation boxes of 128, 64 and 32 rows; weight boxes: tile, 128 rows
   int rc = B200MOE_OK;
   for (int i = 0; i < 3 && rc == B200MOE_OK; ++i)
-    rc = make_rows_map(&ma[i], a, K, static_cast<int64_t>(p.m_tiles_total) * 128, 0, kBlockM >> i);
+    rc = make_rows_map(&ma[i], a, Kb, static_cast<int64_t>(p.m_tiles_total) * 128, 0, kBlockM >> i);
   if (rc != B200MOE_OK) return rc;
-  rc = make_rows_map(&mb, b, K, p.n_total, p.E, pair ? bn / 2 : bn, nibbles);
+  rc = make_rows_map(&mb, b, Kb, p.n_total, p.E, pair ? bn / 2 : bn, nibbles);
   // the copy reports the bytes it read from global memory: a 4-bit slab is 64 bytes per row there
   p.b_tx = static_cast<uint32_t>((pair ? bn / 2 : bn) * (nibbles ? kBlockK / 2 : kBlockK));
   if (rc != B200MOE_OK) return rc;
-  rc = make_rows_map(&mb128, b, K, p.n_total, p.E, 128, nibbles);  // half tiles of the single-CTA launches
+  rc = make_rows_map(&mb128, b, Kb, p.n_total, p.E, 128, nibbles);  // half tiles of the single-CTA launches
   if (rc != B200MOE_OK) return rc;
-  rc = make_atoms_map(&msa, p.a_sf, static_cast<int64_t>(p.m_tiles_total) * p.k_blocks);
-  if (rc != B200MOE_OK) return rc;
-  rc = make_atoms_map(&msb, p.b_sf, static_cast<int64_t>(p.E) * p.b_row_atoms * p.k_blocks);
-  if (rc != B200MOE_OK) return rc;
+  if (kind == 0) {
+    rc = make_atoms_map(&msa, p.a_sf, static_cast<int64_t>(p.m_tiles_total) * p.k_blocks);
+    if (rc != B200MOE_OK) return rc;
+    rc = make_atoms_map(&msb, p.b_sf, static_cast<int64_t>(p.E) * p.b_row_atoms * p.k_blocks);
+    if (rc != B200MOE_OK) return rc;
+  } else {
+    msa = msb = ma[0];  // never dereferenced by the dense kernel
+  }
   if (pair) {
     // Two launches: the CTA-pair kernel walks the pairs of live 128-row tiles, the single-CTA kernel the one
     // tile an expert with an odd number of live tiles has left over (a half-empty pair would pay for a full
     // 256-row MMA: with ~1000 rows per expert that was one tile in five).
     p.tile_filter = split_leftover ? 1 : 0;
     p.early_successor = (split_leftover && overlap_leftover) ? 1 : 0;
-    rc = epi == 0 ? launch_tc<256, 6, 0, 2>(ma, mb, mb128, msa, msb, p, st) : launch_tc<256, 6, 1, 2>(ma, mb, mb128, msa, msb, p, st);
+    if (kind == 1)
+      rc = epi == 0 ? launch_tc<256, 6, 0, 2, 1>(ma, mb, mb128, msa, msb, p, st)
+                    : launch_tc<256, 6, 1, 2, 1>(ma, mb, mb128, msa, msb, p, st);
+    else
+      rc = epi == 0 ? launch_tc<256, 6, 0, 2>(ma, mb, mb128, msa, msb, p, st) : launch_tc<256, 6, 1, 2>(ma, mb, mb128, msa, msb, p, st);
     if (rc != B200MOE_OK || !split_leftover) return rc;
     GemmParams p2 = p;
     p2.tile_filter = 2;
@@ -881,12 +995,18 @@ int run_gemm(int epi, const uint8_t* a, const uint8_t* b, GemmParams& p, int K, 
     p2.clock_probe = nullptr;
     p2.b_tx = static_cast<uint32_t>(bn * (nibbles ? kBlockK / 2 : kBlockK));
     CUtensorMap mb2;
-    rc = make_rows_map(&mb2, b, K, p.n_total, p.E, bn, nibbles);
+    rc = make_rows_map(&mb2, b, Kb, p.n_total, p.E, bn, nibbles);
     if (rc != B200MOE_OK) return rc;
     const bool ov = overlap_leftover;
+    if (kind == 1)
+      return epi == 0 ? launch_tc<256, 4, 0, 1, 1>(ma, mb2, mb128, msa, msb, p2, st, ov)
+                      : launch_tc<256, 4, 1, 1, 1>(ma, mb2, mb128, msa, msb, p2, st, ov);
     return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb2, mb128, msa, msb, p2, st, ov)
                     : launch_tc<256, 4, 1, 1>(ma, mb2, mb128, msa, msb, p2, st, ov);
   }
+  if (kind == 1)
+    return epi == 0 ? launch_tc<256, 4, 0, 1, 1>(ma, mb, mb128, msa, msb, p, st)
+                    : launch_tc<256, 4, 1, 1, 1>(ma, mb, mb128, msa, msb, p, st);
   if (bn == 256)
     return epi == 0 ? launch_tc<256, 4, 0, 1>(ma, mb, mb128, msa, msb, p, st) : launch_tc<256, 4, 1, 1>(ma, mb, mb128, msa, msb, p, st);
   return epi == 0 ? launch_tc<128, 6, 0, 1>(ma, mb, mb128, msa, msb, p, st) : launch_tc<128, 6, 1, 1>(ma, mb, mb128, msa, msb, p, st);
@@ -1013,3 +1133,76 @@ extern "C" int b200moe_ep_gemm2_scale_return(const uint8_t* m_codes, const uint8
                     row_src, back_peers, world, back_rows, status, impl, nullptr, stream);
 }
 
+
+// ---- dense (bf16) variants: the reference's non-MX expert kernels ------------------------------------------------
+extern "C" int b200moe_dense_gemm1_swiglu(const void* x_bf16, const void* w1_bf16, const float* w1_col_scale,
+                                          const float* bias_gu_dev, const int32_t* block_to_expert,
+                                          const int32_t* conditions, const int32_t* tile_flags, int n_blocks, int B,
+                                          int E, int H, int I, int act_fn, float gate_lo, float gate_hi, float up_lo,
+                                          float up_hi, void* m_bf16, int32_t* status, int impl,
+                                          b200moe_stream_t stream) {
+  B200MOE_REQUIRE(x_bf16 && w1_bf16 && block_to_expert && m_bf16, B200MOE_ERR_INVALID,
+                  "dense_gemm1: null pointer argument");
+  B200MOE_REQUIRE(I % 32 == 0 && I > 0 && H % 32 == 0 && H > 0, B200MOE_ERR_INVALID,
+                  "dense_gemm1: H and I must be positive multiples of 32 (H = %d, I = %d)", H, I);
+  B200MOE_REQUIRE(act_fn >= 0 && act_fn <= 3, B200MOE_ERR_INVALID, "dense_gemm1: unknown activation %d", act_fn);
+  B200MOE_REQUIRE((reinterpret_cast<uintptr_t>(m_bf16) & 31) == 0, B200MOE_ERR_INVALID,
+                  "dense_gemm1: the intermediate buffer must be 32-byte aligned");
+  GemmParams p{};
+  p.block_to_expert = block_to_expert;
+  p.conditions = conditions;
+  p.tile_flags = tile_flags;
+  p.n_blocks = n_blocks;
+  p.B = B;
+  p.E = E;
+  p.n_total = 2 * I;
+  p.bias = bias_gu_dev;
+  p.col_scale = w1_col_scale;
+  p.act = act_fn;
+  p.gate_lo = gate_lo;
+  p.gate_hi = gate_hi;
+  p.up_lo = up_lo;
+  p.up_hi = up_hi;
+  p.m_codes = static_cast<uint8_t*>(m_bf16);
+  p.I = I;
+  p.status = status;
+  return run_gemm(0, static_cast<const uint8_t*>(x_bf16), static_cast<const uint8_t*>(w1_bf16), p, H, impl, nullptr,
+                  static_cast<cudaStream_t>(stream), 1);
+}
+
+extern "C" int b200moe_dense_gemm2_scale(const void* m_bf16, const void* w2_bf16, const float* w2_col_scale,
+                                         const float* bias_d, const int32_t* block_to_expert,
+                                         const int32_t* conditions, const int32_t* tile_flags,
+                                         const int32_t* token_position_to_id, int hidden_rows, int n_blocks, int B,
+                                         int E, int H, int I, const void* affinities, int aff_dtype, int aff_per_row,
+                                         void* y_pos_bf16, int32_t* status, int impl, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(m_bf16 && w2_bf16 && block_to_expert && y_pos_bf16, B200MOE_ERR_INVALID,
+                  "dense_gemm2: null pointer argument");
+  B200MOE_REQUIRE(H % 32 == 0 && H > 0 && I % 32 == 0 && I > 0, B200MOE_ERR_INVALID,
+                  "dense_gemm2: H and I must be positive multiples of 32 (H = %d, I = %d)", H, I);
+  B200MOE_REQUIRE(aff_dtype == B200MOE_F32 || aff_dtype == B200MOE_BF16, B200MOE_ERR_INVALID,
+                  "dense_gemm2: affinities must be fp32 or bf16");
+  B200MOE_REQUIRE((reinterpret_cast<uintptr_t>(y_pos_bf16) & 31) == 0, B200MOE_ERR_INVALID,
+                  "dense_gemm2: y_pos must be 32-byte aligned");
+  GemmParams p{};
+  p.block_to_expert = block_to_expert;
+  p.conditions = conditions;
+  p.tile_flags = tile_flags;
+  p.tpi = token_position_to_id;
+  p.hidden_rows = hidden_rows;
+  p.n_blocks = n_blocks;
+  p.B = B;
+  p.E = E;
+  p.n_total = H;
+  p.bias = bias_d;
+  p.col_scale = w2_col_scale;
+  p.aff = affinities;
+  p.aff_dtype = aff_dtype;
+  p.aff_per_row = aff_per_row;
+  p.y_pos = static_cast<__nv_bfloat16*>(y_pos_bf16);
+  p.H_out = H;
+  p.I = I;
+  p.status = status;
+  return run_gemm(1, static_cast<const uint8_t*>(m_bf16), static_cast<const uint8_t*>(w2_bf16), p, I, impl, nullptr,
+                  static_cast<cudaStream_t>(stream), 1);
+}

@@ -172,6 +172,50 @@ __global__ void __launch_bounds__(256) scatter_quantize_kernel(const __nv_bfloat
   }
 }
 
+// Dense (non-MX) variants: the token's bf16 row is copied to its positions as it is, or multiplied by the affinity
+// of the position's expert first (the reference's PRE_SCALE mode scales the hidden rows before the first
+// projection, core/moe/moe_cte/moe_cte_torch.py:151-155).  One warp per token, 16-byte accesses.
+__global__ void __launch_bounds__(256) scatter_rows_bf16_kernel(const __nv_bfloat16* __restrict__ hidden, int T, int H,
+                                                                const int32_t* __restrict__ table, int K, int64_t n_pos,
+                                                                const int32_t* __restrict__ block_to_expert, int B, int E,
+                                                                const void* __restrict__ aff, int aff_dtype,
+                                                                __nv_bfloat16* __restrict__ out,
+                                                                int32_t* __restrict__ tile_flags) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int32_t* my_map = table + static_cast<int64_t>(t) * K;
+  const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<int64_t>(t) * H);
+  const int vecs = H >> 3;
+  for (int k = 0; k < K; ++k) {
+    const int64_t p = my_map[k];
+    if (p < 0 || p >= n_pos) continue;  // uniform across the warp
+    if (tile_flags != nullptr && lane == 0) atomicMax(&tile_flags[p >> 7], static_cast<int>(p & 127) + 1);
+    float a = 1.0f;
+    if (aff != nullptr) {
+      const int e = block_to_expert[p / B];
+      a = (e >= 0 && e < E) ? load_as_float(aff, static_cast<int64_t>(t) * E + e, aff_dtype) : 0.0f;
+      a = __bfloat162float(__float2bfloat16_rn(a));  // the reference casts the affinity to the hidden dtype first
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + p * H);
+    for (int v = lane; v < vecs; v += 32) {
+      uint4 raw = __ldg(src + v);
+      if (aff != nullptr) {
+        float f[8];
+        unpack8_bf16(raw, f);
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(f[2 * i] * a, f[2 * i + 1] * a);
+          o[i] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+        raw = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      dst[v] = raw;
+    }
+  }
+}
+
 // ---- weight relayout ---------------------------------------------------------
 // Destination row of gate/up source row (s = 0 gate / 1 up, i): 32 gate rows then
 // the matching 32 up rows.
@@ -371,6 +415,26 @@ extern "C" int b200moe_scatter_quantize_mxfp8(const void* hidden_bf16, int T, in
       static_cast<const __nv_bfloat16*>(hidden_bf16), T, H, inverse_map, K, n_pos, h_packed_order, codes, sf_atoms,
       tile_flags);
   B200MOE_LAUNCH_OK("scatter_quantize_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_scatter_rows_bf16(const void* hidden_bf16, int T, int H, const int32_t* table, int K,
+                                         int64_t n_pos, const int32_t* block_to_expert, int B, int E,
+                                         const void* pre_scale_affinities, int aff_dtype, void* out_bf16,
+                                         int32_t* tile_flags, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(hidden_bf16 && table && out_bf16, B200MOE_ERR_INVALID, "scatter_rows: null pointer argument");
+  B200MOE_REQUIRE(T > 0 && H > 0 && H % 8 == 0 && n_pos > 0 && K >= 1, B200MOE_ERR_INVALID,
+                  "scatter_rows: T, K, n_pos must be positive and H a positive multiple of 8 (H = %d)", H);
+  B200MOE_REQUIRE(pre_scale_affinities == nullptr || (block_to_expert != nullptr && B > 0 && E > 0 &&
+                                                      (aff_dtype == B200MOE_F32 || aff_dtype == B200MOE_BF16)),
+                  B200MOE_ERR_INVALID, "scatter_rows: scaling needs block_to_expert, B, E and fp32 / bf16 affinities");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (tile_flags != nullptr)
+    B200MOE_CUDA_OK(cudaMemsetAsync(tile_flags, 0, static_cast<size_t>(ceil_div64(n_pos, 128)) * 4, st));
+  scatter_rows_bf16_kernel<<<(T + 7) / 8, 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(hidden_bf16), T, H, table, K, n_pos, block_to_expert, B, E,
+      pre_scale_affinities, aff_dtype, static_cast<__nv_bfloat16*>(out_bf16), tile_flags);
+  B200MOE_LAUNCH_OK("scatter_rows_bf16_kernel");
   return B200MOE_OK;
 }
 

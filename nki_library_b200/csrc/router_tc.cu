@@ -28,24 +28,6 @@ struct RouterTcArgs {
   int32_t* status;
 };
 
-// kind::f16 instruction descriptor: fp32 accumulate, bf16 A and B, both K-major.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
-         (static_cast<uint32_t>(M >> 4) << 24);
-}
-
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 __global__ void transpose_pad_kernel(const __nv_bfloat16* __restrict__ w, int H, int E, int EN,
                                      __nv_bfloat16* __restrict__ wT) {
   // w [H, E] -> wT [EN, H], rows e >= E zero

@@ -135,7 +135,7 @@ def prepare_from_nki(gate_up_proj_weight, gate_up_proj_scale, down_proj_weight, 
 
 
 _cache: dict = {}  # key -> (weak references to the source tensors, prepared weights)
-_cache_lock = threading.Lock()
+_cache_lock = threading.RLock()  # re-entrant: a weak-reference callback may fire while the lock is held
 
 
 def _evict(key) -> None:
@@ -161,4 +161,81 @@ def prepare_from_nki_cached(gate_up_proj_weight, gate_up_proj_scale, down_proj_w
     refs = tuple(None if t is None else weakref.ref(t, lambda _r, k=key: _evict(k)) for t in srcs)
     with _cache_lock:
         _cache[key] = (refs, prepared)
+    return prepared
+
+
+# ---------------------------------------------------------------------------------------------------
+# Dense (non-MX) expert weights: bf16, or fp8 with one dequantisation factor per output row ("fp8-row").
+# ---------------------------------------------------------------------------------------------------
+@dataclass
+class DenseExpertWeights:
+    """bf16 weights in the tensor-core feed layout of the dense contractions."""
+    E: int
+    H: int
+    I: int
+    w1: torch.Tensor                  # bf16 [E, 2I, H], gate/up rows interleaved per 32 like the MX layout
+    w2: torch.Tensor                  # bf16 [E, H, I]
+    scale_gu: Optional[torch.Tensor]  # fp32 [E, 2I] (interleaved order) or None
+    scale_d: Optional[torch.Tensor]   # fp32 [E, H] or None
+    bias_gu: Optional[torch.Tensor]   # fp32 [E, 2I] (interleaved order)
+    bias_d: Optional[torch.Tensor]    # fp32 [E, H]
+    h_packed_order: bool = False
+
+    def nbytes(self) -> int:
+        return (self.w1.numel() + self.w2.numel()) * 2
+
+
+def _interleave_gate_up(t: torch.Tensor) -> torch.Tensor:
+    """``[E, 2, I, ...]`` -> ``[E, 2I, ...]`` with rows ordered 32 gate, the matching 32 up, 32 gate, ..."""
+    E, two, I = t.shape[:3]
+    rest = t.shape[3:]
+    return t.reshape(E, 2, I // 32, 32, *rest).transpose(1, 2).reshape(E, 2 * I, *rest).contiguous()
+
+
+def prepare_dense(gate_up_proj_weight, down_proj_weight, gate_and_up_proj_bias=None, down_proj_bias=None,
+                  gate_up_proj_scale=None, down_proj_scale=None) -> DenseExpertWeights:
+    """Reference storage of the non-MX variants -> feed layout (once per model load).
+
+    ``gate_up_proj_weight [E, H, 2, I]`` and ``down_proj_weight [E, I, H]`` in bf16 / fp16 / fp32 or an fp8 dtype;
+    biases ``[E, 2, I]`` / ``[E, H]``; fp8-row factors ``gate_up_proj_scale [E or 1, 1, 2I]`` (or ``[E, 2, I]``, the
+    decode kernels' form) and ``down_proj_scale [E or 1, 1, H]`` (or ``[E, H]``)
+    (core/moe/moe_cte/moe_cte_torch.py:163-206, core/moe/moe_tkg/moe_tkg_torch.py:226-290)."""
+    _lib.require_cuda(gate_up_proj_weight, down_proj_weight, gate_and_up_proj_bias, down_proj_bias, gate_up_proj_scale,
+                      down_proj_scale)
+    E, H, two, I = gate_up_proj_weight.shape
+    _lib.kernel_assert(two == 2 and I % 32 == 0 and H % 32 == 0,
+                       "gate_up_proj_weight must be [E, H, 2, I] with H and I multiples of 32")
+    _lib.kernel_assert(tuple(down_proj_weight.shape[:1]) == (E,) and down_proj_weight.shape[-1] == H and
+                       down_proj_weight.shape[1] >= I, "down_proj_weight must be [E, I, H]")
+    w1 = _interleave_gate_up(gate_up_proj_weight.to(torch.bfloat16).permute(0, 2, 3, 1))      # [E, 2, I, H] -> rows
+    w2 = down_proj_weight[:, :I, :].to(torch.bfloat16).transpose(1, 2).contiguous()            # [E, H, I]
+    scale_gu = scale_d = None
+    if gate_up_proj_scale is not None and gate_up_proj_scale.numel() > 0:
+        s = gate_up_proj_scale.float().reshape(-1, 2, I)
+        scale_gu = _interleave_gate_up(s.expand(E, 2, I))
+        scale_d = down_proj_scale.float().reshape(-1, H).expand(E, H).contiguous()
+    bias_gu = None if gate_and_up_proj_bias is None else _interleave_gate_up(gate_and_up_proj_bias.float().reshape(E, 2, I))
+    bias_d = None if down_proj_bias is None else down_proj_bias.float().reshape(E, H).contiguous()
+    return DenseExpertWeights(E, H, I, w1, w2, scale_gu, scale_d, bias_gu, bias_d)
+
+
+_dense_cache: dict = {}
+
+
+def prepare_dense_cached(*srcs) -> DenseExpertWeights:
+    """``prepare_dense`` memoised on the identity and version of the source tensors (entries die with them)."""
+    key = tuple((id(t), t.data_ptr(), tuple(t.shape), t._version) if t is not None else None for t in srcs)
+    with _cache_lock:
+        hit = _dense_cache.get(key)
+    if hit is not None and all(r is None or r() is s for r, s in zip(hit[0], srcs)):
+        return hit[1]
+    prepared = prepare_dense(*srcs)
+
+    def drop(_r, k=key):
+        with _cache_lock:
+            _dense_cache.pop(k, None)
+
+    refs = tuple(None if t is None else weakref.ref(t, drop) for t in srcs)
+    with _cache_lock:
+        _dense_cache[key] = (refs, prepared)
     return prepared

@@ -77,6 +77,7 @@ class Reference:
     """Handles to the reference's MX CPU functions."""
 
     def __init__(self, ref_root: str):
+        self.root = ref_root
         sys.path.insert(0, os.path.join(HERE, "standins"))
         sys.path.insert(0, os.path.join(ref_root, "src"))
         sys.path.insert(0, ref_root)
@@ -296,7 +297,74 @@ def decode_fixture(ref: Reference, out: dict) -> None:
         print(f"  decode {name}: {time.time() - t0:.1f} s", flush=True)
 
 
-PARTS = {"quantize": quantize_fixture, "matmul": matmul_fixture, "proj": projection_fixture,
+def dense_fixture(ref: Reference, out: dict) -> None:
+    """The non-MX CPU references: ``moe_cte_torch_ref`` (core/moe/moe_cte/moe_cte_torch.py:26-242, compiled out of
+    its module, whose package imports NKI kernels) and ``moe_tkg_torch_ref`` (core/moe/moe_tkg/moe_tkg_torch.py:36)."""
+    from enum import Enum
+    core = os.path.join(ref.root, "src", "nkilib_src", "nkilib", "core")
+    t = os.path.join(ref.root, "test", "integration", "nkilib", "core", "moe", "moe_cte", "test_moe_cte_common.py")
+    enum_ns = load_definitions(t, {"BWMMFunc"}, {"Enum": Enum, "Tuple": tuple, "Callable": object})
+    fake = types.ModuleType("test.integration.nkilib.core.moe.moe_cte.test_moe_cte_common")
+    fake.BWMMFunc = enum_ns["BWMMFunc"]
+    sys.modules[fake.__name__] = fake  # moe_cte_torch_ref imports the enum from there at call time
+    utils = importlib.import_module("nkilib_src.nkilib.core.moe.moe_cte.moe_cte_torch_utils")
+    SkipMode = ref.utils_ns["SkipMode"]
+    ns = load_definitions(os.path.join(core, "moe", "moe_cte", "moe_cte_torch.py"), {"moe_cte_torch_ref"},
+                          {"torch": torch, "Optional": __import__("typing").Optional, "ActFnType": ref.types.ActFnType,
+                           "ExpertAffinityScaleMode": ref.types.ExpertAffinityScaleMode,
+                           "torch_act_fn": utils.torch_act_fn, "SkipMode": SkipMode})
+    acts = {"silu": ref.types.ActFnType.SiLU, "swish": ref.types.ActFnType.Swish, "gelu": ref.types.ActFnType.GELU,
+            "gelu_tanh": ref.types.ActFnType.GELU_Tanh_Approx}
+    modes = {"post": ref.types.ExpertAffinityScaleMode.POST_SCALE, "pre": ref.types.ExpertAffinityScaleMode.PRE_SCALE,
+             "none": ref.types.ExpertAffinityScaleMode.NO_SCALE}
+    BW = enum_ns["BWMMFunc"]
+    for name, c in gi.DENSE_CTE_CASES.items():
+        d = gi.dense_cte_inputs(name)
+        T, E, K, B = c["T"], c["E"], c["K"], c["B"]
+        ref.common_ns["get_router_with_controlled_distribution"] = \
+            lambda T, TOPK, E, alpha=None, _i=d["expert_index"]: _i.astype(np.float64)
+        N = ref.common_ns["get_n_blocks"](T, K, E, B)
+        _, tpi, b2e, cond = ref.common_ns["generate_token_position_to_id_and_experts"](
+            T, K, E, B, SkipMode(c["skip_token"], False), N, is_block_parallel=False)
+        g_hi, g_lo, u_hi, u_lo = c["clamps"]
+        fp8 = c["weights"] == "fp8row"
+        wdt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+        res = ns["moe_cte_torch_ref"](
+            hidden_states=torch.from_numpy(d["hidden"]).to(torch.bfloat16),
+            expert_affinities_masked=torch.from_numpy(d["aff"]).to(torch.bfloat16).reshape(-1, 1),
+            gate_up_proj_weight=torch.from_numpy(d["gate_up"]).to(wdt), down_proj_weight=torch.from_numpy(d["down"]).to(wdt),
+            token_position_to_id=torch.from_numpy(tpi), block_to_expert=torch.from_numpy(b2e), block_size=B,
+            bwmm_func=BW.SHARD_ON_INTERMEDIATE_HW if c["hybrid"] else BW.SHARD_ON_INTERMEDIATE,
+            conditions=torch.from_numpy(cond) if c["hybrid"] else None,
+            gate_and_up_proj_bias=None if d["bias_gu"] is None else torch.from_numpy(d["bias_gu"]),
+            down_proj_bias=None if d["bias_d"] is None else torch.from_numpy(d["bias_d"]),
+            gate_up_proj_scale=torch.from_numpy(d["gate_up_scale"].reshape(E, 1, -1)) if fp8 else None,
+            down_proj_scale=torch.from_numpy(d["down_scale"].reshape(E, 1, -1)) if fp8 else None,
+            activation_function=acts[c["act"]], skip_dma=SkipMode(c["skip_token"], False),
+            expert_affinities_scaling_mode=modes[c["scaling"]], gate_clamp_upper_limit=g_hi,
+            gate_clamp_lower_limit=g_lo, up_clamp_upper_limit=u_hi, up_clamp_lower_limit=u_lo, top_k=K)["output"]
+        out[f"dense_cte/{name}/out"] = res[:T].numpy().astype(np.float32)
+        out[f"dense_cte/{name}/tpi"] = tpi.astype(np.int32)
+        out[f"dense_cte/{name}/block_to_expert"] = b2e.astype(np.int32)
+        out[f"dense_cte/{name}/conditions"] = cond.astype(np.int32)
+    for name in gi.DENSE_TKG_CASES:
+        d = gi.dense_tkg_inputs(name)
+        fp8 = d["weights"] == "fp8row"
+        wdt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+        g_hi, g_lo, u_hi, u_lo = d["clamps"]
+        res = ref.tkg.moe_tkg_torch_ref(
+            torch.from_numpy(d["hidden"]), torch.from_numpy(d["gate_up"]).to(wdt), torch.from_numpy(d["down"]).to(wdt),
+            torch.from_numpy(d["aff"]), torch.from_numpy(d["expert_index"]), d["all_expert"],
+            expert_gate_up_bias=torch.from_numpy(d["bias_gu"]), expert_down_bias=torch.from_numpy(d["bias_d"]),
+            expert_gate_up_weights_scale=torch.from_numpy(d["gate_up_scale"]) if fp8 else None,
+            expert_down_weights_scale=torch.from_numpy(d["down_scale"]) if fp8 else None,
+            expert_affinities_scaling_mode=ref.types.ExpertAffinityScaleMode.POST_SCALE, activation_fn=acts[d["act"]],
+            gate_clamp_upper_limit=g_hi, gate_clamp_lower_limit=g_lo, up_clamp_upper_limit=u_hi,
+            up_clamp_lower_limit=u_lo)["out"]
+        out[f"dense_tkg/{name}/out"] = res.numpy().astype(np.float32)
+
+
+PARTS = {"dense": dense_fixture, "quantize": quantize_fixture, "matmul": matmul_fixture, "proj": projection_fixture,
          "grouping": grouping_fixture, "decode": decode_fixture, "layer": layer_fixture}
 
 
@@ -308,7 +376,7 @@ def main(ref_root: str, only=None) -> None:
     out: dict = {}
     if only:
         with np.load(path) as old:
-            out = {k: old[k] for k in old.files if k.split("/")[0] not in only}
+            out = {k: old[k] for k in old.files if k.split("/")[0].split("_")[0] not in only}
     for name, fn in PARTS.items():
         if not only or name in only:
             fn(ref, out)

@@ -296,3 +296,74 @@ def sample_rows(name, n_rows, count):
     """The token rows of a large case whose reference outputs are kept (seeded choice, ascending)."""
     rng = np.random.default_rng(sum(map(ord, name)) + 1)
     return np.sort(rng.choice(n_rows, size=count, replace=False))
+
+
+# ---------------------------------------------------------------------------
+# Dense (non-MX) fixtures: inputs for moe_cte_torch_ref / moe_tkg_torch_ref.
+# ---------------------------------------------------------------------------
+# name: dict(T, H, I, E, K, B, weights "bf16" | "fp8row", act, bias, clamps (gate_hi, gate_lo, up_hi, up_lo),
+#            scaling "post" | "pre" | "none", skip_token, hybrid)
+DENSE_CTE_CASES = {
+    "c1_bf16_post": dict(T=256, H=512, I=1024, E=4, K=2, B=128, weights="bf16", act="silu", bias=True,
+                         clamps=(None, None, None, None), scaling="post", skip_token=True, hybrid=False),
+    "c1_fp8row_pre_swish_clamp": dict(T=256, H=512, I=1024, E=4, K=2, B=128, weights="fp8row", act="swish", bias=True,
+                                      clamps=(7.0, None, 7.0, -7.0), scaling="pre", skip_token=False, hybrid=False),
+    "b256_bf16_hybrid_gelu": dict(T=600, H=768, I=384, E=6, K=2, B=256, weights="bf16", act="gelu", bias=False,
+                                  clamps=(None, None, None, None), scaling="post", skip_token=True, hybrid=True),
+}
+# name: (T, H, I, E, K, weights, act, all_expert)
+DENSE_TKG_CASES = {
+    "sel_t8_bf16_silu": (8, 512, 256, 4, 2, "bf16", "silu", False),
+    "all_t16_fp8row_swish": (16, 512, 256, 4, 2, "fp8row", "swish", True),
+    "sel_t4_fp8row_gelu_tanh": (4, 768, 384, 8, 4, "fp8row", "gelu_tanh", False),
+}
+
+
+def _fp8_exact(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.float8_e4m3fn).float().numpy()
+
+
+def _dense_weights(rng, E, H, I, kind):
+    """``gate_up [E, H, 2, I]``, ``down [E, I, H]`` as fp32 values exactly representable in the storage type, and
+    the fp8-row factors (None for bf16): fp8 weights hold values ~N(0, 1) and the factors carry the 0.02 magnitude."""
+    if kind == "bf16":
+        return (bf16_round(rng.standard_normal((E, H, 2, I)) * 0.02), bf16_round(rng.standard_normal((E, I, H)) * 0.02),
+                None, None)
+    gu = _fp8_exact(rng.standard_normal((E, H, 2, I)))
+    dn = _fp8_exact(rng.standard_normal((E, I, H)))
+    return gu, dn, (rng.uniform(0.01, 0.03, (E, 2, I))).astype(np.float32), (rng.uniform(0.01, 0.03, (E, H))).astype(np.float32)
+
+
+def dense_cte_inputs(name):
+    c = DENSE_CTE_CASES[name]
+    T, H, I, E, K = c["T"], c["H"], c["I"], c["E"], c["K"]
+    rng = np.random.default_rng(_case_seed(name))
+    rows = T if c["skip_token"] else T + 1
+    hidden = bf16_round(rng.standard_normal((rows, H)))
+    if not c["skip_token"]:
+        hidden[T] = 0
+    gu, dn, gs, ds = _dense_weights(rng, E, H, I, c["weights"])
+    idx = np.argsort(-rng.random((T, E)), axis=1, kind="stable")[:, :K].astype(np.int32)
+    mask = np.zeros((T, E), dtype=np.int32)
+    mask[np.arange(T)[:, None], idx] = 1
+    aff = np.zeros((rows, E), dtype=np.float32)
+    aff[:T] = bf16_round(rng.random((T, E)) * mask)
+    out = dict(case=c, hidden=hidden, aff=aff, expert_index=idx, mask=mask, gate_up=gu, down=dn, gate_up_scale=gs,
+               down_scale=ds, bias_gu=None, bias_d=None)
+    if c["bias"]:
+        out["bias_gu"] = bf16_round(rng.uniform(-2.0625, 0.52, (E, 2, I)))
+        out["bias_d"] = bf16_round(rng.uniform(-1.632, 1.4375, (E, H)))
+    return out
+
+
+def dense_tkg_inputs(name):
+    T, H, I, E, K, kind, act, all_expert = DENSE_TKG_CASES[name]
+    rng = np.random.default_rng(_case_seed(name))
+    hidden = bf16_round(rng.standard_normal((T, H)))
+    gu, dn, gs, ds = _dense_weights(rng, E, H, I, kind)
+    idx = np.argsort(-rng.random((T, E)), axis=1, kind="stable")[:, :K].astype(np.int32)
+    aff = bf16_round(rng.random((T, E)))
+    return dict(T=T, H=H, I=I, E=E, K=K, weights=kind, act=act, all_expert=all_expert, hidden=hidden, aff=aff,
+                expert_index=idx, gate_up=gu, down=dn, gate_up_scale=gs, down_scale=ds,
+                bias_gu=bf16_round(rng.uniform(-2.0625, 0.52, (E, 2, I))),
+                bias_d=bf16_round(rng.uniform(-1.632, 1.4375, (E, H))), clamps=(7.0, None, 7.0, -7.0))

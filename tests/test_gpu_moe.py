@@ -457,3 +457,52 @@ def test_moe_tkg_all_expert_rank_slice(rank, dynamic):
     ref = moe.moe_tkg_rows(hidden, masked, None, *local, bias_gu=bgu[sl], bias_d=bd[sl], is_all_expert=True,
                            expert_offset=rank * E_L)
     assert max_rel(out.float().cpu().numpy(), bf16_values(ref)) <= TOL
+
+
+@pytest.mark.parametrize("layout", ["rows", "reference"])
+def test_moe_block_tkg_all_expert_fused_norm_quantise(layout):
+    """All-expert decode block: RMSNorm (+ residual) and the MXFP8 quantisation run as one kernel (the reference's
+    rmsnorm_mx_quantize_tkg step, core/moe_block/moe_block_tkg.py:199-218).  The quantised rows must equal what the
+    stand-alone quantiser makes of the normalised rows, bit for bit, in the plain and in the packed hidden order;
+    the block's output is checked against the composite oracle."""
+    import nki_library_b200 as m
+    from nki_library_b200 import _lib, pipeline
+    Bt, S, H, I, E, K = 3, 8, 1024, 512, 4, 2
+    T = Bt * S
+    rng = np.random.default_rng(81)
+    inp = bf16_values(rng.standard_normal((Bt, S, H)).astype(np.float32) * 2.0)
+    res = bf16_values(rng.standard_normal((Bt, S, H)).astype(np.float32))
+    gamma = bf16_values(rng.uniform(0.5, 1.5, (1, H)).astype(np.float32))
+    rw = bf16_values((rng.standard_normal((H, E)) * 0.05).astype(np.float32))
+    w_np = make_rows_weights(E, H, I, 82)
+    to = lambda a: None if a is None else torch.from_numpy(a).to(torch.bfloat16).cuda()
+    if layout == "rows":
+        weights, h_order = _prep(m, w_np), None
+    else:
+        gw, gs = mx.rows_to_ref_gate_up(w_np[0], w_np[1])
+        dw, ds = mx.rows_to_ref_down(w_np[2], w_np[3])
+        weights = m.prepare_from_nki(torch.from_numpy(gw.view(np.int32)).cuda(), torch.from_numpy(gs).cuda(),
+                                     torch.from_numpy(dw.view(np.int32)).cuda(), torch.from_numpy(ds).cuda())
+        h_order = mx.hidden_packed_order(H)
+    outs = m.moe_block_tkg(to(inp), to(gamma), to(rw), weights, None, top_k=K, router_act_fn=m.RouterActFnType.SOFTMAX,
+                           router_pre_norm=True, norm_topk_prob=False, is_all_expert=True,
+                           rank_id=torch.zeros((1, 1), dtype=torch.int32, device="cuda"),
+                           expert_affinities_scaling_mode=m.ExpertAffinityScaleMode.POST_SCALE, residual=to(res))
+    x = bf16_values(inp.reshape(T, H) + res.reshape(T, H))
+    assert np.array_equal(outs[2].float().cpu().numpy(), x)
+    normed = bf16_values(routing.rms_norm(torch.from_numpy(x), torch.from_numpy(gamma)).numpy())
+    # the fused kernel's codes and scales of expert 0's rows == quantising its own normalised output separately
+    ws = pipeline.get_workspace(E * 128, H, I, "cuda")
+    got_codes = ws.xq[:T].cpu().numpy()
+    got_scales = sf_atoms_to_rows(ws.x_sf.cpu().numpy(), E * 128, H)[:T]
+    normed_gpu = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    _lib.call("b200moe_rmsnorm", _lib.ptr(to(x.reshape(T, H))), None, _lib.ptr(to(gamma.reshape(-1))), _lib.BF16, T, H, 0,
+              1e-6, _lib.ptr(normed_gpu), None, _lib.stream_ptr())
+    nv = normed_gpu.float().cpu().numpy()
+    ref_codes, ref_scales = mx.quantize_mx_rows(nv if h_order is None else nv[:, h_order])
+    assert np.array_equal(got_codes, ref_codes) and np.array_equal(got_scales, ref_scales)
+    logits, idx, aff = routing.router_topk(torch.from_numpy(normed), torch.from_numpy(rw), None, K, routing.SOFTMAX,
+                                           True, False)
+    masked = aff.numpy() * routing.mask_from_index(idx.numpy(), E)
+    ref = moe.moe_tkg_rows(normed, masked, None, *w_np, is_all_expert=True, h_order=h_order)
+    assert max_rel(outs[0].float().cpu().numpy(), bf16_values(ref)) <= 3e-2

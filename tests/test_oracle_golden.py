@@ -348,3 +348,45 @@ def test_large_operand_dequantise_equals_table_lookup():
     fast = mx.dequantize_mx_rows(codes, scales)
     slow = np.concatenate([mx.dequantize_mx_rows(codes[i:i + 256], scales[i:i + 256]) for i in range(0, 2048, 256)])
     assert np.array_equal(fast, slow, equal_nan=True)
+
+
+# ---------------------------------------------------------------------------
+# Non-MX (bf16 / fp8-row) variants against the reference's torch references
+# ---------------------------------------------------------------------------
+from oracle import dense  # noqa: E402
+
+_DENSE_ACT = {"silu": dense.SILU, "swish": dense.SWISH, "gelu": dense.GELU, "gelu_tanh": dense.GELU_TANH}
+_DENSE_SCALING = {"post": dense.POST_SCALE, "pre": dense.PRE_SCALE, "none": dense.NO_SCALE}
+
+
+@pytest.mark.parametrize("name", list(gi.DENSE_CTE_CASES))
+def test_dense_prefill_oracle_matches_reference_moe_cte_torch_ref(name, mx_gold):
+    """``moe_cte_torch_ref`` (core/moe/moe_cte/moe_cte_torch.py:26-242): bf16 and fp8-row weights, POST_SCALE and
+    PRE_SCALE, bias, clamps, the hybrid variant's ``conditions``; block assignment from the reference's generator."""
+    c = gi.DENSE_CTE_CASES[name]
+    d = gi.dense_cte_inputs(name)
+    N = routing.get_n_blocks(c["T"], c["K"], c["E"], c["B"])
+    tpi, b2e, cond, _ = routing.group_tokens(d["mask"], c["B"], N, skip_token=c["skip_token"], mx_conditions=False)
+    assert np.array_equal(tpi, mx_gold[f"dense_cte/{name}/tpi"])
+    assert np.array_equal(b2e, mx_gold[f"dense_cte/{name}/block_to_expert"])
+    assert np.array_equal(cond, mx_gold[f"dense_cte/{name}/conditions"])
+    g_hi, g_lo, u_hi, u_lo = c["clamps"]
+    E = c["E"]
+    out = dense.moe_cte_dense(
+        d["hidden"], d["aff"], d["gate_up"], d["down"], tpi, b2e, c["B"], cond if c["hybrid"] else None, d["bias_gu"],
+        d["bias_d"], None if d["gate_up_scale"] is None else d["gate_up_scale"].reshape(E, 1, -1),
+        None if d["down_scale"] is None else d["down_scale"].reshape(E, 1, -1), _DENSE_ACT[c["act"]], (g_lo, g_hi),
+        (u_lo, u_hi), _DENSE_SCALING[c["scaling"]], c["skip_token"])
+    assert _rel(out, mx_gold[f"dense_cte/{name}/out"]) <= 1e-5
+
+
+@pytest.mark.parametrize("name", list(gi.DENSE_TKG_CASES))
+def test_dense_decode_oracle_matches_reference_moe_tkg_torch_ref(name, mx_gold):
+    """``moe_tkg_torch_ref`` on non-MX weights (core/moe/moe_tkg/moe_tkg_torch.py:36-297): selective and all-expert,
+    bf16 and fp8-row."""
+    d = gi.dense_tkg_inputs(name)
+    g_hi, _, u_hi, u_lo = d["clamps"]
+    out = dense.moe_tkg_dense(d["hidden"], d["aff"], d["expert_index"], d["gate_up"], d["down"], d["bias_gu"],
+                              d["bias_d"], _DENSE_ACT[d["act"]], g_hi, (u_lo, u_hi), d["gate_up_scale"], d["down_scale"],
+                              True, d["all_expert"])
+    assert _rel(out, mx_gold[f"dense_tkg/{name}/out"]) <= 1e-5
