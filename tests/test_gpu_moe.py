@@ -492,7 +492,7 @@ def test_moe_block_tkg_all_expert_fused_norm_quantise(layout):
     assert np.array_equal(outs[2].float().cpu().numpy(), x)
     normed = bf16_values(routing.rms_norm(torch.from_numpy(x), torch.from_numpy(gamma)).numpy())
     # the fused kernel's codes and scales of expert 0's rows == quantising its own normalised output separately
-    ws = pipeline.get_workspace(E * 128, H, I, "cuda")
+    ws = pipeline.get_workspace(E * 128, H, I, outs[0].device)
     got_codes = ws.xq[:T].cpu().numpy()
     got_scales = sf_atoms_to_rows(ws.x_sf.cpu().numpy(), E * 128, H)[:T]
     normed_gpu = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
