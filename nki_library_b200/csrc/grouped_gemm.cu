@@ -499,8 +499,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        if (CTAS == 2 && cta_rank != 0) mbar_arrive_leader(&tmem_empty[acc]);
-        else mbar_arrive(&tmem_empty[acc]);
+        // relaxed: the accumulator is in registers (wait::ld above); a releasing arrive would first wait for this
+        // thread's global stores of the previous tile to become visible and hold the next tile's MMAs back
+        if (CTAS == 2 && cta_rank != 0) mbar_arrive_leader_relaxed(&tmem_empty[acc]);
+        else mbar_arrive_relaxed(&tmem_empty[acc]);
       }
       if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
       if (CTAS == 2 && cta_rank != 0 && !second) continue;  // half-empty pair: these rows belong to someone else
