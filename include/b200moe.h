@@ -318,10 +318,15 @@ int b200moe_rmsnorm_quantize_mxfp8(const void* inp_bf16, const void* residual_bf
  * Flag tables are int32 [4][8], zero-initialised; epoch_dev is a zero-initialised device int32 that
  * exchange_counts bumps once per step (so a recorded CUDA graph of a step can be replayed).
  *
- * Step order on every rank's stream: exchange_counts -> dispatch_quantize -> signal_wait(slot 1) ->
- * plan -> grouped_gemm1 / grouped_gemm2 (token_position_to_id = row_valid, hidden_rows = cap_rows,
- * per-row affinities) -> return_rows -> signal_wait(slot 2) -> combine.  A wait that runs out
- * (about two seconds) or a receive buffer that is too small sets *status non-zero. */
+ * Step order on every rank's stream: exchange_counts -> dispatch_quantize (which also writes the receiver's
+ * plan when given its outputs; b200moe_ep_plan is the same computation as a launch of its own) ->
+ * signal_wait(slot 1) -> grouped_gemm1 / grouped_gemm2 (token_position_to_id = row_valid, hidden_rows =
+ * cap_rows, per-row affinities) -> return_rows -> signal_wait(slot 2) -> combine.  A wait that runs out
+ * (about two seconds) or a receive buffer that is too small sets *status non-zero.
+ * dispatch_quantize: every rank walks its (token, k) pairs starting with those bound for rank + 1 and wraps
+ * around, so the ranks store into different GPUs at any moment.  Plan outputs (block_to_expert == NULL: none):
+ * block_to_expert / conditions [n_blocks_cap (+2)], row_valid [n_blocks_cap * B], tile_flags
+ * [n_blocks_cap * B / 128], all in this rank's own memory; they depend on the count table only. */
 int b200moe_ipc_export(const void* dev_ptr, void* handle_out_64, int64_t* offset_out);
 int b200moe_ipc_open(const void* handle_64, int64_t offset, void** dev_ptr_out);
 int b200moe_ipc_close(void* dev_ptr, int64_t offset);
@@ -336,7 +341,8 @@ int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32_t* pair_to
                                  const float* affinities, const int32_t* counts_all, int T, int K, int H, int E, int B,
                                  int rank, int world, int h_packed_order, void* const* xq_peers, void* const* sf_peers,
                                  void* const* aff_peers, void* const* src_peers, int64_t cap_rows,
-                                 b200moe_stream_t stream);
+                                 int n_blocks_cap, int32_t* block_to_expert, int32_t* conditions, int32_t* row_valid,
+                                 int32_t* tile_flags, int32_t* status, b200moe_stream_t stream);
 /* The down contraction of an expert-parallel step with the return fused into its epilogue: instead of writing
  * y_pos and copying it out afterwards (b200moe_ep_return_rows), every result row is stored straight into the
  * buffer of the GPU its token came from -- row (row_src[r] & 0xffffff) of back_peers[row_src[r] >> 24], plain

@@ -92,7 +92,8 @@ SIGNATURES = {
                                 c_void_p, c_void_p]),
     "b200moe_ep_dispatch_quantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                             c_void_p, c_int64, c_void_p]),
+                                             c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p]),
     "b200moe_ep_gemm2_scale_return": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                               c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p]),

@@ -42,6 +42,13 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
   return v;
 }
 
+// 32-byte store; the address must be 32-byte aligned (rows are H bytes, H % 32 == 0, on a 256-byte aligned base).
+__device__ __forceinline__ void st_peer_256(void* p, const uint32_t (&c)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(c[0]), "r"(c[1]), "r"(c[2]),
+               "r"(c[3]), "r"(c[4]), "r"(c[5]), "r"(c[6]), "r"(c[7])
+               : "memory");
+}
+
 // Thread r < world posts `epoch` into word [slot][rank] of rank r's flag table; thread s < world then waits
 // for word [slot][s] of this rank's own table.  One CTA.
 __device__ void post_and_wait(const PeerPtrs& flags, int rank, int world, int slot, int epoch, int32_t* status,
@@ -109,55 +116,72 @@ __device__ void build_layout(const int32_t* counts_all, int world, int E, int B,
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(512) ep_plan_kernel(const int32_t* __restrict__ counts_all, int rank, int world,
+// The receiver's plan, from the count table alone: block -> local expert, the dynamic-loop conditions, which rows
+// hold a token and how many leading rows of every 128-row tile do.  Rows of an expert are packed from its first
+// block, so everything follows from (first block, row count) of the owning expert; nothing is scanned.  Work is
+// spread over `gthreads` threads (`gtid` = this thread's index among them).
+__device__ void plan_rows(const int32_t* s_total, const int32_t* s_first, int rank, int world, int E, int B,
+                          int n_blocks_cap, int32_t* block_to_expert, int32_t* conditions, int32_t* row_valid,
+                          int32_t* tile_flags, int32_t* status, int64_t gtid, int64_t gthreads) {
+  const int E_L = E / world;
+  const int e0 = rank * E_L;
+  const int used_raw = s_first[e0 + E_L - 1] + (s_total[e0 + E_L - 1] + B - 1) / B;
+  if (gtid == 0 && used_raw > n_blocks_cap) atomicCAS(status, 0, 21);  // more rows arrived than the buffer holds
+  const int used = min(used_raw, n_blocks_cap);
+  // first local expert whose block range holds b (the last expert for blocks nobody owns)
+  auto owner_of = [&](int b) {
+    for (int l = 0; l < E_L; ++l) {
+      const int e = e0 + l;
+      if (b >= s_first[e] && b < s_first[e] + (s_total[e] + B - 1) / B) return l;
+    }
+    return -1;
+  };
+  for (int64_t b = gtid; b < n_blocks_cap + 2; b += gthreads) {
+    conditions[b] = b < used ? 1 : 0;
+    if (b < n_blocks_cap) {
+      const int l = owner_of(static_cast<int>(b));
+      block_to_expert[b] = l < 0 ? E_L - 1 : l;
+    }
+  }
+  const int tiles_per_block = B >> 7;
+  const int64_t n_tiles = static_cast<int64_t>(n_blocks_cap) * tiles_per_block;
+  const int lane = static_cast<int>(gtid & 31);
+  for (int64_t t = gtid >> 5; t < n_tiles; t += gthreads >> 5) {  // a warp per tile (gthreads is a multiple of 32)
+    const int b = static_cast<int>(t / tiles_per_block);
+    const int l = b < used ? owner_of(b) : -1;
+    int live = 0;  // leading rows of this tile that hold a token
+    if (l >= 0) {
+      const int64_t end = static_cast<int64_t>(s_first[e0 + l]) * B + s_total[e0 + l];  // one past the expert's last row
+      live = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(128), end - t * 128)));
+    }
+    if (lane == 0) tile_flags[t] = live;
+    int32_t* rv = row_valid + t * 128;
+#pragma unroll
+    for (int j = lane; j < 128; j += 32) rv[j] = j < live ? static_cast<int32_t>(t * 128 + j) : -1;
+  }
+}
+
+__global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t* __restrict__ counts_all, int rank, int world,
                                                       int E, int B, int n_blocks_cap, int32_t* block_to_expert,
                                                       int32_t* conditions, int32_t* row_valid, int32_t* tile_flags,
                                                       int32_t* status) {
   __shared__ int32_t s_total[kMaxExpertsEp];
   __shared__ int32_t s_first[kMaxExpertsEp];
-  __shared__ int s_used;
   build_layout(counts_all, world, E, B, s_total, s_first);
-  const int E_L = E / world;
-  if (threadIdx.x == 0) {
-    const int last = rank * E_L + E_L - 1;
-    s_used = s_first[last] + (s_total[last] + B - 1) / B;
-    if (s_used > n_blocks_cap) atomicCAS(status, 0, 21);  // more rows arrived than the buffer holds
-  }
-  __syncthreads();
-  const int used = min(s_used, n_blocks_cap);
-  for (int b = threadIdx.x; b < n_blocks_cap; b += blockDim.x) {
-    int owner = E_L - 1;
-    for (int l = 0; l < E_L; ++l) {
-      const int e = rank * E_L + l;
-      if (b >= s_first[e] && b < s_first[e] + (s_total[e] + B - 1) / B) { owner = l; break; }
-    }
-    block_to_expert[b] = owner;
-  }
-  for (int b = threadIdx.x; b < n_blocks_cap + 2; b += blockDim.x) conditions[b] = b < used ? 1 : 0;
-  const int64_t rows = static_cast<int64_t>(n_blocks_cap) * B;
-  for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
-    const int b = static_cast<int>(r / B);
-    int valid = 0;
-    if (b < used) {
-      for (int l = 0; l < E_L; ++l) {
-        const int e = rank * E_L + l;
-        const int nb = (s_total[e] + B - 1) / B;
-        if (b >= s_first[e] && b < s_first[e] + nb) {
-          valid = (r - static_cast<int64_t>(s_first[e]) * B) < s_total[e];
-          break;
-        }
-      }
-    }
-    row_valid[r] = valid ? static_cast<int32_t>(r) : -1;
-  }
-  __syncthreads();
-  // per 128-row tile: how many leading rows hold a token (rows of an expert are packed from its first block)
-  for (int t = threadIdx.x; t < rows / 128; t += blockDim.x) {
-    int last = 127;
-    while (last >= 0 && row_valid[static_cast<int64_t>(t) * 128 + last] < 0) --last;
-    tile_flags[t] = last + 1;
-  }
+  plan_rows(s_total, s_first, rank, world, E, B, n_blocks_cap, block_to_expert, conditions, row_valid, tile_flags,
+            status, static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x,
+            static_cast<int64_t>(gridDim.x) * blockDim.x);
 }
+
+// Outputs of the receiver's plan when the dispatch launch computes it as well (block_to_expert == nullptr: not).
+struct PlanOut {
+  int n_blocks_cap;
+  int32_t* block_to_expert;
+  int32_t* conditions;
+  int32_t* row_valid;
+  int32_t* tile_flags;
+  int32_t* status;
+};
 
 __device__ __forceinline__ void unpack8_bf16_ep(const uint4& raw, float* out) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -172,7 +196,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_quantize_kernel(
     const __nv_bfloat16* __restrict__ hidden, const int32_t* __restrict__ pair_token,
     const int32_t* __restrict__ pair_expert, const float* __restrict__ aff, const int32_t* __restrict__ counts_all,
     int T, int K, int H, int E, int B, int rank, int world, int packed, PeerPtrs xq, PeerPtrs sf, PeerPtrs row_aff,
-    PeerPtrs row_src, int64_t cap_rows) {
+    PeerPtrs row_src, int64_t cap_rows, PlanOut plan) {
   __shared__ int32_t s_total[kMaxExpertsEp];
   __shared__ int32_t s_first[kMaxExpertsEp];
   __shared__ int32_t s_base[kMaxExpertsEp];    // row of my first pair of expert e in the owner's buffer
@@ -183,15 +207,32 @@ __global__ void __launch_bounds__(256) ep_dispatch_quantize_kernel(
     for (int s = 0; s < rank; ++s) before += counts_all[s * E + e];
     s_base[e] = s_first[e] * B + before;
   }
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {  // exclusive scan of this rank's own counts, 32 experts per round
+    const int lane = threadIdx.x;
     int run = 0;
-    for (int e = 0; e < E; ++e) {
-      s_prefix[e] = run;
-      run += counts_all[rank * E + e];
+    for (int base = 0; base < E; base += 32) {
+      const int e = base + lane;
+      const int c = e < E ? counts_all[rank * E + e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      if (e < E) s_prefix[e] = run + incl - c;
+      run += __shfl_sync(0xffffffffu, incl, 31);
     }
   }
   __syncthreads();
   const int E_L = E / world;
+  if (plan.block_to_expert != nullptr)
+    plan_rows(s_total, s_first, rank, world, E, B, plan.n_blocks_cap, plan.block_to_expert, plan.conditions,
+              plan.row_valid, plan.tile_flags, plan.status, static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x,
+              static_cast<int64_t>(gridDim.x) * blockDim.x);
+  // Every rank starts with the pairs bound for the rank after it and wraps around, so that at any moment the
+  // ranks store into different GPUs (pairs are sorted by expert, i.e. by destination): in plain order all of them
+  // would write to rank 0 first, then to rank 1, ..., each time through a single GPU's ingress.
+  const int64_t rot = s_prefix[((rank + 1) % world) * E_L];
   const int blocks_per_row = H >> 5;
   const int64_t k_atoms = (H + 127) >> 7;
   const int64_t n_pairs = static_cast<int64_t>(T) * K;
@@ -200,8 +241,9 @@ __global__ void __launch_bounds__(256) ep_dispatch_quantize_kernel(
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_padded;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const bool live = i < total;
-    const int64_t p = live ? i / blocks_per_row : 0;
-    const int kb = live ? static_cast<int>(i - p * blocks_per_row) : 0;
+    const int64_t p_seq = live ? i / blocks_per_row : 0;
+    const int kb = live ? static_cast<int>(i - p_seq * blocks_per_row) : 0;
+    const int64_t p = p_seq + rot < n_pairs ? p_seq + rot : p_seq + rot - n_pairs;
     const int tok = live ? pair_token[p] : -1;
     const int e = live ? pair_expert[p] : -1;
     const bool ok = tok >= 0 && tok < T && e >= 0 && e < E;
@@ -243,9 +285,9 @@ __global__ void __launch_bounds__(256) ep_dispatch_quantize_kernel(
     const uint32_t s2 = __shfl_sync(0xffffffffu, scale, (lane & ~3) + 2);
     const uint32_t s3 = __shfl_sync(0xffffffffu, scale, (lane & ~3) + 3);
     if (!in_cap) continue;
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(xq.p[d]) + row * H + kb * 32);
-    dst[0] = make_uint4(c[0], c[1], c[2], c[3]);
-    dst[1] = make_uint4(c[4], c[5], c[6], c[7]);
+    // one 32-byte store per thread: a warp covers 1 KB of the row with whole sectors (two 16-byte stores would
+    // each touch half of every sector, which NVLink carries as twice the packets)
+    st_peer_256(static_cast<uint8_t*>(xq.p[d]) + row * H + kb * 32, c);
     if ((kb & 3) == 0) {
       const uint32_t cell = scale | (s1 << 8) | (s2 << 16) | (s3 << 24);
       *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(sf.p[d]) + sf_atom_offset(row, kb, k_atoms)) = cell;
@@ -384,7 +426,8 @@ extern "C" int b200moe_ep_plan(const int32_t* counts_all, int rank, int world, i
   B200MOE_REQUIRE(B > 0 && B % 128 == 0 && n_blocks_cap > 0, B200MOE_ERR_INVALID, "ep_plan: bad block geometry");
   const int rc = check_world(rank, world, E);
   if (rc != B200MOE_OK) return rc;
-  ep_plan_kernel<<<1, 512, 0, static_cast<cudaStream_t>(stream)>>>(counts_all, rank, world, E, B, n_blocks_cap,
+  const int64_t plan_threads = (static_cast<int64_t>(n_blocks_cap) * (B / 128)) * 32;
+  ep_plan_kernel<<<grid_cap(plan_threads, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(counts_all, rank, world, E, B, n_blocks_cap,
                                                                    block_to_expert, conditions, row_valid, tile_flags,
                                                                    status);
   B200MOE_LAUNCH_OK("ep_plan_kernel");
@@ -396,9 +439,16 @@ extern "C" int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32
                                             const int32_t* counts_all, int T, int K, int H, int E, int B, int rank,
                                             int world, int h_packed_order, void* const* xq_peers,
                                             void* const* sf_peers, void* const* aff_peers, void* const* src_peers,
-                                            int64_t cap_rows, b200moe_stream_t stream) {
+                                            int64_t cap_rows, int n_blocks_cap, int32_t* block_to_expert,
+                                            int32_t* conditions, int32_t* row_valid, int32_t* tile_flags,
+                                            int32_t* status, b200moe_stream_t stream) {
   B200MOE_REQUIRE(hidden_bf16 && pair_token && pair_expert && affinities && counts_all, B200MOE_ERR_INVALID,
                   "ep_dispatch_quantize: null argument");
+  PlanOut plan{n_blocks_cap, block_to_expert, conditions, row_valid, tile_flags, status};
+  if (block_to_expert != nullptr)
+    B200MOE_REQUIRE(conditions && row_valid && tile_flags && status && n_blocks_cap > 0 && B > 0 && B % 128 == 0 &&
+                        static_cast<int64_t>(n_blocks_cap) * B <= cap_rows,
+                    B200MOE_ERR_INVALID, "ep_dispatch_quantize: incomplete or oversized plan outputs");
   B200MOE_REQUIRE(H > 0 && H % 128 == 0, B200MOE_ERR_INVALID, "ep_dispatch_quantize: H must be a multiple of 128");
   B200MOE_REQUIRE(static_cast<int64_t>(T) * K < (1 << 24), B200MOE_ERR_INVALID,
                   "ep_dispatch_quantize: at most 2^24 (token, k) pairs per rank");
@@ -409,10 +459,13 @@ extern "C" int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32
   if ((rc = fill_peers(sf, sf_peers, world)) != B200MOE_OK) return rc;
   if ((rc = fill_peers(ra, aff_peers, world)) != B200MOE_OK) return rc;
   if ((rc = fill_peers(rs, src_peers, world)) != B200MOE_OK) return rc;
+  for (int i = 0; i < world; ++i)
+    B200MOE_REQUIRE(reinterpret_cast<uintptr_t>(xq.p[i]) % 32 == 0, B200MOE_ERR_INVALID,
+                    "ep_dispatch_quantize: activation buffers must be 32-byte aligned");
   const int64_t work = static_cast<int64_t>(T) * K * (H / 32);
   ep_dispatch_quantize_kernel<<<grid_cap(work, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(hidden_bf16), pair_token, pair_expert, affinities, counts_all, T, K, H, E, B,
-      rank, world, h_packed_order, xq, sf, ra, rs, cap_rows);
+      rank, world, h_packed_order, xq, sf, ra, rs, cap_rows, plan);
   B200MOE_LAUNCH_OK("ep_dispatch_quantize_kernel");
   return B200MOE_OK;
 }

@@ -226,10 +226,9 @@ class PeerExpertParallelMoE:
         self.rank = dist.get_rank(group)
         # The down contraction can store its rows into the peers itself (no separate return launch).  Its epilogue
         # owns one row per thread and stores 32 bytes at a time; measured per step on B200 / NVSwitch against the
-        # separate, fully coalesced copy kernel: 1.423 vs 1.470 ms at 2 ranks, 1.482 vs 1.546 ms at 4.  At 8 ranks
-        # it was only measured with 16-byte stores, which lost everywhere beyond 2 ranks (1.68 vs 1.59 ms), so the
-        # default stays separate there.
-        self.fuse_return = (self.world <= 4) if fuse_return is None else bool(fuse_return)
+        # separate, fully coalesced copy kernel: 1.423 vs 1.470 ms at 2 ranks, 1.482 vs 1.546 ms at 4, 1.473 vs
+        # 1.532 ms at 8.  (With 16-byte stores it lost everywhere beyond 2 ranks.)
+        self.fuse_return = True if fuse_return is None else bool(fuse_return)
         fuse_return = self.fuse_return
         _lib.kernel_assert(num_experts % self.world == 0,
                            f"num_experts ({num_experts}) must be divisible by the number of ranks ({self.world})")
@@ -283,16 +282,16 @@ class PeerExpertParallelMoE:
         self.gstatus = torch.zeros(1, dtype=torch.int32, device=dev)
         self.gws = torch.empty(lib.b200moe_group_tokens_workspace_bytes(self.T, self.E), dtype=torch.uint8, device=dev)
         self.timers = None
-        # router 2, grouping 3, count exchange, dispatch, wait, plan, contractions (CTA-pair launch + left-over
+        # router 2, grouping 3, count exchange, dispatch (+ plan), wait, contractions (CTA-pair launch + left-over
         # launch each when the block size allows pairs), return, wait, combine
-        self.kernels_per_forward = (2 + 3 + 1 + 1 + 1 + 1 + (4 if self.B % 256 == 0 else 2) + (0 if fuse_return else 1)
+        self.kernels_per_forward = (2 + 3 + 1 + 1 + 1 + (4 if self.B % 256 == 0 else 2) + (0 if fuse_return else 1)
                                     + 1 + 1)
         self._graph = None
 
     def forward(self, hidden: torch.Tensor) -> torch.Tensor:
         """``hidden [tokens_per_rank, H]`` bf16 -> bf16 ``[tokens_per_rank, H]`` (this rank's tokens).
 
-        Fourteen launches of this library's kernels on the current stream, nothing else: no allocation, no
+        Thirteen or fourteen launches of this library's kernels on the current stream, nothing else: no allocation, no
         collective call, no host synchronisation.  Every rank of the group must call it the same number of times.
         """
         _lib.kernel_assert(tuple(hidden.shape) == (self.T, self.H) and hidden.dtype == torch.bfloat16,
@@ -320,11 +319,10 @@ class PeerExpertParallelMoE:
         mark("t0")
         _lib.call("b200moe_ep_dispatch_quantize", _lib.ptr(hidden), _lib.ptr(self.pair_token), _lib.ptr(self.pair_expert),
                   _lib.ptr(self.aff), _lib.ptr(self.counts_all), T, K, H, E, B, self.rank, G, int(w.h_packed_order),
-                  self.p_xq, self.p_sf, self.p_aff, self.p_src, self.cap_rows, st)
-        _lib.call("b200moe_ep_signal_wait", self.p_flags, self.rank, G, 1, epoch, status, st)
-        _lib.call("b200moe_ep_plan", _lib.ptr(self.counts_all), self.rank, G, E, B, self.n_blocks_cap,
+                  self.p_xq, self.p_sf, self.p_aff, self.p_src, self.cap_rows, self.n_blocks_cap,
                   _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(self.row_valid), _lib.ptr(self.tile_flags),
-                  status, st)
+                  status, st)   # the receiver's plan rides in the same launch (it needs the count table only)
+        _lib.call("b200moe_ep_signal_wait", self.p_flags, self.rank, G, 1, epoch, status, st)
         mark("t1")
         _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(self.xq), _lib.ptr(self.sf), _lib.ptr(w.w1),
                   _lib.ptr(w.w1_sf), w.w_format, _lib.ptr(w.bias_gu), _lib.ptr(self.b2e), _lib.ptr(self.cond),
