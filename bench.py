@@ -55,7 +55,8 @@ WORKLOADS = {
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
 # profiles/ (file named beside each figure; null where no capture of the current kernel exists).
 NCU_TRAFFIC = {
-    "mixtral_prefill": {"bytes": None, "from": None},
+    "mixtral_prefill": {"bytes": 1.711e9, "from": "profiles/grouped_mxfp8_gemm_mixtral_prefill.md (gate/up contraction, "
+                        "pair + left-over launch, captured on this workload at full size)"},
     "mixtral_decode": {"bytes": None, "from": None},
 }
 
@@ -690,17 +691,19 @@ def run_multi(args, cfg, name, dev, peaks, world, rank):
     if any(status):
         raise RuntimeError(f"device status after the timed steps: {status}")
     # eager pass with events around the phases
-    per_kernel = None
-    if args.ep_backend == "peer":
+    def phase_ms(lay, inp, n_steps):
+        """Eager steps with events around the exchange and the two contractions (this rank's own clock)."""
         timers = {}
-        layer.timers = timers
-        for _ in range(args.steps):
-            layer.forward(x)
+        lay.timers = timers
+        for _ in range(n_steps):
+            lay.forward(inp)
         barrier()
-        layer.timers = None
+        lay.timers = None
         n = len(timers["t0"])
-        per_kernel = {nm: sum(timers[f"t{i}"][j].elapsed_time(timers[f"t{i + 1}"][j]) for j in range(n)) / n
-                      for i, nm in enumerate(("dispatch", "gemm1_swiglu", "gemm2_scale"))}
+        return {nm: sum(timers[f"t{i}"][j].elapsed_time(timers[f"t{i + 1}"][j]) for j in range(n)) / n
+                for i, nm in enumerate(("dispatch", "gemm1_swiglu", "gemm2_scale"))}
+
+    per_kernel = phase_ms(layer, x, args.steps) if args.ep_backend == "peer" else None
     # parity: rank 0's output against the single-GPU fused layer on the same tokens and all ranks' weights
     parity = None
     out_ep = layer.forward(x).clone()
@@ -772,11 +775,13 @@ def run_multi(args, cfg, name, dev, peaks, world, rank):
                 continue
             try:
                 lay5, h5, _, _ = build(c5, c5["T"] // world, 100 + rank)
-                ms5 = timed(lay5, h5.to(dev), 10, use_graph)
+                x5 = h5.to(dev)
+                ms5 = timed(lay5, x5, 10, use_graph)
+                k5 = phase_ms(lay5, x5, 5)
                 st5 = lay5.device_status()
                 strong[wl] = {"total_tokens": c5["T"], "tokens_per_gpu": c5["T"] // world,
                               "experts_per_gpu": c5["E"] // world, "ms_per_step": ms5,
-                              "tokens_per_s": c5["T"] / (ms5 * 1e-3), "device_status": st5,
+                              "tokens_per_s": c5["T"] / (ms5 * 1e-3), "kernel_ms": k5, "device_status": st5,
                               "capacity_factor": args.capacity_factor,
                               "layer_tflops_per_gpu": algorithmic_work(c5)["layer_flops"] / world / (ms5 * 1e-3) / 1e12}
                 del lay5
@@ -814,13 +819,36 @@ def run_multi(args, cfg, name, dev, peaks, world, rank):
                     "d2h_bytes_per_step": T * H * 2,
                     "per_rank_gb_per_s": {"h2d": T * H * 2 / (ms_e2e * 1e-3) / 1e9,
                                           "d2h": T * H * 2 / (ms_e2e * 1e-3) / 1e9,
-                                          "h2d_copy_alone_all_ranks_at_once": h2d_alone}},
+                                          "h2d_copy_alone_all_ranks_at_once": h2d_alone},
+                    "cpu_affinity": getattr(args, "cpu_affinity", None)},
             "gpu_launches": launches * args.steps,
             "launch_mode": "cuda graph replay" if use_graph else "eager",
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()
+
+
+def bind_to_gpu_cpus(local: int):
+    """Run this process on the CPUs NVML names as local to its GPU, so that pinned host buffers (first touched
+    from here) sit in the memory next to the GPU's PCIe root.  Returns a short description for the JSON line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        phys = int(visible.split(",")[local]) if visible and visible.split(",")[local].isdigit() else local
+        handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+        n_cpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (n_cpu + 63) // 64)
+        ideal = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        use = ideal & allowed
+        if not use or use == allowed:
+            return "unchanged (%d cpus)" % len(allowed)
+        os.sched_setaffinity(0, use)
+        return "gpu-local (%d of %d cpus)" % (len(use), len(allowed))
+    except Exception as exc:  # no NVML, no permission: keep the default placement
+        return "unchanged (%s)" % type(exc).__name__
 
 
 def run_ours(args, cfg, name):
@@ -835,7 +863,8 @@ def run_ours(args, cfg, name):
     if world == 1:
         run_single(args, cfg, name, dev, peaks)
     else:
-        dist.init_process_group("nccl", device_id=dev)
+        args.cpu_affinity = bind_to_gpu_cpus(local)   # before any pinned buffer exists; N = 1 keeps all cores
+        dist.init_process_group("nccl", device_id=dev)   # (its CPU leg uses them)
         run_multi(args, cfg, name, dev, peaks, world, rank)
 
 
