@@ -57,7 +57,8 @@ WORKLOADS = {
 NCU_TRAFFIC = {
     "mixtral_prefill": {"bytes": 1.711e9, "from": "profiles/grouped_mxfp8_gemm_mixtral_prefill.md (gate/up contraction, "
                         "pair + left-over launch, captured on this workload at full size)"},
-    "mixtral_decode": {"bytes": None, "from": None},
+    "mixtral_decode": {"bytes": 989.8e6, "from": "profiles/grouped_mxfp8_gemm_mixtral_decode.md (gate/up launch, captured "
+                       "on this workload at full size)"},
 }
 
 

@@ -225,6 +225,36 @@ __device__ __forceinline__ int tile_copy_rows(const GemmParams& p, int m_tile) {
   return f <= 0 ? 0 : (f <= 32 ? 32 : (f <= 64 ? 64 : kBlockM));
 }
 
+// A CTA's own tiles, decoded once in the prologue by all threads: the per-tile decode (a search over the experts,
+// two divisions, tile_flags reads from global memory) costs about a thousand clocks, which the single MMA-issuing
+// thread would otherwise spend at every tile boundary with the tensor pipe idle.
+struct TileRec {
+  int m_tile, n_tile, expert;
+  int flags;  // bit 0 valid, bit 1 second, bits 2-3 part + 1, bits 8-15 / 16-23 activation rows to copy (lead / peer)
+};
+constexpr int kTileTable = 448;  // entries per CTA (7 KB); later tiles are decoded on the spot
+
+__device__ __forceinline__ bool fetch_tile(const GemmParams& p, const Sched& s, const TileRec* table, int it, int tile,
+                                           int mg, int& m_tile, int& n_tile, int& expert, int& second, int& part,
+                                           int& rows_lead, int& rows_peer) {
+  if (it < kTileTable) {
+    const int4 r = *reinterpret_cast<const int4*>(table + it);
+    if (!(r.w & 1)) return false;
+    m_tile = r.x;
+    n_tile = r.y;
+    expert = r.z;
+    second = (r.w >> 1) & 1;
+    part = ((r.w >> 2) & 3) - 1;
+    rows_lead = (r.w >> 8) & 0xff;
+    rows_peer = (r.w >> 16) & 0xff;
+    return true;
+  }
+  if (!decode_tile(p, s, tile, mg, m_tile, n_tile, expert, second, part)) return false;
+  rows_lead = tile_copy_rows(p, m_tile);
+  rows_peer = second ? tile_copy_rows(p, m_tile + 1) : 0;
+  return true;
+}
+
 template <int BLOCK_N, int STAGES, int CTAS = 1>
 struct SmemLayout {
   static constexpr int kA = kBlockM * kBlockK;
@@ -238,7 +268,8 @@ struct SmemLayout {
   static constexpr int kOffSfb = kOffSfa + STAGES * kSfa;
   static constexpr int kOffBar = kOffSfb + STAGES * kSfb;
   static constexpr int kOffSched = kOffBar + 256;
-  static constexpr int kBytes = kOffSched + static_cast<int>(sizeof(Sched)) + 1024;  // + alignment slack
+  static constexpr int kOffTiles = (kOffSched + static_cast<int>(sizeof(Sched)) + 15) & ~15;
+  static constexpr int kBytes = kOffTiles + kTileTable * static_cast<int>(sizeof(TileRec)) + 1024;  // + alignment slack
 };
 
 // KIND 0: MXFP8 activations x MX weights, block-scaled MMAs (kind::mxf8f6f4.block_scale).
@@ -291,6 +322,19 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;
   build_sched(p, sched, CTAS, CTAS == 1 && BLOCK_N == 256, n_units);
   const int total_tiles = sched.total;
+  TileRec* tile_table = reinterpret_cast<TileRec*>(smem + L::kOffTiles);
+  for (int i = threadIdx.x; i < kTileTable; i += kThreads) {
+    const int tile = unit + i * n_units;
+    TileRec r{0, 0, 0, 0};
+    if (tile < total_tiles) {
+      int m_tile, n_tile, e, second, part;
+      if (decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) {
+        const int rl = tile_copy_rows(p, m_tile), rp = second ? tile_copy_rows(p, m_tile + 1) : 0;
+        r = TileRec{m_tile, n_tile, e, 1 | (second << 1) | ((part + 1) << 2) | (rl << 8) | (rp << 16)};
+      }
+    }
+    tile_table[i] = r;  // read after the __syncthreads below
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -337,11 +381,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       uint32_t phase = 0;
       bool ok = true;
       constexpr int kRowsB = BLOCK_N / CTAS;  // weight rows this CTA copies per slab
-      for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
-        int m_tile, n_tile, e, second, part;
-        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) continue;
-        const int rows_lead = tile_copy_rows(p, m_tile);
-        const int rows_peer = second ? tile_copy_rows(p, m_tile + 1) : 0;
+      for (int tile = unit, it = 0; tile < total_tiles && ok; tile += n_units, ++it) {
+        int m_tile, n_tile, e, second, part, rows_lead, rows_peer;
+        if (!fetch_tile(p, sched, tile_table, it, tile, CTAS, m_tile, n_tile, e, second, part, rows_lead, rows_peer))
+          continue;
         m_tile += cta_rank;
         const int my_rows = cta_rank == 0 ? rows_lead : rows_peer;
         const CUtensorMap* map_a = my_rows == 32 ? &tmap_a32 : (my_rows == 64 ? &tmap_a64 : &tmap_a);
@@ -390,9 +433,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
-        int m_tile, n_tile, e, second, part;
-        if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) continue;
+      for (int tile = unit, it = 0; tile < total_tiles && ok; tile += n_units, ++it) {
+        int m_tile, n_tile, e, second, part, rows_lead, rows_peer;
+        if (!fetch_tile(p, sched, tile_table, it, tile, CTAS, m_tile, n_tile, e, second, part, rows_lead, rows_peer))
+          continue;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
@@ -444,9 +488,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = unit; KIND == 0 && tile < total_tiles && ok; tile += n_units) {
-      int m_tile, n_tile, e, second, part;
-      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) continue;
+    for (int tile = unit, it = 0; KIND == 0 && tile < total_tiles && ok; tile += n_units, ++it) {
+      int m_tile, n_tile, e, second, part, rows_lead, rows_peer;
+      if (!fetch_tile(p, sched, tile_table, it, tile, CTAS, m_tile, n_tile, e, second, part, rows_lead, rows_peer))
+        continue;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait(&sf_full[stage], phase, abort_flag, p.status, 6)) { ok = false; break; }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + kSfCol + stage * 16;
@@ -483,9 +528,10 @@ grouped_mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                        (p.up_hi == p.up_hi);
     const float g_lo = p.gate_lo == p.gate_lo ? p.gate_lo : -INFINITY, g_hi = p.gate_hi == p.gate_hi ? p.gate_hi : INFINITY;
     const float u_lo = p.up_lo == p.up_lo ? p.up_lo : -INFINITY, u_hi = p.up_hi == p.up_hi ? p.up_hi : INFINITY;
-    for (int tile = unit; tile < total_tiles; tile += n_units) {
-      int m_tile, n_tile, e, second, part;
-      if (!decode_tile(p, sched, tile, CTAS, m_tile, n_tile, e, second, part)) continue;
+    for (int tile = unit, it = 0; tile < total_tiles; tile += n_units, ++it) {
+      int m_tile, n_tile, e, second, part, rows_lead, rows_peer;
+      if (!fetch_tile(p, sched, tile_table, it, tile, CTAS, m_tile, n_tile, e, second, part, rows_lead, rows_peer))
+        continue;
       m_tile += cta_rank;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after();

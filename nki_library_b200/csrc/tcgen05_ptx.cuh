@@ -30,16 +30,20 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
   asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// The waiting thread is suspended until the phase completes or kSuspendNs pass (it resumes at once on completion,
+// so the hint costs no latency): without a hint the default limit is short and sixteen waiting warps per CTA turn
+// into tens of millions of polling instructions per launch, which a power-capped GPU pays for in clock rate.
+constexpr uint32_t kSuspendNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendNs)
       : "memory");
   return ok != 0;
 }
