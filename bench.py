@@ -55,7 +55,7 @@ WORKLOADS = {
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
 # profiles/ (file named beside each figure; null where no capture of the current kernel exists).
 NCU_TRAFFIC = {
-    "mixtral_prefill": {"bytes": 1.711e9, "from": "profiles/grouped_mxfp8_gemm_mixtral_prefill.md (gate/up contraction, "
+    "mixtral_prefill": {"bytes": 1.623e9, "from": "profiles/grouped_mxfp8_gemm_mixtral_prefill.md (gate/up contraction, "
                         "pair + left-over launch, captured on this workload at full size)"},
     "mixtral_decode": {"bytes": 989.8e6, "from": "profiles/grouped_mxfp8_gemm_mixtral_decode.md (gate/up launch, captured "
                        "on this workload at full size)"},
