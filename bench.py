@@ -45,10 +45,11 @@ WORKLOADS = {
     "ep_prefill_zipf": dict(kind="prefill", T=32768, H=4096, I=1536, E=128, K=8, B=256, zipf=1.2),
     "tiny_prefill": dict(kind="prefill", T=256, H=512, I=1024, E=4, K=2, B=128, zipf=None),
     # cut-down shapes for profiler captures: the Mixtral block geometry with I = 2048 (201 MB of weights, larger
-    # than L2, a few hundred MB on the device) and the fine-grained / expert-parallel shapes with fewer experts
+    # than L2, a few hundred MB on the device) and the fine-grained / expert-parallel shapes with fewer experts and
+    # tokens at the same rows per expert (256 / 2048), so the same launch forms are taken
     "profile_prefill": dict(kind="prefill", T=4096, H=4096, I=2048, E=8, K=2, B=512, zipf=None),
     "profile_decode": dict(kind="decode", T=64, H=4096, I=2048, E=8, K=2, B=128, zipf=None),
-    "profile_finegrained": dict(kind="prefill", T=2048, H=7168, I=2048, E=32, K=8, B=128, zipf=1.2),
+    "profile_finegrained": dict(kind="prefill", T=1024, H=7168, I=2048, E=32, K=8, B=128, zipf=1.2),
     "profile_ep_prefill": dict(kind="prefill", T=8192, H=4096, I=1536, E=32, K=8, B=256, zipf=None),
 }
 
