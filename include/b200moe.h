@@ -320,11 +320,13 @@ int b200moe_rmsnorm_quantize_mxfp8(const void* inp_bf16, const void* residual_bf
  *
  * Step order on every rank's stream: exchange_counts -> dispatch_quantize (which also writes the receiver's
  * plan when given its outputs; b200moe_ep_plan is the same computation as a launch of its own) ->
- * signal_wait(slot 1) -> grouped_gemm1 / grouped_gemm2 (token_position_to_id = row_valid, hidden_rows =
+ * signal_wait(slot 1) -> scales_to_atoms -> grouped_gemm1 / grouped_gemm2 (token_position_to_id = row_valid, hidden_rows =
  * cap_rows, per-row affinities) -> return_rows -> signal_wait(slot 2) -> combine.  A wait that runs out
  * (about two seconds) or a receive buffer that is too small sets *status non-zero.
- * dispatch_quantize: every rank walks its (token, k) pairs starting with those bound for rank + 1 and wraps
- * around, so the ranks store into different GPUs at any moment.  Plan outputs (block_to_expert == NULL: none):
+ * dispatch_quantize walks the tokens: pair_of_token int32 [T, K] holds, for every (token, k), the index of that
+ * pair in the expert-sorted list (the inverse table b200moe_group_tokens writes at block size 1; -1 = none) and
+ * pair_expert [T*K] the expert of every sorted pair; a token's row is quantised once and stored to each GPU
+ * that owns one of its experts (codes into xq_peers, scale bytes row-major into sf_peers = the receivers' sf_rows).  Plan outputs (block_to_expert == NULL: none):
  * block_to_expert / conditions [n_blocks_cap (+2)], row_valid [n_blocks_cap * B], tile_flags
  * [n_blocks_cap * B / 128], all in this rank's own memory; they depend on the count table only. */
 int b200moe_ipc_export(const void* dev_ptr, void* handle_out_64, int64_t* offset_out);
@@ -337,7 +339,12 @@ int b200moe_ep_signal_wait(void* const* flag_tables, int rank, int world, int sl
 int b200moe_ep_plan(const int32_t* counts_all, int rank, int world, int E, int B, int n_blocks_cap,
                     int32_t* block_to_expert, int32_t* conditions, int32_t* row_valid, int32_t* tile_flags,
                     int32_t* status, b200moe_stream_t stream);
-int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32_t* pair_token, const int32_t* pair_expert,
+/* Receiver side of the dispatch: scale bytes arrive row-major (sf_rows uint8 [cap_rows][H / 32], written by the
+ * peers' dispatch_quantize); this lays the rows of every tile that holds a token (tile_flags > 0) into the 512-byte
+ * atoms the contractions read.  Runs after signal_wait(slot 1). */
+int b200moe_ep_scales_to_atoms(const uint8_t* sf_rows, const int32_t* tile_flags, int64_t n_tiles, int H,
+                               uint8_t* sf_atoms, b200moe_stream_t stream);
+int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32_t* pair_of_token, const int32_t* pair_expert,
                                  const float* affinities, const int32_t* counts_all, int T, int K, int H, int E, int B,
                                  int rank, int world, int h_packed_order, void* const* xq_peers, void* const* sf_peers,
                                  void* const* aff_peers, void* const* src_peers, int64_t cap_rows,

@@ -90,6 +90,7 @@ SIGNATURES = {
     "b200moe_ep_signal_wait": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p]),
+    "b200moe_ep_scales_to_atoms": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "b200moe_ep_dispatch_quantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -193,7 +193,7 @@ __device__ __forceinline__ void unpack8_bf16_ep(const uint4& raw, float* out) {
 }
 
 __global__ void __launch_bounds__(256) ep_dispatch_quantize_kernel(
-    const __nv_bfloat16* __restrict__ hidden, const int32_t* __restrict__ pair_token,
+    const __nv_bfloat16* __restrict__ hidden, const int32_t* __restrict__ pair_of_token,
     const int32_t* __restrict__ pair_expert, const float* __restrict__ aff, const int32_t* __restrict__ counts_all,
     int T, int K, int H, int E, int B, int rank, int world, int packed, PeerPtrs xq, PeerPtrs sf, PeerPtrs row_aff,
     PeerPtrs row_src, int64_t cap_rows, PlanOut plan) {
@@ -229,30 +229,23 @@ __global__ void __launch_bounds__(256) ep_dispatch_quantize_kernel(
     plan_rows(s_total, s_first, rank, world, E, B, plan.n_blocks_cap, plan.block_to_expert, plan.conditions,
               plan.row_valid, plan.tile_flags, plan.status, static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x,
               static_cast<int64_t>(gridDim.x) * blockDim.x);
-  // Every rank starts with the pairs bound for the rank after it and wraps around, so that at any moment the
-  // ranks store into different GPUs (pairs are sorted by expert, i.e. by destination): in plain order all of them
-  // would write to rank 0 first, then to rank 1, ..., each time through a single GPU's ingress.
-  const int64_t rot = s_prefix[((rank + 1) % world) * E_L];
+  // Token-major: a thread quantises one 32-element block of a token's row once and stores it to every GPU that
+  // owns one of the token's experts (`pair_of_token[t, k]` = index of that (token, k) pair in the expert-sorted
+  // list, or -1), so `hidden` is read and quantised once per token, not once per pair.  A token's experts are
+  // spread over the ranks, so at any moment the ranks of the group store into different GPUs (walking the sorted
+  // pairs instead, all ranks would write to rank 0 first, then to rank 1, ..., each time through one ingress).
   const int blocks_per_row = H >> 5;
-  const int64_t k_atoms = (H + 127) >> 7;
   const int64_t n_pairs = static_cast<int64_t>(T) * K;
-  const int64_t total = n_pairs * blocks_per_row;
+  const int64_t total = static_cast<int64_t>(T) * blocks_per_row;
   const int64_t total_padded = (total + 31) & ~static_cast<int64_t>(31);  // whole warps stay in the loop (shuffles)
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_padded;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const bool live = i < total;
-    const int64_t p_seq = live ? i / blocks_per_row : 0;
-    const int kb = live ? static_cast<int>(i - p_seq * blocks_per_row) : 0;
-    const int64_t p = p_seq + rot < n_pairs ? p_seq + rot : p_seq + rot - n_pairs;
-    const int tok = live ? pair_token[p] : -1;
-    const int e = live ? pair_expert[p] : -1;
-    const bool ok = tok >= 0 && tok < T && e >= 0 && e < E;
-    const int d = ok ? e / E_L : 0;
-    const int64_t row = ok ? static_cast<int64_t>(s_base[e]) + (p - s_prefix[e]) : 0;
-    const bool in_cap = ok && row < cap_rows;
+    const int tok = live ? static_cast<int>(i / blocks_per_row) : 0;
+    const int kb = live ? static_cast<int>(i - static_cast<int64_t>(tok) * blocks_per_row) : 0;
     uint32_t c[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     uint32_t scale = 0;
-    if (in_cap) {
+    if (live) {
       const __nv_bfloat16* src = hidden + static_cast<int64_t>(tok) * H;
       float v[32];
       if (!packed) {
@@ -284,18 +277,58 @@ __global__ void __launch_bounds__(256) ep_dispatch_quantize_kernel(
     const uint32_t s1 = __shfl_sync(0xffffffffu, scale, (lane & ~3) + 1);
     const uint32_t s2 = __shfl_sync(0xffffffffu, scale, (lane & ~3) + 2);
     const uint32_t s3 = __shfl_sync(0xffffffffu, scale, (lane & ~3) + 3);
-    if (!in_cap) continue;
-    // one 32-byte store per thread: a warp covers 1 KB of the row with whole sectors (two 16-byte stores would
-    // each touch half of every sector, which NVLink carries as twice the packets)
-    st_peer_256(static_cast<uint8_t*>(xq.p[d]) + row * H + kb * 32, c);
-    if ((kb & 3) == 0) {
-      const uint32_t cell = scale | (s1 << 8) | (s2 << 16) | (s3 << 24);
-      *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(sf.p[d]) + sf_atom_offset(row, kb, k_atoms)) = cell;
+    const uint32_t cell = scale | (s1 << 8) | (s2 << 16) | (s3 << 24);
+    // Scale bytes travel row-major ([row][H / 32], re-laid into 512-byte atoms by the receiver): when a warp holds 32
+    // blocks of one row its 32 scale bytes leave as one 32-byte store from lane 0 -- as 4-byte cells scattered over
+    // the atoms they were a third of the dispatch time (eight tiny NVLink writes per warp and destination).
+    const bool warp_row = (blocks_per_row & 31) == 0;
+    uint32_t cells[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cells[j] = __shfl_sync(0xffffffffu, cell, 4 * j);
+    if (!live) continue;
+    for (int k = 0; k < K; ++k) {
+      const int64_t p = pair_of_token[static_cast<int64_t>(tok) * K + k];
+      if (p < 0 || p >= n_pairs) continue;
+      const int e = pair_expert[p];
+      if (e < 0 || e >= E) continue;
+      const int d = e / E_L;
+      const int64_t row = static_cast<int64_t>(s_base[e]) + (p - s_prefix[e]);
+      if (row >= cap_rows) continue;  // receive buffer too small: the receiver's plan reports it
+      // one 32-byte store per thread: a warp covers 1 KB of the row with whole sectors (two 16-byte stores would
+      // each touch half of every sector, which NVLink carries as twice the packets)
+      st_peer_256(static_cast<uint8_t*>(xq.p[d]) + row * H + kb * 32, c);
+      uint8_t* sf_row = static_cast<uint8_t*>(sf.p[d]) + row * blocks_per_row;
+      if (warp_row) {
+        if (lane == 0) st_peer_256(sf_row + kb, cells);
+      } else if ((kb & 3) == 0) {
+        *reinterpret_cast<uint32_t*>(sf_row + kb) = cell;
+      }
+      if (kb == 0) {
+        static_cast<float*>(row_aff.p[d])[row] = aff[static_cast<int64_t>(tok) * E + e];
+        static_cast<int32_t*>(row_src.p[d])[row] = (rank << 24) | static_cast<int32_t>(p);
+      }
     }
-    if (kb == 0) {
-      static_cast<float*>(row_aff.p[d])[row] = aff[static_cast<int64_t>(tok) * E + e];
-      static_cast<int32_t*>(row_src.p[d])[row] = (rank << 24) | static_cast<int32_t>(p);
-    }
+  }
+}
+
+// Receiver side: scale bytes arrive row-major; the contraction's TMA reads 512-byte atoms (128 rows x one 128-wide
+// K slab).  A warp builds one atom: lane l owns rows l, l+32, l+64, l+96 and writes their four cells as 16 bytes.
+__global__ void __launch_bounds__(256) ep_scales_to_atoms_kernel(const uint8_t* __restrict__ sf_rows,
+                                                                 const int32_t* __restrict__ tile_flags,
+                                                                 int64_t n_tiles, int k_atoms, uint8_t* sf_atoms) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t total = n_tiles * k_atoms;
+  const int blocks_per_row = k_atoms * 4;
+  for (int64_t w = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; w < total; w += warps) {
+    const int64_t t = w / k_atoms;
+    const int a = static_cast<int>(w - t * k_atoms);
+    if (tile_flags[t] <= 0) continue;  // no row of this tile holds a token
+    uint32_t c[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      c[j] = *reinterpret_cast<const uint32_t*>(sf_rows + (t * 128 + lane + 32 * j) * blocks_per_row + a * 4);
+    *reinterpret_cast<uint4*>(sf_atoms + w * 512 + lane * 16) = make_uint4(c[0], c[1], c[2], c[3]);
   }
 }
 
@@ -434,7 +467,7 @@ extern "C" int b200moe_ep_plan(const int32_t* counts_all, int rank, int world, i
   return B200MOE_OK;
 }
 
-extern "C" int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32_t* pair_token,
+extern "C" int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32_t* pair_of_token,
                                             const int32_t* pair_expert, const float* affinities,
                                             const int32_t* counts_all, int T, int K, int H, int E, int B, int rank,
                                             int world, int h_packed_order, void* const* xq_peers,
@@ -442,7 +475,7 @@ extern "C" int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32
                                             int64_t cap_rows, int n_blocks_cap, int32_t* block_to_expert,
                                             int32_t* conditions, int32_t* row_valid, int32_t* tile_flags,
                                             int32_t* status, b200moe_stream_t stream) {
-  B200MOE_REQUIRE(hidden_bf16 && pair_token && pair_expert && affinities && counts_all, B200MOE_ERR_INVALID,
+  B200MOE_REQUIRE(hidden_bf16 && pair_of_token && pair_expert && affinities && counts_all, B200MOE_ERR_INVALID,
                   "ep_dispatch_quantize: null argument");
   PlanOut plan{n_blocks_cap, block_to_expert, conditions, row_valid, tile_flags, status};
   if (block_to_expert != nullptr)
@@ -462,11 +495,28 @@ extern "C" int b200moe_ep_dispatch_quantize(const void* hidden_bf16, const int32
   for (int i = 0; i < world; ++i)
     B200MOE_REQUIRE(reinterpret_cast<uintptr_t>(xq.p[i]) % 32 == 0, B200MOE_ERR_INVALID,
                     "ep_dispatch_quantize: activation buffers must be 32-byte aligned");
-  const int64_t work = static_cast<int64_t>(T) * K * (H / 32);
+  for (int i = 0; i < world; ++i)
+    B200MOE_REQUIRE(reinterpret_cast<uintptr_t>(sf.p[i]) % 32 == 0, B200MOE_ERR_INVALID,
+                    "ep_dispatch_quantize: scale buffers must be 32-byte aligned");
+  const int64_t work = static_cast<int64_t>(T) * (H / 32);
   ep_dispatch_quantize_kernel<<<grid_cap(work, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(hidden_bf16), pair_token, pair_expert, affinities, counts_all, T, K, H, E, B,
+      static_cast<const __nv_bfloat16*>(hidden_bf16), pair_of_token, pair_expert, affinities, counts_all, T, K, H, E, B,
       rank, world, h_packed_order, xq, sf, ra, rs, cap_rows, plan);
   B200MOE_LAUNCH_OK("ep_dispatch_quantize_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_ep_scales_to_atoms(const uint8_t* sf_rows, const int32_t* tile_flags, int64_t n_tiles, int H,
+                                          uint8_t* sf_atoms, b200moe_stream_t stream) {
+  B200MOE_REQUIRE(sf_rows && tile_flags && sf_atoms, B200MOE_ERR_INVALID, "ep_scales_to_atoms: null argument");
+  B200MOE_REQUIRE(n_tiles > 0 && H > 0 && H % 128 == 0, B200MOE_ERR_INVALID,
+                  "ep_scales_to_atoms: H must be a multiple of 128 and n_tiles positive");
+  B200MOE_REQUIRE(reinterpret_cast<uintptr_t>(sf_rows) % 4 == 0 && reinterpret_cast<uintptr_t>(sf_atoms) % 16 == 0,
+                  B200MOE_ERR_INVALID, "ep_scales_to_atoms: misaligned buffer");
+  const int k_atoms = H / 128;
+  ep_scales_to_atoms_kernel<<<grid_cap(n_tiles * k_atoms * 32, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      sf_rows, tile_flags, n_tiles, k_atoms, sf_atoms);
+  B200MOE_LAUNCH_OK("ep_scales_to_atoms_kernel");
   return B200MOE_OK;
 }
 

@@ -226,9 +226,11 @@ class PeerExpertParallelMoE:
         self.rank = dist.get_rank(group)
         # The down contraction can store its rows into the peers itself (no separate return launch).  Its epilogue
         # owns one row per thread and stores 32 bytes at a time; measured per step on B200 / NVSwitch against the
-        # separate, fully coalesced copy kernel: 1.423 vs 1.470 ms at 2 ranks, 1.482 vs 1.546 ms at 4, 1.473 vs
-        # 1.532 ms at 8.  (With 16-byte stores it lost everywhere beyond 2 ranks.)
-        self.fuse_return = True if fuse_return is None else bool(fuse_return)
+        # separate, fully coalesced copy kernel at I = 14336: 1.423 vs 1.470 ms at 2 ranks, 1.482 vs 1.546 ms at 4,
+        # 1.473 vs 1.532 ms at 8.  A result row of H bf16 values costs 2*H*I flop, so with a small I the rows leave
+        # faster than NVLink carries 32-byte pieces and the epilogue stalls the MMAs: at I = 1536 (32768 tokens,
+        # top-8, 2 ranks) the fused form took 4.37 ms per step, the separate copy 4.17 ms.
+        self.fuse_return = (weights.I >= 4096) if fuse_return is None else bool(fuse_return)
         fuse_return = self.fuse_return
         _lib.kernel_assert(num_experts % self.world == 0,
                            f"num_experts ({num_experts}) must be divisible by the number of ranks ({self.world})")
@@ -248,16 +250,17 @@ class PeerExpertParallelMoE:
             "counts": (self.world * self.E * 4, torch.int32),
             "row_aff": (self.cap_rows * 4, torch.float32),
             "row_src": (self.cap_rows * 4, torch.int32),
-            "sf": (lib.b200moe_sf_bytes(self.cap_rows, self.H), torch.uint8),
+            "sf_rows": (self.cap_rows * (self.H // 32), torch.uint8),   # scale bytes as they arrive: [row][H / 32]
             "xq": (self.cap_rows * self.H, torch.uint8),
             "back": (pairs * self.H * 2, torch.bfloat16),
         }
         self.mem = PeerArena(layout, dev, group)
         v = self.mem.views
         self.counts_all, self.row_aff, self.row_src = v["counts"], v["row_aff"], v["row_src"]
-        self.xq, self.sf, self.back = v["xq"], v["sf"], v["back"].view(pairs, self.H)
+        self.xq, self.sf_rows, self.back = v["xq"], v["sf_rows"], v["back"].view(pairs, self.H)
+        self.sf = torch.zeros(lib.b200moe_sf_bytes(self.cap_rows, self.H), dtype=torch.uint8, device=dev)  # atoms, local
         self.p_flags, self.p_counts = self.mem.peers("flags"), self.mem.peers("counts")
-        self.p_xq, self.p_sf = self.mem.peers("xq"), self.mem.peers("sf")
+        self.p_xq, self.p_sf = self.mem.peers("xq"), self.mem.peers("sf_rows")
         self.p_aff, self.p_src, self.p_back = self.mem.peers("row_aff"), self.mem.peers("row_src"), self.mem.peers("back")
         # receiver-side plan and scratch (local)
         self.b2e = torch.zeros(self.n_blocks_cap, dtype=torch.int32, device=dev)
@@ -282,16 +285,16 @@ class PeerExpertParallelMoE:
         self.gstatus = torch.zeros(1, dtype=torch.int32, device=dev)
         self.gws = torch.empty(lib.b200moe_group_tokens_workspace_bytes(self.T, self.E), dtype=torch.uint8, device=dev)
         self.timers = None
-        # router 2, grouping 3, count exchange, dispatch (+ plan), wait, contractions (CTA-pair launch + left-over
-        # launch each when the block size allows pairs), return, wait, combine
-        self.kernels_per_forward = (2 + 3 + 1 + 1 + 1 + (4 if self.B % 256 == 0 else 2) + (0 if fuse_return else 1)
+        # router 2, grouping 3, count exchange, dispatch (+ plan), wait, scale re-layout, contractions (CTA-pair
+        # launch + left-over launch each when the block size allows pairs), return, wait, combine
+        self.kernels_per_forward = (2 + 3 + 1 + 1 + 1 + 1 + (4 if self.B % 256 == 0 else 2) + (0 if fuse_return else 1)
                                     + 1 + 1)
         self._graph = None
 
     def forward(self, hidden: torch.Tensor) -> torch.Tensor:
         """``hidden [tokens_per_rank, H]`` bf16 -> bf16 ``[tokens_per_rank, H]`` (this rank's tokens).
 
-        Thirteen or fourteen launches of this library's kernels on the current stream, nothing else: no allocation, no
+        Fourteen or fifteen launches of this library's kernels on the current stream, nothing else: no allocation, no
         collective call, no host synchronisation.  Every rank of the group must call it the same number of times.
         """
         _lib.kernel_assert(tuple(hidden.shape) == (self.T, self.H) and hidden.dtype == torch.bfloat16,
@@ -317,12 +320,14 @@ class PeerExpertParallelMoE:
         _lib.call("b200moe_ep_exchange_counts", _lib.ptr(self.counts), self.p_counts, self.p_flags, self.rank, G, E,
                   epoch, status, st)
         mark("t0")
-        _lib.call("b200moe_ep_dispatch_quantize", _lib.ptr(hidden), _lib.ptr(self.pair_token), _lib.ptr(self.pair_expert),
+        _lib.call("b200moe_ep_dispatch_quantize", _lib.ptr(hidden), _lib.ptr(self.inv), _lib.ptr(self.pair_expert),
                   _lib.ptr(self.aff), _lib.ptr(self.counts_all), T, K, H, E, B, self.rank, G, int(w.h_packed_order),
                   self.p_xq, self.p_sf, self.p_aff, self.p_src, self.cap_rows, self.n_blocks_cap,
                   _lib.ptr(self.b2e), _lib.ptr(self.cond), _lib.ptr(self.row_valid), _lib.ptr(self.tile_flags),
                   status, st)   # the receiver's plan rides in the same launch (it needs the count table only)
         _lib.call("b200moe_ep_signal_wait", self.p_flags, self.rank, G, 1, epoch, status, st)
+        _lib.call("b200moe_ep_scales_to_atoms", _lib.ptr(self.sf_rows), _lib.ptr(self.tile_flags), self.cap_rows // 128,
+                  H, _lib.ptr(self.sf), st)
         mark("t1")
         _lib.call("b200moe_grouped_gemm1_swiglu", _lib.ptr(self.xq), _lib.ptr(self.sf), _lib.ptr(w.w1),
                   _lib.ptr(w.w1_sf), w.w_format, _lib.ptr(w.bias_gu), _lib.ptr(self.b2e), _lib.ptr(self.cond),

@@ -20,12 +20,12 @@ pytestmark = pytest.mark.gpu
 E, K, H, I, B, T_LOCAL = 8, 2, 512, 256, 128, 300
 
 
-def _inputs(rank):
+def _inputs(rank, h=H):
     from moe_testlib import bf16_values, make_rows_weights
     rng = np.random.default_rng(200 + rank)
-    hidden = bf16_values(rng.standard_normal((T_LOCAL, H)).astype(np.float32))
-    router_w = bf16_values((np.random.default_rng(3).standard_normal((H, E)) * 0.05).astype(np.float32))
-    return hidden, router_w, make_rows_weights(E, H, I, seed=9)
+    hidden = bf16_values(rng.standard_normal((T_LOCAL, h)).astype(np.float32))
+    router_w = bf16_values((np.random.default_rng(3).standard_normal((h, E)) * 0.05).astype(np.float32))
+    return hidden, router_w, make_rows_weights(E, h, I, seed=9)
 
 
 def _zipf_bias(s=1.2):
@@ -72,11 +72,13 @@ def _worker(rank, world, port, results, backend, zipf=False, capacity_factor=2.5
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("hidden_size", [512, 1024])
 @pytest.mark.parametrize("fuse_return", [True, False])
-def test_peer_memory_exchange_single_rank(fuse_return):
+def test_peer_memory_exchange_single_rank(fuse_return, hidden_size):
     """World size 1: every 'peer' is this GPU, so the dispatch / plan / return kernels run without a second device.
     ``fuse_return``: the down contraction stores its rows into the (peer) result buffer itself, or a separate
-    kernel copies them out of y_pos."""
+    kernel copies them out of y_pos.  ``hidden_size`` 1024: a warp of the dispatch holds 32 blocks of one row and
+    sends their scale bytes as one 32-byte store; 512: two rows per warp, 4-byte cells."""
     import nki_library_b200 as m
     from moe_testlib import bf16_values, max_rel
     from nki_library_b200.ep import PeerExpertParallelMoE
@@ -85,7 +87,7 @@ def test_peer_memory_exchange_single_rank(fuse_return):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29733")
     dist.init_process_group("gloo", rank=0, world_size=1)
     try:
-        hidden, router_w, w_np = _inputs(0)
+        hidden, router_w, w_np = _inputs(0, hidden_size)
         full = m.prepare_from_rows(*(torch.from_numpy(a).cuda() for a in w_np))
         x = torch.from_numpy(hidden).to(torch.bfloat16).cuda()
         layer = PeerExpertParallelMoE(torch.from_numpy(router_w).cuda(), full, E, K, B, T_LOCAL,
