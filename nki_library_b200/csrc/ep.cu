@@ -1,19 +1,23 @@
 // Expert-parallel dispatch and combine over peer memory (NVLink / NVSwitch), one process per GPU.
 //
 // Every rank exposes four buffers to its peers through CUDA IPC: the quantised activation rows its
-// experts will consume (codes + scale atoms, already in the block layout the grouped contraction
-// reads), per-row affinity and origin, a per-source count table, and the rows coming back to it.
+// experts will consume (codes in the block layout the grouped contraction reads, scale bytes per row),
+// per-row affinity and origin, a per-source count table, and the rows coming back to it.
 // A step needs no host synchronisation and no collective library call:
 //
 //   exchange_counts   each rank stores its per-expert pair counts into every peer's table, then all
 //                     ranks wait for one another (flag words written with system-scope release)
-//   dispatch_quantize MXFP8-quantises each (token, k) pair's hidden row and stores codes, scales,
-//                     affinity and origin straight into the owning rank's buffers at the row the
-//                     receiver's block layout assigns to it (computed from the count table)
-//   plan              the receiver derives block_to_expert / conditions / row validity locally
+//   dispatch_quantize MXFP8-quantises each token's hidden row once and stores codes, scale bytes
+//                     (row-major), affinity and origin straight into the buffers of every rank that
+//                     owns one of the token's experts, at the row the receiver's block layout assigns
+//                     to that (token, k) pair (computed from the count table); the same launch writes
+//                     this rank's own receive plan (block_to_expert / conditions / row validity)
 //   signal_wait       "my stores are done" flags, waited for before the contractions start
+//   scales_to_atoms   local: the scale bytes that arrived row-major go into the 512-byte atoms the
+//                     contractions read
 //   return_rows       after the down contraction each result row is stored into its origin
-//                     rank's return buffer; a last signal_wait precedes the local combine
+//                     rank's return buffer (or the contraction's epilogue does so itself); a last
+//                     signal_wait precedes the local combine
 //
 // All waits are bounded (about two seconds) and report through a status word.
 #include <cuda.h>
