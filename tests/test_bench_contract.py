@@ -33,3 +33,30 @@ def test_reference_arm_prints_one_contract_line():
 def test_reference_arm_other_ranks_stay_silent():
     """Under a multi-rank launch only rank 0 runs the host arm; the others exit 0 without output."""
     assert _run({"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"}) == []
+
+
+def test_gpu_local_cpu_binding_uses_the_nvml_mask(monkeypatch):
+    """``bind_to_gpu_cpus`` narrows the process to the CPUs NVML reports for the GPU (a fake NVML here), keeps the
+    placement when the mask covers everything or nothing, and never raises."""
+    import types
+    sys.path.insert(0, ROOT)
+    import bench
+    allowed = set(range(8))
+    calls = []
+    fake = types.SimpleNamespace(nvmlInit=lambda: None, nvmlDeviceGetHandleByIndex=lambda i: ("gpu", i),
+                                 nvmlDeviceGetCpuAffinity=lambda h, n: [0b00001111] + [0] * (n - 1))
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    monkeypatch.setattr(os, "sched_getaffinity", lambda pid: set(allowed), raising=False)
+    monkeypatch.setattr(os, "sched_setaffinity", lambda pid, cpus: calls.append(set(cpus)), raising=False)
+    monkeypatch.delenv("CUDA_VISIBLE_DEVICES", raising=False)
+    assert bench.bind_to_gpu_cpus(0).startswith("gpu-local (4 of 8")
+    assert calls == [{0, 1, 2, 3}]
+    fake.nvmlDeviceGetCpuAffinity = lambda h, n: [0xFF] + [0] * (n - 1)      # mask = everything allowed
+    assert bench.bind_to_gpu_cpus(0).startswith("unchanged") and len(calls) == 1
+    fake.nvmlDeviceGetCpuAffinity = lambda h, n: [0xFF00] + [0] * (n - 1)    # mask disjoint from the allowed set
+    assert bench.bind_to_gpu_cpus(0).startswith("unchanged") and len(calls) == 1
+
+    def broken(h, n):
+        raise RuntimeError("no NVML")
+    fake.nvmlDeviceGetCpuAffinity = broken
+    assert bench.bind_to_gpu_cpus(0) == "unchanged (RuntimeError)"
