@@ -320,15 +320,16 @@ int b200moe_rmsnorm_quantize_mxfp8(const void* inp_bf16, const void* residual_bf
  *
  * Step order on every rank's stream: exchange_counts -> dispatch_quantize (which also writes the receiver's
  * plan when given its outputs; b200moe_ep_plan is the same computation as a launch of its own) ->
- * signal_wait(slot 1) -> scales_to_atoms -> grouped_gemm1 / grouped_gemm2 (token_position_to_id = row_valid, hidden_rows =
- * cap_rows, per-row affinities) -> return_rows -> signal_wait(slot 2) -> combine.  A wait that runs out
- * (about two seconds) or a receive buffer that is too small sets *status non-zero.
+ * signal_wait(slot 1) -> scales_to_atoms -> grouped_gemm1 / grouped_gemm2 (token_position_to_id = row_valid,
+ * hidden_rows = cap_rows, per-row affinities) -> return_rows -> signal_wait(slot 2) -> combine.  A wait that
+ * runs out (about two seconds) or a receive buffer that is too small sets *status non-zero.
  * dispatch_quantize walks the tokens: pair_of_token int32 [T, K] holds, for every (token, k), the index of that
  * pair in the expert-sorted list (the inverse table b200moe_group_tokens writes at block size 1; -1 = none) and
  * pair_expert [T*K] the expert of every sorted pair; a token's row is quantised once and stored to each GPU
- * that owns one of its experts (codes into xq_peers, scale bytes row-major into sf_peers = the receivers' sf_rows).  Plan outputs (block_to_expert == NULL: none):
- * block_to_expert / conditions [n_blocks_cap (+2)], row_valid [n_blocks_cap * B], tile_flags
- * [n_blocks_cap * B / 128], all in this rank's own memory; they depend on the count table only. */
+ * that owns one of its experts (codes into xq_peers, scale bytes row-major into sf_peers = the receivers'
+ * sf_rows).  Plan outputs (block_to_expert == NULL: none): block_to_expert / conditions [n_blocks_cap (+2)],
+ * row_valid [n_blocks_cap * B], tile_flags [n_blocks_cap * B / 128], all in this rank's own memory; they depend
+ * on the count table only. */
 int b200moe_ipc_export(const void* dev_ptr, void* handle_out_64, int64_t* offset_out);
 int b200moe_ipc_open(const void* handle_64, int64_t offset, void** dev_ptr_out);
 int b200moe_ipc_close(void* dev_ptr, int64_t offset);
