@@ -77,13 +77,6 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
       "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
       : "memory");
 }
-// Ask L2 for a weight slab without a shared-memory destination: extends the bytes in flight from HBM beyond what
-// the pipeline stages hold (weight-streaming shapes, where every weight byte is read once).
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int x, int y, int z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(map), "r"(x), "r"(y), "r"(z)
-               : "memory");
-}
-
 // ---- thread-block-pair (cta_group::2) variants --------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;
